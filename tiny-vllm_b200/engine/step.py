@@ -1,0 +1,249 @@
+"""The step function: one flat batch through the model, from the cache.
+
+A step is a list of entries (request, its next tokens, the places among them
+whose logits are wanted).  Portions of prompts stand beside single decoded
+tokens, cut anywhere.  The step runs only the tokens it is given, writes their
+keys and values into the pages the cache manager assigns, and returns the
+logits at the wanted places as float32 ``[wanted, vocab]``.
+
+Counterparts in the reference: the flat batch of tinyvllm/batch.py:100-136, the
+device inputs of tinyvllm/runtime/contracts.py:47-145 and
+tinyvllm/runtime/inputs.py:14-137, the checks of tinyvllm/runtime/runner.py:101-193
+and ``ModelRunner.run`` (:196-246).  Differences: metadata is int32 and goes up
+in one copy for every kind of batch; logits can be wanted at any place of an
+entry, not only its last token; there is no per-request loop on the host.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, StepCachePlan
+from ..cache.storage import CacheStorage, bytes_per_page, group_runs
+from ..ops import attention as attention_ops
+
+
+class StepError(ValueError):
+    """A step was asked for something the engine cannot run."""
+
+
+class OutOfPages(RuntimeError):
+    """The page pool cannot hold the tokens of this step."""
+
+
+@dataclass(frozen=True)
+class StepEntry:
+    request_id: object
+    tokens: tuple[int, ...]
+    want: tuple[int, ...] = ()          # places among ``tokens`` whose logits are wanted
+
+
+@dataclass
+class StepContext:
+    """Everything a part may read about the running step (device tensors are int32)."""
+
+    storage: CacheStorage
+    num_tokens: int
+    num_rows: int
+    num_wanted: int
+    token_ids: torch.Tensor              # [tokens]
+    positions: torch.Tensor              # [tokens] absolute position of each token
+    token_row: torch.Tensor              # [tokens] index of the token's entry, -1 for padding
+    want_rows: torch.Tensor              # [wanted] flat token index of each wanted place
+    state_slots: torch.Tensor            # [rows] state slot of each entry
+    row_starts: torch.Tensor             # [rows + 1] first flat token of each entry
+    slots: list[torch.Tensor]            # per group [tokens]: cache slot each token is written to
+    block_tables: list[torch.Tensor]     # per group [rows, blocks]
+    cache_sources: tuple                 # per run: the run whose cache it reads, or None
+    max_position: int                    # largest position in the step (bounds the split of attention)
+    split_chunks: int                    # 0: walk the keys per row; n: spread n chunks over the grid
+    workspace_of: object = None          # callable(floats) -> float32 scratch tensor
+    # host copies, for parts that plan on the host (and for tests)
+    host_rows: tuple = ()                # (request_id, first position, count, state_slot, fresh) per entry
+
+    def writes_cache(self, run: int) -> bool:
+        return self.cache_sources[run] is None
+
+    def workspace(self, floats: int) -> torch.Tensor:
+        return self.workspace_of(floats)
+
+    def attend(self, mixer, qkv, keys, values, group: int):
+        return attention_ops.paged_attention(self, mixer, qkv, keys, values, group)
+
+
+class StepRunner:
+    """Model + cache + the step function that generation, replay and tests all use."""
+
+    def __init__(self, model, *, page_size: int, num_pages, max_requests: int,
+                 max_model_len: int | None = None) -> None:
+        self.model = model
+        self.device = model.device
+        self.dtype = model.dtype
+        self.page_size = page_size
+        self.max_model_len = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
+        needs = model.cache_needs()
+        self.cache_sources = tuple(model.cache_sources())
+        groups, where = group_runs(needs, list(self.cache_sources))
+        if isinstance(num_pages, int):
+            num_pages = [num_pages] * len(groups)
+        self.manager = CacheManager(groups, page_size, list(num_pages), max_requests)
+        self.storage = CacheStorage(groups, where, needs, page_size=page_size,
+                                    pages_per_group=list(num_pages), num_state_slots=max_requests,
+                                    dtype=self.dtype, device=self.device)
+        self.vocab_size = model.spec.vocab_size
+        self._pinned: torch.Tensor | None = None
+        self._pinned_free: torch.cuda.Event | None = None
+        self._workspace: torch.Tensor | None = None
+
+    # ------------------------------------------------------------- sizing
+    @staticmethod
+    def bytes_per_token(model, dtype: torch.dtype) -> int:
+        """Cache bytes one token takes in all groups (windows count as full here)."""
+        needs = model.cache_needs()
+        groups, _ = group_runs(needs, model.cache_sources())
+        return sum(bytes_per_page(g, 1, torch.empty((), dtype=dtype).element_size()) for g in groups)
+
+    # ----------------------------------------------------------- requests
+    def open(self, request_id) -> int:
+        return self.manager.open(request_id)
+
+    def close(self, request_id) -> None:
+        self.manager.close(request_id)
+
+    # ------------------------------------------------------------ scratch
+    def _workspace_of(self, floats: int) -> torch.Tensor:
+        if self._workspace is None or self._workspace.numel() < floats:
+            if torch.cuda.is_current_stream_capturing():
+                raise StepError("scratch memory must be sized before a graph is captured")
+            self._workspace = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
+        return self._workspace
+
+    def reserve_workspace(self, floats: int) -> None:
+        self._workspace_of(floats)
+
+    # --------------------------------------------------------------- steps
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        for entry in entries:
+            if not entry.tokens:
+                raise StepError(f"request {entry.request_id!r}: an entry needs at least one token")
+            if not self.manager.is_open(entry.request_id):
+                raise StepError(f"request {entry.request_id!r} is not open")
+            for token in entry.tokens:
+                if type(token) is not int or not 0 <= token < self.vocab_size:
+                    raise StepError(f"request {entry.request_id!r}: {token!r} is not a token id "
+                                    f"below {self.vocab_size}")
+            for place in entry.want:
+                if type(place) is not int or not 0 <= place < len(entry.tokens):
+                    raise StepError(f"request {entry.request_id!r}: wanted place {place!r} is not "
+                                    f"among its {len(entry.tokens)} tokens")
+            end = self.manager.length(entry.request_id) + len(entry.tokens)
+            if end > self.max_model_len:
+                raise StepError(f"request {entry.request_id!r} would reach {end} tokens, "
+                                f"the limit is {self.max_model_len}")
+
+    def plan(self, entries: Sequence[StepEntry]) -> StepCachePlan | None:
+        """Check the entries and take their pages; None when pages run out."""
+        self.validate(entries)
+        return self.manager.plan([(e.request_id, len(e.tokens)) for e in entries])
+
+    def build_context(self, entries: Sequence[StepEntry], plan: StepCachePlan,
+                      *, split_chunks: int | None = None) -> StepContext:
+        """Lower entries + cache plan to device tensors (one pinned buffer, one copy)."""
+        rows = len(entries)
+        counts = [len(e.tokens) for e in entries]
+        tokens = sum(counts)
+        wanted = sum(len(e.want) for e in entries)
+        groups = len(self.manager.groups)
+        blocks = [max(1, max(len(p.tables[g]) for p in plan.entries)) for g in range(groups)]
+        sizes = [tokens, tokens, tokens, wanted, rows, rows + 1]
+        for g in range(groups):
+            sizes += [tokens, rows * blocks[g]]
+        offsets = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
+        host = np.zeros(int(offsets[-1]), dtype=np.int32)
+
+        def view(i):
+            return host[offsets[i]:offsets[i] + sizes[i]]
+
+        cursor, wanted_cursor, max_position = 0, 0, 0
+        row_starts = view(5)
+        for r, (entry, planned) in enumerate(zip(entries, plan.entries)):
+            n = counts[r]
+            view(0)[cursor:cursor + n] = entry.tokens
+            view(1)[cursor:cursor + n] = np.arange(planned.start, planned.start + n, dtype=np.int32)
+            view(2)[cursor:cursor + n] = r
+            for place in entry.want:
+                view(3)[wanted_cursor] = cursor + place
+                wanted_cursor += 1
+            view(4)[r] = planned.state_slot
+            row_starts[r] = cursor
+            for g in range(groups):
+                view(6 + 2 * g)[cursor:cursor + n] = planned.slots[g]
+                table = planned.tables[g]
+                view(7 + 2 * g)[r * blocks[g]:r * blocks[g] + len(table)] = table
+            max_position = max(max_position, planned.start + n - 1)
+            cursor += n
+        row_starts[rows] = cursor
+
+        device = self._upload(host)
+
+        def dview(i):
+            return device[int(offsets[i]):int(offsets[i]) + sizes[i]]
+
+        if split_chunks is None:
+            split_chunks = attention_ops.choose_split(tokens, max_position)
+        fresh = [p.state_slot for p in plan.entries if p.fresh_state]
+        self.storage.clear_state(fresh)
+        return StepContext(
+            storage=self.storage, num_tokens=tokens, num_rows=rows, num_wanted=wanted,
+            token_ids=dview(0), positions=dview(1), token_row=dview(2), want_rows=dview(3),
+            state_slots=dview(4), row_starts=dview(5),
+            slots=[dview(6 + 2 * g) for g in range(groups)],
+            block_tables=[dview(7 + 2 * g).view(rows, blocks[g]) for g in range(groups)],
+            cache_sources=self.cache_sources, max_position=max_position, split_chunks=split_chunks,
+            workspace_of=self._workspace_of,
+            host_rows=tuple((p.request_id, p.start, p.count, p.state_slot, p.fresh_state)
+                            for p in plan.entries),
+        )
+
+    def _upload(self, host: np.ndarray) -> torch.Tensor:
+        count = host.shape[0]
+        if self._pinned is None or self._pinned.numel() < count:
+            if self._pinned_free is not None:
+                self._pinned_free.synchronize()
+            self._pinned = torch.empty(max(count, 1 << 16), dtype=torch.int32, pin_memory=True)
+            self._pinned_free = None
+        if self._pinned_free is not None:
+            self._pinned_free.synchronize()          # the previous step's copy has left the buffer
+        self._pinned[:count].numpy()[:] = host
+        device = torch.empty(count, dtype=torch.int32, device=self.device)
+        device.copy_(self._pinned[:count], non_blocking=True)
+        self._pinned_free = torch.cuda.Event()
+        self._pinned_free.record()
+        return device
+
+    def execute(self, ctx: StepContext) -> torch.Tensor | None:
+        return self.model.forward(ctx)
+
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+        """Plan, run and commit one step; raises :class:`OutOfPages` if it does not fit."""
+        entries = list(entries)
+        plan = self.plan(entries)
+        if plan is None:
+            raise OutOfPages(
+                "the page pool is too small for this step: "
+                + ", ".join(f"group {g} has {self.manager.free_pages(g)} free pages"
+                            for g in range(len(self.manager.groups))))
+        try:
+            ctx = self.build_context(entries, plan)
+            logits = self.execute(ctx)
+        except BaseException:
+            self.manager.rollback(plan)
+            raise
+        self.manager.commit(plan)
+        return logits

@@ -1,0 +1,8 @@
+"""CUDA kernels of the package and their Python face."""
+
+from .build import KernelBuildError, compile_all, compile_library, load_library, source_names
+from .kernels import KernelError
+from .linear import linear
+
+__all__ = ["KernelBuildError", "KernelError", "compile_all", "compile_library", "linear",
+           "load_library", "source_names"]

@@ -1,0 +1,300 @@
+"""Python face of the CUDA kernels: tensors in, launch on the current stream.
+
+Every function checks shapes and dtypes, refuses what its kernel does not take
+with a clear error, and raises :class:`KernelError` if the launch fails.  There
+is no other implementation behind these functions: without a GPU and a built
+library they raise.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or its launch failed."""
+
+
+def dtype_tag(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 and bfloat16, not {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: the kernel does not take these sizes")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise KernelError("the kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+_functions: dict[str, ctypes._CFuncPtr] = {}
+
+
+def _fn(library: str, name: str, argtypes, restype=c_int):
+    function = _functions.get(name)
+    if function is None:
+        function = getattr(load_library(library), name)
+        function.argtypes = argtypes
+        function.restype = restype
+        _functions[name] = function
+    return function
+
+
+# ------------------------------------------------------------------ embedding
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = table[ids[t]]; ids int32."""
+    _need_cuda(table, ids)
+    if ids.dtype != torch.int32 or ids.dim() != 1 or table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("embed_rows wants a contiguous [vocab, width] table and int32 ids [tokens]")
+    rows, (vocab, width) = ids.shape[0], table.shape
+    if out is None:
+        out = torch.empty((rows, width), dtype=table.dtype, device=table.device)
+    fn = _fn("pointwise", "tvb_embed_rows",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(table.data_ptr(), ids.data_ptr(), out.data_ptr(), rows, width, vocab,
+              dtype_tag(table.dtype), _stream()), "embed_rows")
+    return out
+
+
+# -------------------------------------------------------------------- RMSNorm
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual: torch.Tensor | None = None,
+             rows: torch.Tensor | None = None, out: torch.Tensor | None = None,
+             residual_out: torch.Tensor | None = None, want_residual: bool = True):
+    """RMSNorm over the last dimension of x [tokens, width].
+
+    With ``residual`` the rounded sum x + residual is normalised and returned as
+    the second result (the new residual stream).  With ``rows`` (int32) only
+    those rows are produced, in that order, and no residual is returned.
+    """
+    _need_cuda(x, weight, residual, rows)
+    if x.dim() != 2 or not x.is_contiguous() or weight.shape != (x.shape[1],):
+        raise KernelError("rms_norm wants contiguous x [tokens, width] and weight [width]")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype
+                                 or not residual.is_contiguous()):
+        raise KernelError("rms_norm: residual must match x")
+    width = x.shape[1]
+    if width * 4 > 200 * 1024:
+        raise KernelError(f"rms_norm: width {width} is larger than a row buffer of shared memory holds")
+    count = x.shape[0] if rows is None else rows.shape[0]
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("rms_norm: rows must be int32")
+    if out is None:
+        out = torch.empty((count, width), dtype=x.dtype, device=x.device)
+    if residual is not None and rows is None and want_residual and residual_out is None:
+        residual_out = torch.empty_like(x)
+    if rows is not None or residual is None:
+        residual_out = None
+    fn = _fn("pointwise", "tvb_rms_norm",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+              c_int, c_int, c_void_p])
+    _check(fn(x.data_ptr(), _ptr(residual), weight.data_ptr(), out.data_ptr(), _ptr(residual_out),
+              _ptr(rows), count, width, eps, dtype_tag(x.dtype), dtype_tag(weight.dtype), _stream()),
+           "rms_norm")
+    if residual is not None and rows is None:
+        return out, residual_out
+    return out
+
+
+# ------------------------------------------------------------- SiLU(gate) * up
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """round(round(silu(gate)) * up) of packed rows [tokens, 2 * inter]."""
+    _need_cuda(gate_up)
+    if gate_up.dim() != 2 or gate_up.shape[1] % 2 or not gate_up.is_contiguous():
+        raise KernelError("silu_mul wants contiguous [tokens, 2 * inter]")
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    fn = _fn("pointwise", "tvb_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(gate_up.data_ptr(), out.data_ptr(), rows, inter, dtype_tag(gate_up.dtype), _stream()),
+           "silu_mul")
+    return out
+
+
+# -------------------------------------------------------------- rotary tables
+def rope_tables(inv_freq: torch.Tensor, positions: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """float32 cos and sin of position * inv_freq[j], [positions, half]."""
+    _need_cuda(inv_freq)
+    if inv_freq.dtype != torch.float32 or inv_freq.dim() != 1:
+        raise KernelError("rope_tables wants float32 inv_freq [half]")
+    half = inv_freq.shape[0]
+    cos = torch.empty((positions, half), dtype=torch.float32, device=inv_freq.device)
+    sin = torch.empty_like(cos)
+    fn = _fn("pointwise", "tvb_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(inv_freq.data_ptr(), cos.data_ptr(), sin.data_ptr(), positions, half, _stream()),
+           "rope_tables")
+    return cos, sin
+
+
+# ------------------------------------ q/k norm + rotation + cache write, fused
+def qk_norm_rope_store(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: int,
+                       positions: torch.Tensor, q_weight: torch.Tensor | None,
+                       k_weight: torch.Tensor | None, eps: float,
+                       cos: torch.Tensor | None, sin: torch.Tensor | None,
+                       slots: torch.Tensor | None, key_cache: torch.Tensor | None,
+                       value_cache: torch.Tensor | None) -> None:
+    """In place on the packed projection [tokens, (num_q + 2 num_kv) * head_dim]: q heads are
+    normalised and rotated where they stand; k heads are normalised, rotated and written to
+    ``key_cache`` at ``slots``; v heads are copied to ``value_cache``.  Caches are
+    [pages, page_size, num_kv, head_dim]; without ``slots`` nothing is written."""
+    _need_cuda(qkv, positions, q_weight, k_weight, cos, sin, slots, key_cache, value_cache)
+    tokens = qkv.shape[0]
+    if qkv.dim() != 2 or not qkv.is_contiguous() or qkv.shape[1] != (num_q + 2 * num_kv) * head_dim:
+        raise KernelError("qk_norm_rope_store: qkv must be contiguous [tokens, (q + 2 kv) * head_dim]")
+    if head_dim % 2 or head_dim > 256:
+        raise KernelError(f"qk_norm_rope_store takes even head sizes up to 256, not {head_dim}")
+    if positions.dtype != torch.int32 or positions.shape != (tokens,):
+        raise KernelError("qk_norm_rope_store: positions must be int32 [tokens]")
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("qk_norm_rope_store: q and k norm weights come together")
+    weight_tag = dtype_tag(qkv.dtype)
+    if q_weight is not None:
+        if q_weight.shape != (head_dim,) or k_weight.shape != (head_dim,) or q_weight.dtype != k_weight.dtype:
+            raise KernelError("qk_norm_rope_store: norm weights must be [head_dim] of one dtype")
+        weight_tag = dtype_tag(q_weight.dtype)
+    table_positions = 0
+    if cos is not None:
+        if cos.dtype != torch.float32 or cos.shape != sin.shape or cos.shape[1] != head_dim // 2:
+            raise KernelError("qk_norm_rope_store: tables must be float32 [positions, head_dim / 2]")
+        table_positions = cos.shape[0]
+    if slots is not None:
+        want = key_cache.shape[2:] if key_cache is not None else None
+        if (slots.dtype != torch.int32 or slots.shape != (tokens,) or key_cache is None
+                or value_cache is None or tuple(want) != (num_kv, head_dim)
+                or key_cache.dtype != qkv.dtype or value_cache.shape != key_cache.shape
+                or not key_cache.is_contiguous() or not value_cache.is_contiguous()):
+            raise KernelError("qk_norm_rope_store: slots int32 [tokens]; caches contiguous "
+                              "[pages, page_size, num_kv, head_dim] of the dtype of qkv")
+    fn = _fn("pointwise", "tvb_qk_norm_rope_store",
+             [c_void_p] * 9 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p])
+    _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
+              positions.data_ptr(), _ptr(slots), _ptr(key_cache), _ptr(value_cache), tokens, num_q,
+              num_kv, head_dim, table_positions, eps, dtype_tag(qkv.dtype), weight_tag, _stream()),
+           "qk_norm_rope_store")
+
+
+# ------------------------------------------------------------------ attention
+_chunk_keys: int | None = None
+
+
+def attention_chunk_keys() -> int:
+    global _chunk_keys
+    if _chunk_keys is None:
+        _chunk_keys = _fn("attention_rows", "tvb_attention_chunk_keys", [])()
+    return _chunk_keys
+
+
+def attention_rows_scratch_floats(tokens: int, num_q: int, head_dim: int, max_chunks: int) -> int:
+    return tokens * num_q * max_chunks * (head_dim + 2)
+
+
+def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor,
+                   value_cache: torch.Tensor, block_tables: torch.Tensor, token_row: torch.Tensor,
+                   positions: torch.Tensor, *, num_q: int, num_kv: int, head_dim: int,
+                   window: int | None, scale: float, out: torch.Tensor | None = None,
+                   scratch: torch.Tensor | None = None, max_chunks: int = 0) -> torch.Tensor:
+    """Paged causal attention, one warp per (token, head).
+
+    ``q`` holds the query heads of token t at ``t * q_token_stride`` elements
+    (the packed projection serves as it is).  ``max_chunks > 0`` spreads the
+    chunks of every row over the grid and needs ``scratch`` (float32, at least
+    :func:`attention_rows_scratch_floats` long); 0 walks them in one warp."""
+    _need_cuda(q, key_cache, value_cache, block_tables, token_row, positions, scratch)
+    tokens = positions.shape[0]
+    if head_dim > 256 or num_q % num_kv:
+        raise KernelError(f"attention_rows takes head sizes up to 256 and whole groups "
+                          f"(head_dim {head_dim}, {num_q} / {num_kv} heads)")
+    if key_cache.dim() != 4 or tuple(key_cache.shape[2:]) != (num_kv, head_dim) or \
+            value_cache.shape != key_cache.shape or key_cache.dtype != q.dtype or \
+            not key_cache.is_contiguous() or not value_cache.is_contiguous():
+        raise KernelError("attention_rows: caches must be contiguous [pages, page_size, num_kv, head_dim]")
+    for name, t in (("block_tables", block_tables), ("token_row", token_row), ("positions", positions)):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"attention_rows: {name} must be contiguous int32")
+    if block_tables.dim() != 2 or token_row.shape != (tokens,):
+        raise KernelError("attention_rows: block_tables [requests, blocks], token_row [tokens]")
+    if out is None:
+        out = torch.empty((tokens, num_q * head_dim), dtype=q.dtype, device=q.device)
+    if max_chunks > 0:
+        need = attention_rows_scratch_floats(tokens, num_q, head_dim, max_chunks)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention_rows: split mode needs {need} float32 of scratch")
+    fn = _fn("attention_rows", "tvb_attention_rows",
+             [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(q.data_ptr(), q_token_stride, key_cache.data_ptr(), value_cache.data_ptr(),
+              block_tables.data_ptr(), block_tables.shape[1], token_row.data_ptr(),
+              positions.data_ptr(), out.data_ptr(), _ptr(scratch), max_chunks, tokens, num_q, num_kv,
+              head_dim, key_cache.shape[1], window or 0, scale, dtype_tag(q.dtype), _stream()),
+           "attention_rows")
+    return out
+
+
+# ----------------------------------------------------------------------- GEMM
+def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """a [m, k] . w [n, k]^T on the float32 cores, ascending k."""
+    _need_cuda(a, w)
+    if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or a.dtype != w.dtype:
+        raise KernelError("gemm_nt_simt wants a [m, k] and w [n, k] of one dtype")
+    if a.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("gemm_nt_simt wants rows that are contiguous")
+    m, k = a.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or a.dtype, device=a.device)
+    fn = _fn("gemm_simt", "tvb_gemm_nt_simt",
+             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
+              c_int, c_int, c_void_p])
+    _check(fn(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+              m, n, k, dtype_tag(a.dtype), dtype_tag(out.dtype), _stream()), "gemm_nt_simt")
+    return out
+
+
+# ------------------------------------------------------------------- sampling
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+                top_p: torch.Tensor, seeds: torch.Tensor, draws: torch.Tensor,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of logits [rows, vocab].  temperature, top_p float32 [rows];
+    top_k int32 [rows]; seeds, draws int32 [rows, 2] (low and high word of a 64-bit value)."""
+    _need_cuda(logits, temperature, top_k, top_p, seeds, draws)
+    rows, vocab = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("sample_rows wants rows that are contiguous")
+    checks = ((temperature, torch.float32, (rows,)), (top_p, torch.float32, (rows,)),
+              (top_k, torch.int32, (rows,)), (seeds, torch.int32, (rows, 2)), (draws, torch.int32, (rows, 2)))
+    for tensor, dtype, shape in checks:
+        if tensor.dtype != dtype or tuple(tensor.shape) != shape or not tensor.is_contiguous():
+            raise KernelError("sample_rows: a per-row argument has the wrong dtype or shape")
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    fn = _fn("sampling", "tvb_sample_rows",
+             [c_void_p, c_longlong, c_int, c_int] + [c_void_p] * 6 + [c_int, c_void_p])
+    _check(fn(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
+              top_k.data_ptr(), top_p.data_ptr(), seeds.data_ptr(), draws.data_ptr(), out.data_ptr(),
+              dtype_tag(logits.dtype), _stream()), "sample_rows")
+    return out

@@ -1,0 +1,82 @@
+"""Grouped-query attention over the paged cache, with per-head q/k RMSNorm.
+
+qkv = x . Wqkv^T packed as [q | k | v] (tinyvllm/models/qwen3.py:230-240,
+:273-280); q and k are normalised per head and rotated, k and v go to their
+cache pages (:284-299; tinyvllm/kernels/kv_store.cu:26-90); every query attends
+the keys of its request up to its own position, at most ``window`` of them
+(tinyvllm/runtime/attention.py:34-55; tinyvllm/kernels/paged_decode.cu:85-466);
+then the output projection (:303).  All sizes, the scale, the eps and the window
+are parameters; the position encoding is a part of its own.
+"""
+
+from __future__ import annotations
+
+from ..ops import kernels, linear
+from .base import BuildContext, KVNeed, ParamSpec, Part
+from .registry import register_part
+
+
+class GQAAttention(Part):
+    def __init__(self, ctx: BuildContext, *, hidden_size: int, num_heads: int, num_kv_heads: int,
+                 head_dim: int, scale: float, qk_norm_eps: float | None, window: int | None,
+                 position=None, names: dict | None = None) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError("query heads must be a multiple of key-value heads")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"the attention kernels take head sizes in steps of 16 up to 256, not {head_dim}")
+        self.hidden_size = hidden_size
+        self.num_heads = num_heads
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.scale = float(scale)
+        self.qk_norm_eps = qk_norm_eps
+        self.window = window
+        self.prefix = ctx.prefix
+        n = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", **(names or {})}
+        self.names = {key: f"{ctx.prefix}.{value}" for key, value in n.items()}
+        self.position = ctx.build("position", position, ctx) if position is not None else None
+        self.qkv_weight = self.o_weight = self.q_norm_weight = self.k_norm_weight = None
+
+    # ------------------------------------------------------------ declaration
+    def param_specs(self):
+        q_rows, kv_rows = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        specs = [
+            ParamSpec.packed("qkv_weight", [(self.names["q"], q_rows), (self.names["k"], kv_rows),
+                                            (self.names["v"], kv_rows)], self.hidden_size),
+            ParamSpec.single("o_weight", self.names["o"], (self.hidden_size, q_rows)),
+        ]
+        if self.qk_norm_eps is not None:
+            specs += [
+                ParamSpec.single("q_norm_weight", self.names["q_norm"], (self.head_dim,),
+                                 role="vector", init="around_one"),
+                ParamSpec.single("k_norm_weight", self.names["k_norm"], (self.head_dim,),
+                                 role="vector", init="around_one"),
+            ]
+        return specs
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def cache_need(self):
+        return KVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    # ---------------------------------------------------------------- running
+    def forward(self, x, ctx, run: int):
+        qkv = linear(x, self.qkv_weight)
+        keys, values = ctx.storage.kv_of(run)
+        group = ctx.storage.group_of(run)
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.cos, self.position.sin
+        kernels.qk_norm_rope_store(
+            qkv, num_q=self.num_heads, num_kv=self.num_kv_heads, head_dim=self.head_dim,
+            positions=ctx.positions, q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
+            eps=self.qk_norm_eps or 0.0, cos=cos, sin=sin,
+            slots=ctx.slots[group] if ctx.writes_cache(run) else None,
+            key_cache=keys, value_cache=values)
+        attended = ctx.attend(self, qkv, keys, values, group)
+        return linear(attended, self.o_weight)
+
+
+register_part("mixer", "gqa_attention", GQAAttention)

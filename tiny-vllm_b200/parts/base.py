@@ -1,0 +1,117 @@
+"""Interfaces of the parts a model is put together from.
+
+A part is built from the parameters of its :class:`PartSpec` plus the build
+context (device, storage dtype, checkpoint prefix).  It declares its tensors
+as :class:`ParamSpec` (checkpoint names, shapes, packing), what cache it needs,
+and runs on the tensors of one step.  No part knows the model it is in.
+
+Kinds of parts and what each must offer
+---------------------------------------
+norm            ``forward(x) -> y`` and ``add(x, residual) -> (y, new_residual)``,
+                optionally ``add_rows(x, residual, rows) -> y`` on chosen rows
+position        ``prepare(ctx)``; handed to the mixer that asked for it
+mixer           ``cache_need() -> KVNeed | StateNeed | None`` and
+                ``forward(x, ctx, run) -> y`` where ``ctx`` is the step's
+                :class:`StepContext` and ``run`` the index in the run list
+feed_forward    ``forward(x, ctx) -> y``
+block           ``forward(hidden, residual, ctx, run) -> (hidden, residual)``
+embedding       ``forward(token_ids) -> hidden``
+head            ``forward(hidden_rows) -> logits`` (float32)
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+
+@dataclass(frozen=True)
+class ParamSource:
+    """One checkpoint tensor and the rows of the destination it fills."""
+
+    name: str
+    row_start: int
+    rows: int
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """One device tensor of a part.
+
+    ``sources`` lists the checkpoint tensors that are packed along the first
+    dimension.  ``role``: "matrix" and "table" tensors take the storage dtype;
+    a "vector" that the file stores in 32-bit stays in 32-bit; "integer"
+    tensors become int32.  ``init`` is the law of the random-weights mode:
+    "normal" draws N(0, 0.02), "around_one" draws 1 + U(-0.1, 0.1).
+    """
+
+    attr: str
+    shape: tuple[int, ...]
+    sources: tuple[ParamSource, ...]
+    role: str = "matrix"
+    init: str = "normal"
+
+    @staticmethod
+    def single(attr: str, name: str, shape: tuple[int, ...], *, role: str = "matrix",
+               init: str = "normal") -> "ParamSpec":
+        return ParamSpec(attr, shape, (ParamSource(name, 0, shape[0]),), role, init)
+
+    @staticmethod
+    def packed(attr: str, names_rows: list[tuple[str, int]], cols: int) -> "ParamSpec":
+        sources, start = [], 0
+        for name, rows in names_rows:
+            sources.append(ParamSource(name, start, rows))
+            start += rows
+        return ParamSpec(attr, (start, cols), tuple(sources))
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """A growing cache of keys and values, ``window`` keys long if given."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Per-request state of fixed size, zero when a request starts."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class BuildContext:
+    """What every part constructor receives besides its own parameters."""
+
+    device: torch.device
+    dtype: torch.dtype          # storage dtype: torch.bfloat16 or torch.float32
+    prefix: str = ""            # checkpoint prefix of the layer, "" for top-level parts
+    build: Callable[..., Any] | None = None   # build(kind_group, PartSpec, ctx) for nested parts
+
+    def child(self, name: str) -> "BuildContext":
+        prefix = f"{self.prefix}.{name}" if self.prefix else name
+        return BuildContext(self.device, self.dtype, prefix, self.build)
+
+
+class Part:
+    """Base of all parts: tensors by declaration, nested parts by listing."""
+
+    def param_specs(self) -> list[ParamSpec]:
+        return []
+
+    def children(self) -> list["Part"]:
+        return []
+
+    def bind(self, attr: str, tensor: torch.Tensor) -> None:
+        setattr(self, attr, tensor)
+
+    def all_parts(self) -> list["Part"]:
+        found = [self]
+        for child in self.children():
+            found.extend(child.all_parts())
+        return found

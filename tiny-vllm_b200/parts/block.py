@@ -1,0 +1,37 @@
+"""Arrangement of a layer's parts: pre-norm with a deferred residual sum.
+
+The first layer keeps its input as the residual stream and norms it; every
+later norm first adds the previous part's output to the stream.  The
+feed-forward output is NOT added here: the next block's first norm (or the
+model's final norm) adds it (tinyvllm/models/qwen3.py:386-412).
+"""
+
+from __future__ import annotations
+
+from .base import BuildContext, Part
+from .registry import register_part
+
+
+class PreNormResidualBlock(Part):
+    def __init__(self, ctx: BuildContext, *, mixer, feed_forward, norm, mixer_norm_name: str,
+                 feed_forward_norm_name: str, mixer_name: str, feed_forward_name: str) -> None:
+        self.mixer_norm = ctx.build("norm", norm, ctx.child(mixer_norm_name))
+        self.mixer = ctx.build("mixer", mixer, ctx.child(mixer_name))
+        self.feed_forward_norm = ctx.build("norm", norm, ctx.child(feed_forward_norm_name))
+        self.feed_forward = ctx.build("feed_forward", feed_forward, ctx.child(feed_forward_name))
+
+    def children(self):
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def forward(self, hidden, residual, ctx, run: int):
+        if residual is None:
+            residual = hidden
+            x = self.mixer_norm.forward(hidden)
+        else:
+            x, residual = self.mixer_norm.add(hidden, residual)
+        mixed = self.mixer.forward(x, ctx, run)
+        x, residual = self.feed_forward_norm.add(mixed, residual)
+        return self.feed_forward.forward(x, ctx), residual
+
+
+register_part("block", "prenorm_residual", PreNormResidualBlock)
