@@ -1,0 +1,153 @@
+"""The engine against the plain implementation, for every way of cutting the work.
+
+Each test replays the same requests through the step function (the one that
+generation uses) in float32 and in bfloat16 and compares every logit row with
+the whole-sequence oracle of tests/plain_qwen3.py."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import replay_helpers as rh
+from tiny_configs import PAGE_SIZES, TINY_CONFIGS, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+DTYPES = [torch.float32, torch.bfloat16]
+LENGTHS = {
+    "a": (1, 7, 19, 70, 300, 600),
+    "b": (3, 16, 31, 50, 290, 700),
+    "c": (5, 45, 130, 530),
+}
+
+
+def requests_of(name: str) -> dict:
+    vocab = TINY_CONFIGS[name].vocab_size
+    return {f"{name}{n}": random_tokens(vocab, n, 1000 + n) for n in LENGTHS[name]}
+
+
+def make_runner(folder, dtype, page_size, pages, max_requests=8):
+    from tinyvllm_b200.config.registry import read_model_config
+    from tinyvllm_b200.engine.model import Model
+    from tinyvllm_b200.engine.step import StepRunner
+
+    model = Model(read_model_config(folder).to_spec(), device="cuda:0", dtype=dtype).load(folder)
+    return StepRunner(model, page_size=page_size, num_pages=pages, max_requests=max_requests)
+
+
+def peak_pages(steps, page_size):
+    held, peak = {}, 0
+    for step in steps:
+        for entry in step["entries"]:
+            held[entry["id"]] = held.get(entry["id"], 0) + len(entry["tokens"])
+        peak = max(peak, sum(-(-n // page_size) for n in held.values()))
+        for rid in step["end"]:
+            held.pop(rid, None)
+    return peak
+
+
+@pytest.fixture(scope="module")
+def runners(model_folders):
+    """One roomy runner per (configuration, dtype); every trace ends all its requests."""
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            pages = -(-3000 // PAGE_SIZES[name])
+            cache[(name, dtype)] = make_runner(model_folders[name], dtype, PAGE_SIZES[name], pages)
+        return cache[(name, dtype)]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", sorted(TINY_CONFIGS))
+def test_whole_requests(name, dtype, runners, model_folders):
+    requests = requests_of(name)
+    with torch.inference_mode():
+        got = rh.run_steps(runners(name, dtype), rh.whole(requests))
+    assert len(got) == sum(len(t) for t in requests.values())
+    rh.compare(got, rh.oracle(model_folders[name], requests, dtype), dtype, what=f"whole {name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", sorted(TINY_CONFIGS))
+def test_last_32_tokens_one_by_one(name, dtype, runners, model_folders):
+    requests = requests_of(name)
+    with torch.inference_mode():
+        got = rh.run_steps(runners(name, dtype), rh.tail_by_one(requests))
+    rh.compare(got, rh.oracle(model_folders[name], requests, dtype), dtype, what=f"tail {name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", sorted(TINY_CONFIGS))
+def test_portions_of_changing_size(name, dtype, runners, model_folders):
+    requests = requests_of(name)
+    with torch.inference_mode():
+        got = rh.run_steps(runners(name, dtype), rh.portions(requests, seed=7))
+    assert len(got) == sum(len(t) for t in requests.values())
+    rh.compare(got, rh.oracle(model_folders[name], requests, dtype), dtype, what=f"portions {name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", sorted(TINY_CONFIGS))
+def test_mixed_batches_with_scarce_pages(name, dtype, model_folders):
+    """Up to four live requests, portions beside single tokens, and a pool exactly as
+    large as the peak demand, so that pages of finished requests are taken again."""
+    requests = requests_of(name)
+    steps = rh.mixed(requests, seed=11)
+    assert max(len(s["entries"]) for s in steps) == 4
+    assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"])
+    page = PAGE_SIZES[name]
+    pages = peak_pages(steps, page)
+    assert pages * page < sum(len(t) for t in requests.values())     # the pool is used more than once
+    runner = make_runner(model_folders[name], dtype, page, pages, max_requests=4)
+    with torch.inference_mode():
+        got = rh.run_steps(runner, steps)
+    assert len(got) == sum(len(t) for t in requests.values())
+    for pool in runner.manager.pools:
+        assert pool.free_count == pool.num_pages
+    rh.compare(got, rh.oracle(model_folders[name], requests, dtype), dtype, what=f"mixed {name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_cutting_does_not_change_float_bits_beyond_rounding(dtype, runners, model_folders):
+    """Whole against portions against mixed, engine against engine: the rows agree to rounding."""
+    name = "b"
+    requests = requests_of(name)
+    runner = runners(name, dtype)
+    with torch.inference_mode():
+        base = rh.run_steps(runner, rh.whole(requests))
+        cut = rh.run_steps(runner, rh.portions(requests, seed=3))
+        mix = rh.run_steps(runner, rh.mixed(requests, seed=5))
+    limit = 1e-5 if dtype == torch.float32 else 3e-2
+    for key, row in base.items():
+        scale = row.abs().max().item()
+        assert (cut[key] - row).abs().max().item() <= limit * scale, key
+        assert (mix[key] - row).abs().max().item() <= limit * scale, key
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_trace_run_program(dtype_name, model_folders, tmp_path):
+    """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and 'done' lines out."""
+    name = "b"
+    dtype = getattr(torch, dtype_name)
+    requests = {k: v for k, v in list(requests_of(name).items())[:5]}
+    steps = rh.mixed(requests, seed=13)
+    out_dir = tmp_path / "out"
+    text = "".join(json.dumps(step) + "\n" for step in steps)
+    result = subprocess.run(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_folders[name]),
+         "--dtype", dtype_name, "--out", str(out_dir), "--max-tokens", str(rh.live_token_need(steps))],
+        input=text, capture_output=True, text=True, timeout=900,
+        env={**os.environ, "PYTHONPATH": ""})
+    assert result.returncode == 0, result.stderr[-2000:]
+    assert result.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    got = rh.read_trace_output(steps, out_dir, TINY_CONFIGS[name].vocab_size)
+    rh.compare(got, rh.oracle(model_folders[name], requests, dtype), dtype, what="trace_run")

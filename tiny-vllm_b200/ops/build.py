@@ -76,9 +76,8 @@ def _usable_dir() -> Path:
     for folder in _build_dirs():
         try:
             folder.mkdir(parents=True, exist_ok=True)
-            probe = folder / f".probe_{os.getpid()}"
-            probe.write_bytes(b"")
-            probe.unlink()
+            with tempfile.NamedTemporaryFile(dir=folder, prefix=".probe_"):
+                pass
             return folder
         except OSError:
             continue
@@ -106,7 +105,7 @@ def compile_library(name: str, *, verbose: bool = True) -> Path:
     nvcc = _find_nvcc()
     folder = _usable_dir()
     target = folder / f"tvb200_{name}_{_digest(name)}.so"
-    partial = folder / f".{target.name}.{os.getpid()}.tmp"
+    partial = folder / f".{target.name}.{os.getpid()}.{threading.get_ident()}.tmp"
     command = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(partial), str(source),
                *EXTRA_LINK.get(name, ())]
     if verbose:
