@@ -13,6 +13,10 @@ from .config.registry import (ConfigError, architecture_names, read_model_config
                               register_architecture)
 from .config.spec import LayerSpec, ModelSpec, PartSpec, RunStep
 from . import models as _models  # noqa: F401  (registers the architectures)
+from .engine.engine import Engine, GenerateRequest, RequestOutput
+from .engine.llm import LLM, TextOutput
+from .sampling.params import SamplingParams
 
-__all__ = ["ConfigError", "EngineConfig", "LayerSpec", "ModelSpec", "PartSpec", "RunStep",
+__all__ = ["Engine", "GenerateRequest", "LLM", "RequestOutput", "SamplingParams", "TextOutput",
+           "ConfigError", "EngineConfig", "LayerSpec", "ModelSpec", "PartSpec", "RunStep",
            "architecture_names", "read_model_config", "register_architecture"]

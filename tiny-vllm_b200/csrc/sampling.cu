@@ -76,9 +76,7 @@ __device__ __forceinline__ void block_argmax(float& value, int& index, float* va
 template <typename T>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
-                   const float* __restrict__ temperature, const int* __restrict__ top_k,
-                   const float* __restrict__ top_p, const uint32_t* __restrict__ seeds,
-                   const uint32_t* __restrict__ draws, int* __restrict__ tokens) {
+                   const int* __restrict__ packed, int capacity, int* __restrict__ tokens) {
     __shared__ float fscratch[32];
     __shared__ int iscratch[32];
     const int row = blockIdx.x, tid = threadIdx.x;
@@ -91,7 +89,7 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
         if (v > best) { best = v; best_index = i; }
     }
     block_argmax(best, best_index, fscratch, iscratch);
-    const float temp = temperature[row];
+    const float temp = __int_as_float(packed[row]);
     if (!(temp > 0.0f) || best_index == 0x7fffffff) {
         if (tid == 0) tokens[row] = best_index == 0x7fffffff ? 0 : best_index;
         return;
@@ -100,7 +98,7 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
 #define SCORE(i) __fdiv_rn(__fsub_rn(to_float<T>(x[i]), row_max), temp)
 
     // ---- top-k: the k-th largest key, then how many of its equals stay
-    const int k = top_k[row];
+    const int k = packed[2 * capacity + row];
     const bool use_k = k > 0 && k < vocab;
     uint32_t k_key = 0;
     int k_index_limit = vocab;
@@ -134,7 +132,7 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
 #define KEPT_K(key, i) (!use_k || (key) > k_key || ((key) == k_key && (i) < k_index_limit))
 
     // ---- top-p: the smallest key kappa with mass(keys above kappa) <= top_p
-    const float p_limit = top_p[row];
+    const float p_limit = __int_as_float(packed[capacity + row]);
     uint32_t p_key = 0;
     if (p_limit < 1.0f) {
         float part = 0.0f;
@@ -159,8 +157,8 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
     }
 
     // ---- the race
-    const uint32_t seed_lo = seeds[2 * row], seed_hi = seeds[2 * row + 1];
-    const uint32_t draw_lo = draws[2 * row], draw_hi = draws[2 * row + 1];
+    const uint32_t seed_lo = (uint32_t)packed[3 * capacity + row], seed_hi = (uint32_t)packed[4 * capacity + row];
+    const uint32_t draw_lo = (uint32_t)packed[5 * capacity + row], draw_hi = (uint32_t)packed[6 * capacity + row];
     float win = -INFINITY;
     int win_index = 0x7fffffff;
     for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
@@ -179,19 +177,19 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
 #undef KEPT_K
 }
 
+// packed: int32 [7, capacity], field-major: temperature and top_p as float bits, top_k,
+// seed low/high word, draw-counter low/high word; row r reads column r.
 extern "C" int tvb_sample_rows(const void* logits, long long row_stride, int rows, int vocab,
-                               const float* temperature, const int* top_k, const float* top_p,
-                               const uint32_t* seeds, const uint32_t* draws, int* tokens, int dtype,
-                               void* stream) {
+                               const int* packed, int capacity, int* tokens, int dtype, void* stream) {
     if (rows <= 0) return 0;
-    if (vocab <= 0) return TVB_BAD_ARGUMENT;
+    if (vocab <= 0 || capacity < rows) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == TVB_F32)
         sample_rows_kernel<float><<<rows, SAMPLE_THREADS, 0, s>>>(
-            (const float*)logits, row_stride, vocab, temperature, top_k, top_p, seeds, draws, tokens);
+            (const float*)logits, row_stride, vocab, packed, capacity, tokens);
     else if (dtype == TVB_BF16)
         sample_rows_kernel<bf16><<<rows, SAMPLE_THREADS, 0, s>>>(
-            (const bf16*)logits, row_stride, vocab, temperature, top_k, top_p, seeds, draws, tokens);
+            (const bf16*)logits, row_stride, vocab, packed, capacity, tokens);
     else
         return TVB_BAD_ARGUMENT;
     return tvb_last_error();

@@ -1,0 +1,163 @@
+"""Decode steps as CUDA graphs.
+
+A step in which every entry is one decoded token runs the same kernels with the
+same shapes every time, so for a list of batch sizes the whole step (embedding to
+sampled tokens) is captured once and replayed; a step takes the smallest captured
+size that holds it, the spare rows being padding (row -1, slot -1: they write
+nothing and attend nothing).  The step's metadata and sampling arguments go up
+in one copy from pinned memory into the buffers the graph reads.
+
+The reference captures sizes {1, 2, 4, 8, 12, 16} the same way
+(tinyvllm/runtime/graphs.py:36-140, padding tinyvllm/runtime/inputs.py:94-98),
+sampling outside the graph.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..ops import kernels
+from ..sampling.sampler import ROW_WORDS, pack_rows, sample_packed
+from .step import StepContext
+
+
+class _Bucket:
+    """Buffers and graph of one batch size."""
+
+    def __init__(self, runner, size: int, blocks: list[int]) -> None:
+        groups = len(runner.manager.groups)
+        self.size = size
+        self.blocks = blocks
+        sizes = [size, size, size, size, size, size + 1]
+        for g in range(groups):
+            sizes += [size, size * blocks[g]]
+        sizes.append(ROW_WORDS * size)
+        self.sizes = sizes
+        self.offsets = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])]).astype(np.int64)
+        total = int(self.offsets[-1])
+        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.device = torch.zeros(total, dtype=torch.int32, device=runner.device)
+        self.tokens = torch.zeros(size, dtype=torch.int32, device=runner.device)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits = None
+        self.launches = 0
+        self.copied: torch.cuda.Event | None = None      # the last upload has left the pinned buffer
+
+    def host_view(self, i: int) -> np.ndarray:
+        return self.host_np[self.offsets[i]:self.offsets[i] + self.sizes[i]]
+
+    def device_view(self, i: int) -> torch.Tensor:
+        return self.device[int(self.offsets[i]):int(self.offsets[i]) + self.sizes[i]]
+
+
+class DecodeGraphs:
+    def __init__(self, runner, batch_sizes, *, max_model_len: int) -> None:
+        self.runner = runner
+        self.max_model_len = max_model_len
+        page = runner.page_size
+        self.blocks = [-(-max_model_len // page) for _ in runner.manager.groups]
+        chunk = kernels.attention_chunk_keys()
+        self.split_chunks = -(-max_model_len // chunk) if max_model_len > chunk else 0
+        self.buckets = [_Bucket(runner, size, self.blocks) for size in sorted(set(batch_sizes))]
+        self._pool = None
+
+    @property
+    def largest(self) -> int:
+        return self.buckets[-1].size if self.buckets else 0
+
+    def _context(self, bucket: _Bucket) -> StepContext:
+        groups = len(self.runner.manager.groups)
+        size = bucket.size
+        return StepContext(
+            storage=self.runner.storage, num_tokens=size, num_rows=size, num_wanted=size,
+            token_ids=bucket.device_view(0), positions=bucket.device_view(1),
+            token_row=bucket.device_view(2), want_rows=bucket.device_view(3),
+            state_slots=bucket.device_view(4), row_starts=bucket.device_view(5),
+            slots=[bucket.device_view(6 + 2 * g) for g in range(groups)],
+            block_tables=[bucket.device_view(7 + 2 * g).view(size, bucket.blocks[g])
+                          for g in range(groups)],
+            cache_sources=self.runner.cache_sources, max_position=self.max_model_len - 1,
+            split_chunks=self.split_chunks, workspace_of=self.runner._workspace_of)
+
+    def _fill_padding(self, bucket: _Bucket) -> None:
+        bucket.host_np[:] = 0
+        bucket.host_view(1)[:] = -1                     # positions
+        bucket.host_view(2)[:] = -1                     # rows
+        bucket.host_view(3)[:] = np.arange(bucket.size)  # every row's logits are produced
+        bucket.host_view(5)[:] = np.arange(bucket.size + 1)
+        for g in range(len(self.runner.manager.groups)):
+            bucket.host_view(6 + 2 * g)[:] = -1         # slots: write nothing
+        packed = bucket.host_view(len(bucket.sizes) - 1).reshape(ROW_WORDS, bucket.size)
+        packed[1] = np.ones(bucket.size, dtype=np.float32).view(np.int32)   # top_p = 1
+
+    def capture(self) -> None:
+        """Capture every batch size (largest first, so the graphs share one memory pool)."""
+        if self.split_chunks:
+            model = self.runner.model
+            heads = max((getattr(b.mixer, "num_heads", 0) * (getattr(b.mixer, "head_dim", 0) + 2))
+                        for b in model.blocks)
+            self.runner.reserve_workspace(self.largest * heads * self.split_chunks)
+        stream = torch.cuda.Stream(device=self.runner.device)
+        for bucket in reversed(self.buckets):
+            self._fill_padding(bucket)
+            bucket.device.copy_(bucket.host)
+            ctx = self._context(bucket)
+            packed = bucket.device_view(len(bucket.sizes) - 1).view(ROW_WORDS, bucket.size)
+            torch.cuda.synchronize()
+            with torch.cuda.stream(stream):
+                for _ in range(2):                                   # load kernels, settle allocations
+                    sample_packed(self.runner.model.forward(ctx), packed, out=bucket.tokens)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            launched = kernels.launch_count()
+            with torch.cuda.graph(graph, pool=self._pool, stream=stream):
+                bucket.logits = self.runner.model.forward(ctx)
+                sample_packed(bucket.logits, packed, out=bucket.tokens)
+            bucket.launches = kernels.launch_count() - launched
+            if self._pool is None:
+                self._pool = graph.pool()
+            bucket.graph = graph
+        torch.cuda.synchronize()
+
+    def launches_per_step(self, rows: int) -> int:
+        """Kernels of this package inside the graph that a step of ``rows`` rows replays
+        (library matrix products are not counted)."""
+        bucket = self.bucket_for(rows)
+        return bucket.launches if bucket is not None else 0
+
+    def bucket_for(self, rows: int) -> _Bucket | None:
+        for bucket in self.buckets:
+            if bucket.size >= rows and bucket.graph is not None:
+                return bucket
+        return None
+
+    def run(self, plan, entries, params, draws) -> tuple[torch.Tensor, torch.Tensor] | None:
+        """Replay the graph for a step of single tokens; (tokens, logits) views of the first
+        ``len(entries)`` rows, valid until the next replay.  None if no graph holds the step."""
+        rows = len(entries)
+        bucket = self.bucket_for(rows)
+        if bucket is None:
+            return None
+        if bucket.copied is not None:
+            bucket.copied.synchronize()
+        self._fill_padding(bucket)
+        self.runner.storage.clear_state([p.state_slot for p in plan.entries if p.fresh_state])
+        groups = len(self.runner.manager.groups)
+        for r, (entry, planned) in enumerate(zip(entries, plan.entries)):
+            bucket.host_view(0)[r] = entry.tokens[0]
+            bucket.host_view(1)[r] = planned.start
+            bucket.host_view(2)[r] = r
+            bucket.host_view(4)[r] = planned.state_slot
+            for g in range(groups):
+                bucket.host_view(6 + 2 * g)[r] = planned.slots[g][0]
+                table = planned.tables[g]
+                bucket.host_view(7 + 2 * g)[r * bucket.blocks[g]:r * bucket.blocks[g] + len(table)] = table
+        packed = bucket.host_view(len(bucket.sizes) - 1).reshape(ROW_WORDS, bucket.size)
+        packed[:] = pack_rows(params, draws, capacity=bucket.size)
+        bucket.device.copy_(bucket.host, non_blocking=True)
+        bucket.copied = torch.cuda.Event()
+        bucket.copied.record()
+        bucket.graph.replay()
+        return bucket.tokens[:rows], bucket.logits[:rows]

@@ -34,8 +34,18 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far by this process (graph replays not counted)."""
+    return _launches
+
+
+def _check(code: int, what: str, launches: int = 1) -> None:
+    global _launches
     if code == 0:
+        _launches += launches
         return
     if code < 0:
         raise KernelError(f"{what}: the kernel does not take these sizes")
@@ -250,7 +260,7 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
               block_tables.data_ptr(), block_tables.shape[1], token_row.data_ptr(),
               positions.data_ptr(), out.data_ptr(), _ptr(scratch), max_chunks, tokens, num_q, num_kv,
               head_dim, key_cache.shape[1], window or 0, scale, dtype_tag(q.dtype), _stream()),
-           "attention_rows")
+           "attention_rows", 2 if max_chunks > 0 else 1)
     return out
 
 
@@ -276,25 +286,21 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
 
 
 # ------------------------------------------------------------------- sampling
-def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
-                top_p: torch.Tensor, seeds: torch.Tensor, draws: torch.Tensor,
-                out: torch.Tensor | None = None) -> torch.Tensor:
-    """One token per row of logits [rows, vocab].  temperature, top_p float32 [rows];
-    top_k int32 [rows]; seeds, draws int32 [rows, 2] (low and high word of a 64-bit value)."""
-    _need_cuda(logits, temperature, top_k, top_p, seeds, draws)
+def sample_rows(logits: torch.Tensor, packed: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of logits [rows, vocab].  ``packed`` is int32 [7, capacity >= rows],
+    field-major: temperature and top_p as float32 bits, top_k, low and high word of the seed,
+    low and high word of the draw counter; row r reads column r."""
+    _need_cuda(logits, packed)
     rows, vocab = logits.shape
     if logits.stride(1) != 1:
         raise KernelError("sample_rows wants rows that are contiguous")
-    checks = ((temperature, torch.float32, (rows,)), (top_p, torch.float32, (rows,)),
-              (top_k, torch.int32, (rows,)), (seeds, torch.int32, (rows, 2)), (draws, torch.int32, (rows, 2)))
-    for tensor, dtype, shape in checks:
-        if tensor.dtype != dtype or tuple(tensor.shape) != shape or not tensor.is_contiguous():
-            raise KernelError("sample_rows: a per-row argument has the wrong dtype or shape")
+    if packed.dtype != torch.int32 or packed.dim() != 2 or packed.shape[0] != 7 or \
+            packed.shape[1] < rows or not packed.is_contiguous():
+        raise KernelError("sample_rows: packed must be contiguous int32 [7, capacity >= rows]")
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     fn = _fn("sampling", "tvb_sample_rows",
-             [c_void_p, c_longlong, c_int, c_int] + [c_void_p] * 6 + [c_int, c_void_p])
-    _check(fn(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
-              top_k.data_ptr(), top_p.data_ptr(), seeds.data_ptr(), draws.data_ptr(), out.data_ptr(),
-              dtype_tag(logits.dtype), _stream()), "sample_rows")
+             [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(logits.data_ptr(), logits.stride(0), rows, vocab, packed.data_ptr(), packed.shape[1],
+              out.data_ptr(), dtype_tag(logits.dtype), _stream()), "sample_rows")
     return out
