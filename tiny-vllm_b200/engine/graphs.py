@@ -133,6 +133,7 @@ class DecodeGraphs:
                 return bucket
         return None
 
+    @torch.inference_mode()
     def run(self, plan, entries, params, draws) -> tuple[torch.Tensor, torch.Tensor] | None:
         """Replay the graph for a step of single tokens; (tokens, logits) views of the first
         ``len(entries)`` rows, valid until the next replay.  None if no graph holds the step."""

@@ -230,6 +230,7 @@ class StepRunner:
     def execute(self, ctx: StepContext) -> torch.Tensor | None:
         return self.model.forward(ctx)
 
+    @torch.inference_mode()
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
         """Plan, run and commit one step; raises :class:`OutOfPages` if it does not fit."""
         entries = list(entries)
