@@ -1,0 +1,310 @@
+"""Each kernel alone against its plain reference, at sizes other than the engine's."""
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def k():
+    from tinyvllm_b200.ops import kernels
+    return kernels
+
+
+def close(got, want, dtype, *, f32=2e-6, bf16=1e-2):
+    """|got - want| within a fraction of the largest |want| (float32: rounding of a few sums)."""
+    scale = want.abs().max().item() or 1.0
+    limit = f32 if dtype == torch.float32 else bf16
+    err = (got.float().cpu() - want).abs().max().item() / scale
+    assert err <= limit, f"error {err:.3e} of scale, allowed {limit:.1e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_embed_rows(dtype):
+    torch.manual_seed(0)
+    table = torch.randn(1003, 200).to(dtype)
+    ids = torch.tensor([0, 1002, 5, 5, 77], dtype=torch.int32)
+    out = k().embed_rows(table.to(DEV), ids.to(DEV))
+    assert torch.equal(out.cpu(), table[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("width", [48, 1000, 5120, 12000])
+def test_rms_norm_and_residual(dtype, width):
+    torch.manual_seed(width)
+    x = (torch.randn(37, width) * 3).to(dtype)
+    res = torch.randn(37, width).to(dtype)
+    w = (1 + 0.1 * torch.randn(width)).to(dtype)
+    got = k().rms_norm(x.to(DEV), w.to(DEV), 1e-5)
+    close(got, plain.rms_norm(x.float(), w.float(), 1e-5, dtype), dtype, bf16=8e-3)
+    got, new_res = k().rms_norm(x.to(DEV), w.to(DEV), 1e-5, residual=res.to(DEV))
+    want, want_res = plain.add_rms_norm(x.float(), res.float(), w.float(), 1e-5, dtype)
+    assert torch.equal(new_res.float().cpu(), want_res)            # the rounded sum is exact
+    close(got, want, dtype, bf16=8e-3)
+    rows = torch.tensor([36, 0, 5], dtype=torch.int32)
+    picked = k().rms_norm(x.to(DEV), w.to(DEV), 1e-5, residual=res.to(DEV), rows=rows.to(DEV))
+    assert torch.equal(picked.cpu(), got.cpu()[rows.long()])
+    if dtype == torch.bfloat16:                                    # a 32-bit weight stays 32-bit
+        got32 = k().rms_norm(x.to(DEV), w.float().to(DEV), 1e-5)
+        close(got32, plain.rms_norm(x.float(), w.float(), 1e-5, dtype), dtype, bf16=8e-3)
+
+
+def test_rms_norm_refuses_a_row_larger_than_shared_memory():
+    from tinyvllm_b200.ops.kernels import KernelError
+    x = torch.zeros(1, 60000, device=DEV)
+    with pytest.raises(KernelError, match="larger"):
+        k().rms_norm(x, torch.ones(60000, device=DEV), 1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_silu_mul(dtype):
+    torch.manual_seed(1)
+    gate_up = (torch.randn(19, 2 * 333) * 4).to(dtype)
+    got = k().silu_mul(gate_up.to(DEV))
+    close(got, plain.swiglu(gate_up.float(), dtype), dtype, f32=1e-6, bf16=8e-3)
+
+
+def test_rope_tables_match_the_float32_formula():
+    rope_d, theta = 64, 1_000_000.0
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rope_d, 2, dtype=torch.float32) / rope_d))
+    cos, sin = k().rope_tables(inv_freq.to(DEV), 5000)
+    want_cos, want_sin = plain.rope_tables(rope_d, 5000, theta)
+    assert (cos.cpu() - want_cos).abs().max().item() < 5e-7
+    assert (sin.cpu() - want_sin).abs().max().item() < 5e-7
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("heads", [(8, 2, 64), (3, 3, 80), (16, 8, 128), (2, 1, 256)])
+def test_qk_norm_rope_store(dtype, heads):
+    nq, nkv, d = heads
+    torch.manual_seed(d)
+    tokens, page, pages = 23, 8, 9
+    qkv = torch.randn(tokens, (nq + 2 * nkv) * d).to(dtype)
+    qw, kw = (1 + 0.1 * torch.randn(d)).to(dtype), (1 + 0.1 * torch.randn(d)).to(dtype)
+    positions = torch.randint(0, 3000, (tokens,), dtype=torch.int32)
+    slots = torch.randperm(page * pages)[:tokens].to(torch.int32)
+    cos, sin = plain.rope_tables(d, 3000, 10_000.0)
+    kc = torch.zeros(pages, page, nkv, d, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    work = qkv.to(DEV).clone()
+    k().qk_norm_rope_store(work, num_q=nq, num_kv=nkv, head_dim=d, positions=positions.to(DEV),
+                           q_weight=qw.to(DEV), k_weight=kw.to(DEV), eps=1e-6, cos=cos.to(DEV),
+                           sin=sin.to(DEV), slots=slots.to(DEV), key_cache=kc, value_cache=vc)
+    q = qkv[:, :nq * d].float().view(tokens, nq, d)
+    kk = qkv[:, nq * d:(nq + nkv) * d].float().view(tokens, nkv, d)
+    vv = qkv[:, (nq + nkv) * d:].view(tokens, nkv, d)
+    pos = positions.long()
+    want_q, want_k = plain.qk_norm_rope(q, kk, qw.float(), kw.float(), cos[pos], sin[pos], 1e-6, dtype)
+    close(work[:, :nq * d].view(tokens, nq, d), want_q, dtype, bf16=1.6e-2)
+    flat_k = kc.view(-1, nkv, d)[slots.long().to(DEV)]
+    close(flat_k, want_k, dtype, bf16=1.6e-2)
+    assert torch.equal(vc.view(-1, nkv, d)[slots.long().to(DEV)].cpu(), vv)
+    untouched = torch.ones(page * pages, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert kc.view(-1, nkv * d)[untouched.to(DEV)].abs().sum().item() == 0   # no stray writes
+    # without slots nothing is written, q still is
+    kc.zero_()
+    k().qk_norm_rope_store(qkv.to(DEV).clone(), num_q=nq, num_kv=nkv, head_dim=d,
+                           positions=positions.to(DEV), q_weight=qw.to(DEV), k_weight=kw.to(DEV),
+                           eps=1e-6, cos=cos.to(DEV), sin=sin.to(DEV), slots=None, key_cache=kc,
+                           value_cache=vc)
+    assert kc.abs().sum().item() == 0
+
+
+def paged_case(dtype, *, nq, nkv, d, page, lengths, queries, seed, boost=None):
+    """Requests with ``lengths`` keys each scattered over shuffled pages; the last ``queries[i]``
+    positions of request i are query tokens.  ``boost`` = (request, key position, factor) scales one
+    key so that its score stands out."""
+    g = torch.Generator().manual_seed(seed)
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    kc = torch.zeros(total_pages, page, nkv, d)
+    vc = torch.zeros_like(kc)
+    kc.fill_(float("nan")), vc.fill_(float("nan"))              # reading a foreign slot shows
+    blocks = max(-(-n // page) for n in lengths)
+    tables = torch.full((len(lengths), blocks), -1, dtype=torch.int32)
+    keys, values, q_rows, token_row, positions = [], [], [], [], []
+    for r, n in enumerate(lengths):
+        kr, vr = torch.randn(n, nkv, d, generator=g), torch.randn(n, nkv, d, generator=g)
+        if boost and boost[0] == r:
+            kr[boost[1]] *= boost[2]
+        kr, vr = kr.to(dtype).float(), vr.to(dtype).float()
+        keys.append(kr), values.append(vr)
+        for b in range(-(-n // page)):
+            tables[r, b] = order.pop()
+            span = slice(b * page, min(n, (b + 1) * page))
+            kc[tables[r, b], : span.stop - span.start] = kr[span]
+            vc[tables[r, b], : span.stop - span.start] = vr[span]
+        for p in range(n - queries[r], n):
+            q_rows.append(torch.randn(nq, d, generator=g))
+            token_row.append(r), positions.append(p)
+    q = torch.stack(q_rows).to(dtype)
+    return dict(q=q, kc=kc.to(dtype), vc=vc.to(dtype), tables=tables, keys=keys, values=values,
+                token_row=torch.tensor(token_row, dtype=torch.int32),
+                positions=torch.tensor(positions, dtype=torch.int32))
+
+
+def plain_paged(case, scale, window, dtype):
+    out = []
+    for i in range(case["q"].shape[0]):
+        r, p = int(case["token_row"][i]), int(case["positions"][i])
+        out.append(plain.causal_attention(
+            case["q"][i:i + 1].float(), case["keys"][r][:p + 1], case["values"][r][:p + 1], scale,
+            window, dtype, q_positions=torch.tensor([p]))[0])
+    return torch.stack(out)
+
+
+def run_rows(case, *, nq, nkv, d, scale, window, max_chunks):
+    kernels = k()
+    q = case["q"].to(DEV).view(case["q"].shape[0], nq * d)
+    scratch = None
+    if max_chunks:
+        scratch = torch.empty(kernels.attention_rows_scratch_floats(q.shape[0], nq, d, max_chunks),
+                              dtype=torch.float32, device=DEV)
+    return kernels.attention_rows(
+        q, nq * d, case["kc"].to(DEV), case["vc"].to(DEV), case["tables"].to(DEV),
+        case["token_row"].to(DEV), case["positions"].to(DEV), num_q=nq, num_kv=nkv, head_dim=d,
+        window=window, scale=scale, scratch=scratch, max_chunks=max_chunks).view(-1, nq, d)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(8, 2, 64, 16), (6, 6, 48, 5), (16, 8, 128, 16), (4, 1, 256, 32)])
+def test_attention_rows_prompt_portions_and_single_tokens(dtype, shape):
+    nq, nkv, d, page = shape
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[300, 1, 70, 515],
+                      queries=[40, 1, 1, 3], seed=d)
+    scale = d ** -0.5
+    want = plain_paged(case, scale, None, dtype)
+    walked = run_rows(case, nq=nq, nkv=nkv, d=d, scale=scale, window=None, max_chunks=0)
+    close(walked, want, dtype, f32=3e-6, bf16=8e-3)
+    spread = run_rows(case, nq=nq, nkv=nkv, d=d, scale=scale, window=None, max_chunks=3)
+    assert torch.equal(walked, spread)          # both modes do a row's arithmetic in the same order
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_attention_finds_a_far_key_among_hundreds(dtype):
+    """One key, 700 positions back and across two chunk edges, is scaled to dominate."""
+    nq, nkv, d, page = 4, 2, 64, 16
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[900], queries=[1], seed=3)
+    far = 190
+    case["q"][0] = (case["keys"][0][far].repeat_interleave(2, dim=0) * 4).to(dtype)   # q = 4 k_far per head
+    want = plain_paged(case, 1.0, None, dtype)
+    assert (want[0] - case["values"][0][far].repeat_interleave(2, dim=0)).abs().max() < 1e-2
+    for chunks in (0, 4):
+        got = run_rows(case, nq=nq, nkv=nkv, d=d, scale=1.0, window=None, max_chunks=chunks)
+        close(got, want, dtype, f32=3e-6, bf16=8e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("window", [1, 37, 256, 300])
+def test_attention_window_edge(dtype, window):
+    """The key just outside the window is made enormous: it must not be seen; the one just inside must."""
+    nq, nkv, d, page = 2, 1, 32, 8
+    length = 600
+    outside = length - 1 - window
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[length], queries=[5], seed=window,
+                      boost=(0, outside, 50.0) if outside >= 0 else None)
+    want = plain_paged(case, 0.2, window, dtype)
+    for chunks in (0, 3):
+        got = run_rows(case, nq=nq, nkv=nkv, d=d, scale=0.2, window=window, max_chunks=chunks)
+        close(got, want, dtype, f32=3e-6, bf16=8e-3)
+    full = plain_paged(case, 0.2, None, dtype)
+    assert (full[-1] - want[-1]).abs().max() > 1e-3       # the boosted key would have changed the result
+
+
+def test_attention_padding_rows_give_zeros():
+    case = paged_case(torch.float32, nq=2, nkv=1, d=16, page=4, lengths=[9], queries=[2], seed=0)
+    case["token_row"][1] = -1
+    case["positions"][1] = -1
+    for chunks in (0, 2):
+        got = run_rows(case, nq=2, nkv=1, d=16, scale=1.0, window=None, max_chunks=chunks)
+        assert got[1].abs().sum().item() == 0 and torch.isfinite(got[0]).all()
+
+
+def test_attention_refuses_sizes_it_does_not_take():
+    from tinyvllm_b200.ops.kernels import KernelError
+    def call(nq, nkv, d):
+        ints = torch.zeros(1, dtype=torch.int32, device=DEV)
+        cache = torch.zeros(1, 4, nkv, d, device=DEV)
+        return k().attention_rows(torch.zeros(1, nq * d, device=DEV), nq * d, cache, cache,
+                                  ints.view(1, 1), ints, ints, num_q=nq, num_kv=nkv, head_dim=d,
+                                  window=None, scale=1.0)
+
+    with pytest.raises(KernelError, match="head sizes"):
+        call(2, 1, 272)
+    with pytest.raises(KernelError, match="groups"):
+        call(3, 2, 16)
+    assert call(2, 1, 16).shape == (1, 32)
+
+
+@pytest.mark.parametrize("shape", [(1, 7, 5), (70, 129, 33), (300, 200, 1000), (5, 1030, 64)])
+def test_gemm_float32_any_size_and_row_independence(shape):
+    m, n, kk = shape
+    torch.manual_seed(m)
+    a, w = torch.randn(m, kk), torch.randn(n, kk)
+    got = k().gemm_nt_simt(a.to(DEV), w.to(DEV))
+    want = (a.double() @ w.double().T).float()
+    assert (got.cpu() - want).abs().max().item() <= 2e-6 * want.abs().max().item() * math.sqrt(kk)
+    alone = k().gemm_nt_simt(a[:1].to(DEV), w.to(DEV))
+    assert torch.equal(alone[0], got[0])                   # a row's sum does not depend on the batch
+    strided = torch.randn(m, kk + 8)
+    got2 = k().gemm_nt_simt(strided.to(DEV)[:, :kk], w.to(DEV))
+    assert torch.allclose(got2.cpu(), strided[:, :kk] @ w.T, atol=1e-3, rtol=1e-4)
+
+
+def test_gemm_bfloat16_inputs_float32_result():
+    torch.manual_seed(0)
+    a, w = torch.randn(9, 100).bfloat16(), torch.randn(333, 100).bfloat16()
+    got = k().gemm_nt_simt(a.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert got.dtype == torch.float32
+    assert torch.allclose(got.cpu(), a.float() @ w.float().T, atol=1e-4, rtol=1e-5)
+
+
+def pack(rows):
+    import numpy as np
+    from tinyvllm_b200.sampling.params import SamplingParams
+    from tinyvllm_b200.sampling.sampler import pack_rows
+    params = [SamplingParams(temperature=t, top_k=tk, top_p=tp, seed=s) for t, tk, tp, s, _ in rows]
+    return torch.from_numpy(pack_rows(params, [d for *_, d in rows])).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_sampling_matches_the_plain_rules(dtype):
+    torch.manual_seed(5)
+    # bfloat16 logits are made distinct (multiples of 1/32 below 8): with equal values at the
+    # top-p boundary the kernel keeps all of them, the plain rule only the first ones
+    vocab = 1531 if dtype == torch.float32 else 500
+    rows = [(0.0, 0, 1.0, 0, 0), (1.0, 0, 1.0, 1, 0), (0.7, 40, 1.0, 2, 3), (1.3, 0, 0.8, 3, 9),
+            (0.9, 25, 0.5, 2**40 + 7, 2**33 + 1), (1.0, 1, 1.0, 5, 5), (1.0, 0, 1e-4, 6, 1),
+            (2.5, 5000, 0.95, 7, 2)]
+    if dtype == torch.float32:
+        logits = torch.randn(len(rows), vocab) * 2.5
+    else:
+        logits = torch.stack([(torch.randperm(vocab) - 250) / 32.0 for _ in rows]).to(dtype)
+        assert all(len(set(row.tolist())) == vocab for row in logits)
+    got = k().sample_rows(logits.to(DEV), pack(rows)).cpu().tolist()
+    want = [plain.sample(logits[i].float(), *rows[i]) for i in range(len(rows))]
+    assert got == want
+    # a request's token does not depend on its row or its neighbours
+    again = k().sample_rows(logits.flip(0).contiguous().to(DEV), pack(rows[::-1])).cpu().tolist()
+    assert again == want[::-1]
+
+
+def test_sampling_distribution_and_ties():
+    logits = torch.tensor([[0.1, 3.0, 2.9, -1.0, 2.95, 0.0, 3.0]]).repeat(4000, 1)
+    rows = [(0.7, 0, 1.0, seed, 1) for seed in range(4000)]
+    got = k().sample_rows(logits.to(DEV), pack(rows)).cpu()
+    freq = torch.bincount(got.long(), minlength=7).float() / 4000
+    assert (freq - torch.softmax(logits[0] / 0.7, 0)).abs().max().item() < 0.03
+    greedy = k().sample_rows(logits[:1].to(DEV), pack([(0.0, 0, 1.0, 0, 0)])).item()
+    assert greedy == 1                                         # of equal logits the smaller id wins
+    tied = torch.zeros(1, 50)
+    top2 = {k().sample_rows(tied.to(DEV), pack([(1.0, 2, 1.0, seed, 0)])).item() for seed in range(40)}
+    assert top2 == {0, 1}                                      # top-k among ties keeps the smaller ids

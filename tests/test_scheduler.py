@@ -1,0 +1,224 @@
+"""The scheduler's decisions, with the model replaced by a function that makes up tokens.  No GPU."""
+
+import random
+
+import pytest
+
+from tinyvllm_b200.cache.manager import CacheGroup, CacheManager
+from tinyvllm_b200.engine.scheduler import Request, RequestStatus, Scheduler
+from tinyvllm_b200.sampling.params import SamplingParams
+
+
+def make(pages=64, page_size=4, seqs=4, budget=32, chunk=16, max_len=128, window=None, eos=(),
+         reserve=(0, 0)):
+    groups = [CacheGroup((0,), 1, 16, None)]
+    if window is not None:
+        groups.append(CacheGroup((1,), 1, 16, window))
+    cache = CacheManager(groups, page_size, pages, seqs)
+    scheduler = Scheduler(cache, max_num_seqs=seqs, max_num_batched_tokens=budget,
+                          prefill_chunk_size=chunk, max_model_len=max_len, eos_token_ids=eos,
+                          prefill_reserve_tokens=reserve[0], prefill_reserve_requests=reserve[1])
+    return scheduler, cache
+
+
+def request(rid, prompt_len, new=4, **sampling):
+    return Request(rid, tuple(range(1, prompt_len + 1)), SamplingParams(max_new_tokens=new, **sampling))
+
+
+def run_step(scheduler, token_of=lambda rid: 100 + rid):
+    step = scheduler.schedule()
+    if step is None:
+        return None, []
+    events = scheduler.commit(step, {i.request_id: token_of(i.request_id) for i in step.items if i.sample})
+    scheduler.cache.check()
+    return step, events
+
+
+def drain(scheduler, token_of=lambda rid: 100 + rid, limit=10_000):
+    steps = []
+    while scheduler.has_unfinished():
+        step, _ = run_step(scheduler, token_of)
+        assert step is not None, "requests are unfinished but nothing can be scheduled"
+        steps.append(step)
+        assert len(steps) < limit
+    return steps
+
+
+def test_prompt_is_cut_under_the_chunk_and_token_budget():
+    scheduler, _ = make(budget=20, chunk=8)
+    scheduler.add(request(0, 19, new=2))
+    counts = []
+    while scheduler.has_unfinished():
+        step, _ = run_step(scheduler)
+        counts.append([(i.start, i.count, i.sample) for i in step.items])
+    assert counts == [[(0, 8, False)], [(8, 8, False)], [(16, 3, True)], [(19, 1, True)]]
+    done = scheduler.take_finished()
+    assert len(done) == 1 and done[0].output_token_ids == [100, 100] and done[0].finish_reason == "length"
+    assert done[0].computed_tokens == 20          # the last sampled token is never written
+
+
+def test_decodes_come_first_and_share_the_step_with_prefill():
+    scheduler, _ = make(budget=12, chunk=8, seqs=3)
+    scheduler.add(request(0, 3, new=10))
+    run_step(scheduler)                            # request 0 now decodes
+    scheduler.add(request(1, 30, new=2))
+    step, _ = run_step(scheduler)
+    assert [(i.request_id, i.count) for i in step.items] == [(0, 1), (1, 8)]
+    assert step.num_tokens <= 12
+    step, _ = run_step(scheduler)
+    assert [(i.request_id, i.start, i.count) for i in step.items] == [(0, 4, 1), (1, 8, 8)]
+
+
+def test_token_budget_limits_the_whole_step():
+    scheduler, _ = make(budget=10, chunk=10, seqs=4)
+    for rid in range(3):
+        scheduler.add(request(rid, 7, new=3))
+    step, _ = run_step(scheduler)
+    assert [(i.request_id, i.count) for i in step.items] == [(0, 7), (1, 3)]
+    step, _ = run_step(scheduler)
+    assert step.num_tokens <= 10 and step.items[0].request_id == 0 and step.items[0].count == 1
+
+
+def test_finish_reasons_and_eos():
+    scheduler, _ = make(eos=(7,))
+    scheduler.add(request(0, 3, new=5))
+    scheduler.add(request(1, 3, new=5, ignore_eos=True))
+    scheduler.add(request(2, 3, new=0))
+    assert [r.request_id for r in scheduler.take_finished()] == [2]        # nothing to generate
+    tokens = iter([5, 7, 7, 9, 9, 9, 9, 9, 9, 9])
+    while scheduler.has_unfinished():
+        run_step(scheduler, token_of=lambda rid: 7 if rid == 0 and next(tokens) else 7)
+    done = {r.request_id: r for r in scheduler.take_finished()}
+    assert done[0].finish_reason == "stop" and done[0].output_token_ids == [7]
+    assert done[1].finish_reason == "length" and len(done[1].output_token_ids) == 5
+    assert done[0].status is RequestStatus.FINISHED
+
+
+def test_max_model_len_stops_generation_and_refuses_long_prompts():
+    scheduler, _ = make(max_len=12, pages=16)
+    scheduler.add(request(0, 10, new=50))
+    drain(scheduler)
+    done = scheduler.take_finished()[0]
+    assert len(done.prompt_token_ids) + len(done.output_token_ids) == 12
+    with pytest.raises(ValueError, match="max_model_len"):
+        scheduler.add(request(1, 13))
+    with pytest.raises(ValueError, match="at least one token"):
+        scheduler.add(request(2, 0))
+    scheduler.add(request(3, 12, new=5))            # a prompt that fills the context ends at once
+    assert scheduler.take_finished()[0].output_token_ids == []
+
+
+def test_request_that_can_never_fit_is_refused_when_submitted():
+    scheduler, _ = make(pages=4, page_size=4)
+    with pytest.raises(ValueError, match="pages"):
+        scheduler.add(request(0, 20, new=4))
+    scheduler.add(request(1, 10, new=7))            # 10 + 7 - 1 = 16 tokens = 4 pages: fits exactly
+    drain(scheduler)
+
+
+def test_when_pages_run_out_requests_wait_and_nothing_is_preempted():
+    """Admission promises a request its whole lifetime, so a running request never lacks a page."""
+    scheduler, cache = make(pages=8, page_size=4, seqs=4, budget=64, chunk=64)
+    for rid in range(3):
+        scheduler.add(request(rid, 9, new=8))       # 16 written tokens = 4 pages each
+    step, _ = run_step(scheduler)
+    assert [i.request_id for i in step.items] == [0, 1]          # the third does not fit yet
+    assert list(scheduler.waiting) == [2]
+    seen_running = set()
+    while 2 in scheduler.waiting:
+        step, _ = run_step(scheduler)
+        if 2 in scheduler.waiting:
+            seen_running |= {i.request_id for i in step.items}
+    assert seen_running == {0, 1}
+    drain(scheduler)
+    done = {r.request_id: r for r in scheduler.take_finished()}
+    assert all(len(done[rid].output_token_ids) == 8 for rid in range(3))
+    assert cache.free_pages(0) == 8
+
+
+def test_a_large_waiter_does_not_block_smaller_ones():
+    scheduler, _ = make(pages=8, page_size=4, seqs=4, budget=64, chunk=64)
+    scheduler.add(request(0, 17, new=4))            # 20 tokens = 5 pages
+    scheduler.add(request(1, 17, new=4))            # does not fit beside request 0
+    scheduler.add(request(2, 5, new=4))             # 8 tokens = 2 pages: fits
+    step, _ = run_step(scheduler)
+    assert [i.request_id for i in step.items] == [0, 2]
+    assert list(scheduler.waiting) == [1]
+    drain(scheduler)
+    assert sorted(r.request_id for r in scheduler.take_finished()) == [0, 1, 2]
+
+
+def test_windowed_group_is_promised_less_than_a_full_one():
+    scheduler, cache = make(pages=6, page_size=4, window=6, chunk=4, budget=16, seqs=2, max_len=64)
+    probe = request(0, 10, new=12)                  # 21 written tokens: 6 pages in the full group
+    assert scheduler.lifetime_pages(probe) == (6, 4)
+    scheduler.add(probe)
+    drain(scheduler)
+    assert cache.free_pages(0) == 6 and cache.free_pages(1) == 6
+
+
+def test_cancel_gives_everything_back():
+    scheduler, cache = make()
+    scheduler.add(request(0, 20, new=8))
+    scheduler.add(request(1, 5, new=8))
+    run_step(scheduler)
+    assert scheduler.cancel(0) and not scheduler.cancel(0) and not scheduler.cancel(99)
+    done = scheduler.take_finished()
+    assert done[0].status is RequestStatus.ABORTED and done[0].finish_reason == "cancelled"
+    drain(scheduler)
+    assert cache.free_pages(0) == 64 and cache.slots.free_count == 4
+
+
+def test_aborted_step_returns_its_pages():
+    scheduler, cache = make()
+    scheduler.add(request(0, 10, new=2))
+    step = scheduler.schedule()
+    assert cache.free_pages(0) < 64
+    scheduler.abort_step(step)
+    assert cache.free_pages(0) == 64
+    cache.check()
+
+
+def test_prefill_reservation_holds_room_back_from_decodes():
+    scheduler, _ = make(seqs=4, budget=8, chunk=6, reserve=(4, 1))
+    for rid in range(3):
+        scheduler.add(request(rid, 1, new=20))
+    run_step(scheduler)                             # three one-token prompts, all decode afterwards
+    scheduler.add(request(3, 30, new=2))
+    step, _ = run_step(scheduler)
+    kinds = [(i.request_id, i.count) for i in step.items]
+    assert kinds[:3] == [(0, 1), (1, 1), (2, 1)] and kinds[3][0] == 3 and kinds[3][1] >= 4
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_workloads_finish_with_every_token_accounted_for(seed):
+    rng = random.Random(seed)
+    scheduler, cache = make(pages=rng.randrange(24, 60), page_size=rng.choice([2, 4, 8]),
+                            seqs=rng.randrange(2, 6), budget=rng.randrange(8, 40), chunk=8,
+                            window=rng.choice([None, 5, 12]), max_len=96)
+    expected = {}
+    submitted = 0
+    steps = 0
+    while submitted < 25 or scheduler.has_unfinished():
+        if submitted < 25 and rng.random() < 0.4:
+            prompt, new = rng.randrange(1, 40), rng.randrange(0, 20)
+            try:
+                scheduler.add(request(submitted, prompt, new=new))
+                expected[submitted] = min(new, 96 - prompt)
+            except ValueError:
+                pass
+            submitted += 1
+        step, _ = run_step(scheduler)
+        if step is not None:
+            assert step.num_tokens <= scheduler.max_num_batched_tokens
+            assert len(step.items) <= scheduler.max_num_seqs
+            ids = [i.request_id for i in step.items]
+            assert len(ids) == len(set(ids))
+        steps += 1
+        assert steps < 5000
+    done = {}
+    for r in scheduler.take_finished():
+        done[r.request_id] = r
+    # requests finished earlier were already taken by nobody: collect them from the loop above
+    assert all(pool.free_count == pool.num_pages for pool in cache.pools)
+    assert cache.slots.free_count == cache.slots.num_slots
