@@ -149,7 +149,7 @@ def random_prompt(rng: random.Random, count: int) -> list[int]:
     return [rng.randrange(MODEL["vocab_size"]) for _ in range(count)]
 
 
-def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloat16"):
+def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloat16", eager: bool = False):
     from tinyvllm_b200 import EngineConfig
     from tinyvllm_b200.engine.engine import Engine
     from tinyvllm_b200.models import Qwen3Config
@@ -163,7 +163,7 @@ def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloa
         max_num_seqs=max_num_seqs, max_num_batched_tokens=max(4096, max_num_seqs),
         prefill_chunk_size=2048, prefill_reserve_tokens=0, prefill_reserve_requests=0,
         kv_block_size=16, kv_cache_memory_bytes=kv_budget,
-        graph_batch_sizes=(max_num_seqs,))
+        graph_batch_sizes=(max_num_seqs,), enforce_eager=eager)
     return Engine.from_config(engine_config)
 
 
@@ -285,6 +285,30 @@ def run_prefill(engine, repeats: int = 5):
     return statistics.median(times)
 
 
+def eager_profile(args, warmup: int) -> int:
+    """Decode steps and one prefill through the eager path, so that a profiler sees every kernel."""
+    import torch
+
+    from tinyvllm_b200 import SamplingParams
+
+    rng = random.Random(0)
+    with tempfile.TemporaryDirectory() as folder:
+        engine = make_engine(folder, args.layers, args.batch, eager=True)
+        sampling = SamplingParams(max_new_tokens=warmup + args.steps + 4, ignore_eos=True)
+        for _ in range(args.batch):
+            engine.submit(random_prompt(rng, PROMPT_TOKENS), sampling)
+        while engine.scheduler.prefilling or engine.scheduler.waiting:
+            engine.step()
+        torch.cuda.synchronize()
+        for _ in range(warmup + args.steps):
+            engine.step()
+        torch.cuda.synchronize()
+        for request_id in list(engine.scheduler.decoding):
+            engine.cancel(request_id)
+        print("eager profile run: ok", run_prefill(engine, repeats=1), "ms prefill")
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -294,6 +318,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    parser.add_argument("--eager-profile", action="store_true",
+                        help="no graphs: run warm-up + steps decode steps and one prefill kernel by "
+                             "kernel, for a profiler; prints no bench line")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built (this engine is single-GPU)")
@@ -304,6 +331,8 @@ def main() -> int:
 
     import torch
 
+    if args.eager_profile:
+        return eager_profile(args, warmup)
     peak, peak_source = peaks()
     sampler = ClockSampler()
     sampler.start()

@@ -24,6 +24,8 @@ LENGTHS = {
     "a": (1, 7, 19, 70, 300, 600),
     "b": (3, 16, 31, 50, 290, 700),
     "c": (5, 45, 130, 530),
+    "d": (2, 64, 65, 200, 640),
+    "e": (1, 33, 128, 300, 513),
 }
 
 

@@ -308,3 +308,142 @@ def test_sampling_distribution_and_ties():
     tied = torch.zeros(1, 50)
     top2 = {k().sample_rows(tied.to(DEV), pack([(1.0, 2, 1.0, seed, 0)])).item() for seed in range(40)}
     assert top2 == {0, 1}                                      # top-k among ties keeps the smaller ids
+
+
+# ------------------------------------------------------------ tiled bfloat16 kernels
+def prefill_tile_lists(case):
+    """Tiles of up to 64 consecutive query tokens per request, from the flat case."""
+    rows, firsts, counts = [], [], []
+    token_row = case["token_row"].tolist()
+    start = 0
+    while start < len(token_row):
+        end = start
+        while end < len(token_row) and token_row[end] == token_row[start]:
+            end += 1
+        for first in range(start, end, 64):
+            rows.append(token_row[start]), firsts.append(first), counts.append(min(64, end - first))
+        start = end
+    as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    return as_int(rows), as_int(firsts), as_int(counts)
+
+
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("shape", [(8, 2, 64, 16), (4, 4, 128, 16), (16, 8, 128, 5), (2, 1, 64, 64)])
+def test_attention_prefill_tiles(shape, window):
+    nq, nkv, d, page = shape
+    dtype = torch.bfloat16
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[300, 1, 70, 515, 64],
+                      queries=[130, 1, 70, 3, 64], seed=d + nq)
+    scale = d ** -0.5
+    want = plain_paged(case, scale, window, dtype)
+    tile_row, tile_first, tile_count = prefill_tile_lists(case)
+    q = case["q"].to(DEV).view(-1, nq * d)
+    got = k().attention_prefill(q, nq * d, case["kc"].to(DEV), case["vc"].to(DEV), case["tables"].to(DEV),
+                                case["positions"].to(DEV), tile_row, tile_first, tile_count, num_q=nq,
+                                num_kv=nkv, head_dim=d, window=window, scale=scale).view(-1, nq, d)
+    close(got, want, dtype, bf16=1.2e-2)
+
+
+def test_attention_prefill_window_edge_and_far_key():
+    nq, nkv, d, page, dtype = 2, 1, 64, 16, torch.bfloat16
+    for window in (64, 65, 200):
+        length = 700
+        outside = length - 1 - window
+        case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[length], queries=[90],
+                          seed=window, boost=(0, outside, 30.0))
+        want = plain_paged(case, 0.2, window, dtype)
+        tiles = prefill_tile_lists(case)
+        got = k().attention_prefill(case["q"].to(DEV).view(-1, nq * d), nq * d, case["kc"].to(DEV),
+                                    case["vc"].to(DEV), case["tables"].to(DEV), case["positions"].to(DEV),
+                                    *tiles, num_q=nq, num_kv=nkv, head_dim=d, window=window,
+                                    scale=0.2).view(-1, nq, d)
+        close(got, want, dtype, bf16=1.2e-2)
+
+
+@pytest.mark.parametrize("window", [None, 150])
+@pytest.mark.parametrize("shape", [(4, 2, 64, 16, 128), (8, 2, 128, 16, 128), (2, 2, 128, 7, 192),
+                                   (8, 1, 256, 32, 256), (16, 8, 128, 16, 512)])
+def test_attention_decode_fused(shape, window):
+    """Raw projection in, attention out: against q/k norm + rotation + attention of the plain
+    functions, with the new key and value checked in the cache."""
+    nq, nkv, d, page, split_keys = shape
+    dtype = torch.bfloat16
+    lengths = [1, 2, 63, 64, 65, 300, 511, 1000]
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=lengths, queries=[1] * len(lengths),
+                      seed=d + nq)
+    requests = len(lengths)
+    g = torch.Generator().manual_seed(7)
+    qkv = torch.randn(requests, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    qw, kw = (1 + 0.1 * torch.randn(d, generator=g)), (1 + 0.1 * torch.randn(d, generator=g))
+    cos, sin = plain.rope_tables(d, 1200, 10_000.0)
+    positions = case["positions"]
+    # the slot of the new token is the one the block table gives for its position
+    slots = torch.tensor([int(case["tables"][r, int(p) // page]) * page + int(p) % page
+                          for r, p in enumerate(positions)], dtype=torch.int32)
+    kc, vc = case["kc"].to(DEV).clone(), case["vc"].to(DEV).clone()
+    splits = -(-1024 // split_keys)
+    got = k().attention_decode(
+        qkv.to(DEV), num_q=nq, num_kv=nkv, head_dim=d, positions=positions.to(DEV),
+        token_row=case["token_row"].to(DEV), slots=slots.to(DEV), q_weight=qw.to(DEV), k_weight=kw.to(DEV),
+        eps=1e-6, cos=cos.to(DEV), sin=sin.to(DEV), key_cache=kc, value_cache=vc,
+        block_tables=case["tables"].to(DEV), window=window, scale=d ** -0.5, split_keys=split_keys,
+        splits=splits).view(requests, nq, d)
+    q = qkv[:, :nq * d].float().view(requests, nq, d)
+    kn = qkv[:, nq * d:(nq + nkv) * d].float().view(requests, nkv, d)
+    vn = qkv[:, (nq + nkv) * d:].float().view(requests, nkv, d)
+    pos = positions.long()
+    want_q, want_k = plain.qk_norm_rope(q, kn, qw, kw, cos[pos], sin[pos], 1e-6, dtype)
+    rows = []
+    for r, p in enumerate(pos.tolist()):
+        keys = torch.cat([case["keys"][r][:p], want_k[r:r + 1]])
+        values = torch.cat([case["values"][r][:p], vn[r:r + 1]])
+        rows.append(plain.causal_attention(want_q[r:r + 1], keys, values, d ** -0.5, window, dtype,
+                                           q_positions=torch.tensor([p]))[0])
+    close(got, torch.stack(rows), dtype, bf16=1.2e-2)
+    stored_k = kc.view(-1, nkv, d)[slots.long().to(DEV)]
+    close(stored_k, want_k, dtype, bf16=1.6e-2)
+    assert torch.equal(vc.view(-1, nkv, d)[slots.long().to(DEV)].float().cpu(), vn)
+
+
+def test_attention_decode_padding_and_unsupported():
+    from tinyvllm_b200.ops.kernels import KernelError
+    assert k().attention_decode_supports(128, 16, 8, 8)
+    assert not k().attention_decode_supports(48, 4, 2, 8)
+    assert not k().attention_decode_supports(128, 6, 2, 8)       # groups of 3
+    assert not k().attention_decode_supports(128, 16, 8, 9)
+    with pytest.raises(KernelError, match="does not take"):
+        k().attention_decode(torch.zeros(1, 4 * 48, dtype=torch.bfloat16, device=DEV), num_q=2, num_kv=1,
+                             head_dim=48, positions=None, token_row=None, slots=None, q_weight=None,
+                             k_weight=None, eps=0.0, cos=None, sin=None, key_cache=None, value_cache=None,
+                             block_tables=None, window=None, scale=1.0, split_keys=64, splits=1)
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 128), (8, 1024, 4096), (8, 3072, 1024), (5, 1000, 136),
+                                   (17, 2048, 1024), (32, 520, 72), (3, 8, 16)])
+def test_gemm_small_m(shape):
+    m, kk, n = shape
+    torch.manual_seed(n)
+    x, w = torch.randn(m, kk).bfloat16(), (torch.randn(n, kk) * 0.05).bfloat16()
+    want = x.float() @ w.float().T
+    got = k().gemm_small_m(x.to(DEV), w.to(DEV), 1)
+    assert got.dtype == torch.float32
+    close(got, want, torch.float32, f32=2e-5)
+    got16 = k().gemm_small_m(x.to(DEV), w.to(DEV), 0)
+    assert got16.dtype == torch.bfloat16
+    close(got16, want, torch.bfloat16, bf16=5e-3)
+    alone = k().gemm_small_m(x[:1].to(DEV), w.to(DEV), 1)
+    assert torch.equal(alone[0], got[0])                    # a row's sum does not depend on the batch
+    if n % 2 == 0:
+        gate_up = k().gemm_small_m(x.to(DEV), w.to(DEV), 2)
+        assert gate_up.shape == (m, n // 2)
+        close(gate_up, plain.swiglu(want, torch.bfloat16), torch.bfloat16, bf16=1e-2)
+
+
+def test_gemm_small_m_refuses():
+    from tinyvllm_b200.ops.kernels import KernelError
+    with pytest.raises(KernelError, match="up to 32 rows"):
+        k().gemm_small_m(torch.zeros(33, 64, dtype=torch.bfloat16, device=DEV),
+                         torch.zeros(16, 64, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(KernelError, match="multiples of 8"):
+        k().gemm_small_m(torch.zeros(2, 60, dtype=torch.bfloat16, device=DEV),
+                         torch.zeros(16, 60, dtype=torch.bfloat16, device=DEV))

@@ -1,6 +1,6 @@
 """Tiny configurations of the architecture for the tests, and their workloads.
 
-The three differ in every size and option: layers, width, heads and groups
+The first three differ in every size and option: layers, width, heads and groups
 (4:1, 6:2, 5:5), head size (16, 32, 48), feed-forward width, vocabulary (one a
 prime), rotary base, norm eps, tied or untied head, window (none, none, 40 keys
 on two of three layers), page size.  Sizes that are no power of two: 96, 224,
@@ -25,9 +25,19 @@ TINY_CONFIGS = {
         num_attention_heads=5, num_key_value_heads=5, head_dim=48, max_position_embeddings=1536,
         rope_theta=500_000.0, rms_norm_eps=3e-6, tie_word_embeddings=False,
         layer_windows=(40, None, 40)),
+    # head sizes the tiled bfloat16 kernels take: 64 (groups of 2, a window) and 128 (groups of 4)
+    "d": Qwen3Config(
+        vocab_size=211, hidden_size=128, intermediate_size=192, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64, max_position_embeddings=1024,
+        rope_theta=100_000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+        layer_windows=(None, 100)),
+    "e": Qwen3Config(
+        vocab_size=300, hidden_size=160, intermediate_size=256, num_hidden_layers=2,
+        num_attention_heads=8, num_key_value_heads=2, head_dim=128, max_position_embeddings=1024,
+        rope_theta=1_000_000.0, rms_norm_eps=1e-6, tie_word_embeddings=False),
 }
-SEEDS = {"a": 0, "b": 1, "c": 2}
-PAGE_SIZES = {"a": 4, "b": 8, "c": 16}
+SEEDS = {"a": 0, "b": 1, "c": 2, "d": 3, "e": 4}
+PAGE_SIZES = {"a": 4, "b": 8, "c": 16, "d": 16, "e": 32}
 
 
 def random_tokens(vocab: int, count: int, seed: int) -> list[int]:

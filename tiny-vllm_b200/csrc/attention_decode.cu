@@ -1,0 +1,407 @@
+// Decode attention for bfloat16: one new token per request, fused from the packed
+// projection to the attention output.
+//
+// One launch does what the general path does in three: per-head RMSNorm and
+// rotation of the new q and k (tinyvllm/kernels/pointwise.cu:324-450), the write of
+// the new k and v into their cache page (tinyvllm/kernels/kv_store.cu:26-90) and
+// paged GQA attention (tinyvllm/kernels/paged_decode.cu:85-466).  Unlike the
+// reference kernel (one CTA per request and q head, no split over the context,
+// :586-590) a CTA serves HPB q heads that share one kv head, so keys and values
+// are read once per group, and the context is split over a thread-block cluster of
+// up to 8 CTAs whose partial (max, sum, output) are merged through distributed
+// shared memory: no scratch in global memory and no second kernel.
+//
+// Keys of a split are walked in tiles of 64 (16 per warp); LPK = head_dim / 8 lanes
+// share a key, each lane holding 8 dimensions (one 16-byte load).  Scores, softmax
+// and output sums are float32.  Splits start at multiples of `split_keys`, which
+// the host fixes from the context limit, so a request's result does not depend on
+// the batch it is in.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+#define DEC_WARPS 4
+#define DEC_UNROLL 8
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+template <int HEAD_DIM, int HPB>
+struct DecodeShared {
+    float q[HPB][HEAD_DIM];            // normalised, rotated, rounded q heads
+    float k_new[HEAD_DIM];             // the new key and value as stored (rounded)
+    float v_new[HEAD_DIM];
+    float warp_o[DEC_WARPS][HPB][HEAD_DIM];
+    float warp_m[DEC_WARPS][HPB];
+    float warp_l[DEC_WARPS][HPB];
+    float part_o[HPB][HEAD_DIM];       // this CTA's partial, read by rank 0 of the cluster
+    float part_m[HPB];
+    float part_l[HPB];
+};
+
+// RMSNorm + half-split rotation of one head by one warp; result rounded to bfloat16, as float.
+template <int HEAD_DIM, typename W>
+__device__ __forceinline__ void norm_rotate_head(const bf16* __restrict__ src, const W* __restrict__ weight,
+                                                 float eps, const float* __restrict__ cos_row,
+                                                 const float* __restrict__ sin_row, float* __restrict__ dst,
+                                                 int lane) {
+    constexpr int HALF = HEAD_DIM / 2;
+    constexpr int PAIRS = (HALF + 31) / 32;
+    float a[PAIRS], b[PAIRS];
+    float squares = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        a[i] = b[i] = 0.0f;
+        if (j < HALF) {
+            a[i] = __bfloat162float(src[j]);
+            b[i] = __bfloat162float(src[j + HALF]);
+            squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(a[i], a[i]), __fmul_rn(b[i], b[i])));
+        }
+    }
+    float inverse_rms = 1.0f;
+    if (weight) {
+        squares = warp_sum(squares);
+        inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(squares, 1.0f / (float)HEAD_DIM), eps)));
+    }
+#pragma unroll
+    for (int i = 0; i < PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        if (j < HALF) {
+            float x = a[i], y = b[i];
+            if (weight) {
+                x = round_to<bf16>(__fmul_rn(round_to<bf16>(__fmul_rn(x, inverse_rms)), to_float<W>(weight[j])));
+                y = round_to<bf16>(__fmul_rn(round_to<bf16>(__fmul_rn(y, inverse_rms)), to_float<W>(weight[j + HALF])));
+            }
+            if (cos_row) {
+                const float c = round_to<bf16>(cos_row[j]), s = round_to<bf16>(sin_row[j]);
+                const float xc = round_to<bf16>(__fmul_rn(x, c)), ys = round_to<bf16>(__fmul_rn(y, s));
+                const float yc = round_to<bf16>(__fmul_rn(y, c)), xs = round_to<bf16>(__fmul_rn(x, s));
+                x = round_to<bf16>(__fsub_rn(xc, ys));
+                y = round_to<bf16>(__fadd_rn(yc, xs));
+            }
+            dst[j] = x;
+            dst[j + HALF] = y;
+        }
+    }
+}
+
+template <int HEAD_DIM, int HPB, typename W>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_weight,
+                        const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_table,
+                        const float* __restrict__ sin_table, int table_positions,
+                        const int* __restrict__ positions, const int* __restrict__ token_row,
+                        const int* __restrict__ slots, bf16* __restrict__ key_cache,
+                        bf16* __restrict__ value_cache, const int* __restrict__ block_tables,
+                        int table_stride, int page_size, bf16* __restrict__ out, int num_q, int num_kv,
+                        int window, float scale, int split_keys, int write_cache) {
+    constexpr int LPK = HEAD_DIM / 8;          // lanes that share one key
+    constexpr int KPI = 32 / LPK;              // keys per warp instruction
+    constexpr int WARP_KEYS = KPI * DEC_UNROLL;
+    constexpr int TILE_KEYS = WARP_KEYS * DEC_WARPS;
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    DecodeShared<HEAD_DIM, HPB>& sh = *reinterpret_cast<DecodeShared<HEAD_DIM, HPB>*>(shared_raw);
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int split = blockIdx.x;              // = rank in the cluster
+    const int splits = gridDim.x;
+    const int group = num_q / num_kv;
+    const int blocks_per_kv = group / HPB;
+    const int kv_head = blockIdx.y / blocks_per_kv;
+    const int first_q_head = kv_head * group + (blockIdx.y % blocks_per_kv) * HPB;
+    const int request = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = num_q + 2 * num_kv;
+    const int position = positions[request];
+    const int row = token_row[request];
+    bf16* out_row = out + ((int64_t)request * num_q + first_q_head) * HEAD_DIM;
+    if (row < 0 || position < 0) {              // padding: the whole cluster leaves together
+        if (split == 0)
+            for (int i = threadIdx.x; i < HPB * HEAD_DIM; i += blockDim.x) out_row[i] = __float2bfloat16_rn(0.0f);
+        return;
+    }
+
+    // ---- the new token: q heads of this CTA, and k, v of its kv head
+    {
+        const bf16* token = qkv + (int64_t)request * heads * HEAD_DIM;
+        const int table_row = min(position, table_positions - 1);
+        const float* cos_row = cos_table ? cos_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
+        const float* sin_row = sin_table ? sin_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
+        for (int job = warp; job < HPB + 2; job += DEC_WARPS) {
+            if (job < HPB) {
+                norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(first_q_head + job) * HEAD_DIM, q_weight, eps,
+                                              cos_row, sin_row, sh.q[job], lane);
+            } else if (job == HPB) {
+                norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(num_q + kv_head) * HEAD_DIM, k_weight, eps,
+                                              cos_row, sin_row, sh.k_new, lane);
+            } else {
+                const bf16* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
+                for (int i = lane; i < HEAD_DIM; i += 32) sh.v_new[i] = __bfloat162float(v[i]);
+            }
+        }
+    }
+    __syncthreads();
+
+    const int lo = window > 0 ? max(0, position - window + 1) : 0;
+    const int own_split = position / split_keys;          // the split that holds the new token
+    if (split == own_split && write_cache && (blockIdx.y % blocks_per_kv) == 0) {
+        const int slot = slots[request];
+        if (slot >= 0) {
+            bf16* kd = key_cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM;
+            bf16* vd = value_cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM;
+            for (int i = threadIdx.x; i < HEAD_DIM; i += blockDim.x) {
+                kd[i] = __float2bfloat16_rn(sh.k_new[i]);
+                vd[i] = __float2bfloat16_rn(sh.v_new[i]);
+            }
+        }
+    }
+
+    // ---- keys of this split that are already in the cache: [first, last]
+    const int first = max(lo, split * split_keys);
+    const int last = min(position - 1, split * split_keys + split_keys - 1);
+    const int sub = lane % LPK;                 // which 8 dimensions of a key this lane holds
+    const int key_in_instr = lane / LPK;
+    float q_reg[HPB][8];
+#pragma unroll
+    for (int h = 0; h < HPB; ++h)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q_reg[h][i] = sh.q[h][sub * 8 + i];
+
+    float m_run[HPB], l_run[HPB], o_run[HPB][8];
+#pragma unroll
+    for (int h = 0; h < HPB; ++h) {
+        m_run[h] = -INFINITY;
+        l_run[h] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o_run[h][i] = 0.0f;
+    }
+    const int* table = block_tables + (int64_t)row * table_stride;
+    const int64_t row_stride = (int64_t)num_kv * HEAD_DIM;
+    const bf16* k_base = key_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
+    const bf16* v_base = value_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
+
+    for (int tile = first - first % TILE_KEYS; tile <= last; tile += TILE_KEYS) {
+        const int warp_first = tile + warp * WARP_KEYS;
+        if (warp_first > last || warp_first + WARP_KEYS <= first) continue;
+        // slots of this warp's keys: lane i < WARP_KEYS looks up key warp_first + i
+        int my_slot = 0;
+        {
+            const int key = warp_first + lane;
+            if (lane < WARP_KEYS && key >= first && key <= last)
+                my_slot = table[key / page_size] * page_size + key % page_size;
+        }
+        uint4 raw[DEC_UNROLL];
+        bool valid[DEC_UNROLL];
+        int slot_of[DEC_UNROLL];
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            const int index = u * KPI + key_in_instr;
+            const int key = warp_first + index;
+            valid[u] = key >= first && key <= last;
+            slot_of[u] = __shfl_sync(0xffffffffu, my_slot, index);
+            raw[u] = *reinterpret_cast<const uint4*>(k_base + (int64_t)slot_of[u] * row_stride);
+        }
+        float score[HPB][DEC_UNROLL];
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            float kf[8];
+            unpack8(raw[u], kf);
+#pragma unroll
+            for (int h = 0; h < HPB; ++h) {
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dot = __fmaf_rn(q_reg[h][i], kf[i], dot);
+#pragma unroll
+                for (int delta = LPK / 2; delta > 0; delta >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, delta);
+                score[h][u] = valid[u] ? __fmul_rn(dot, scale) : -INFINITY;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u)      // values: issue the loads before the softmax arithmetic
+            raw[u] = *reinterpret_cast<const uint4*>(v_base + (int64_t)slot_of[u] * row_stride);
+        float prob[HPB][DEC_UNROLL];
+#pragma unroll
+        for (int h = 0; h < HPB; ++h) {
+            float tile_max = score[h][0];
+#pragma unroll
+            for (int u = 1; u < DEC_UNROLL; ++u) tile_max = fmaxf(tile_max, score[h][u]);
+#pragma unroll
+            for (int delta = LPK; delta < 32; delta <<= 1)
+                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, delta));
+            const float new_max = fmaxf(m_run[h], tile_max);      // finite: the tile has a valid key
+            const float rescale = m_run[h] == -INFINITY ? 0.0f : __expf(m_run[h] - new_max);
+            m_run[h] = new_max;
+            float sum = 0.0f;
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                prob[h][u] = valid[u] ? __expf(score[h][u] - new_max) : 0.0f;
+                sum += prob[h][u];
+            }
+            l_run[h] = l_run[h] * rescale + sum;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o_run[h][i] *= rescale;
+        }
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            float vf[8];
+            unpack8(raw[u], vf);
+            if (!valid[u]) {                      // whatever lies in a foreign slot must not reach the sum
+#pragma unroll
+                for (int i = 0; i < 8; ++i) vf[i] = 0.0f;
+            }
+#pragma unroll
+            for (int h = 0; h < HPB; ++h)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o_run[h][i] = __fmaf_rn(prob[h][u], vf[i], o_run[h][i]);
+        }
+    }
+
+    // ---- lanes that hold the same dimensions for different keys, then the warps, in a fixed order
+#pragma unroll
+    for (int h = 0; h < HPB; ++h) {
+#pragma unroll
+        for (int delta = LPK; delta < 32; delta <<= 1) {
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], delta);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o_run[h][i] += __shfl_xor_sync(0xffffffffu, o_run[h][i], delta);
+        }
+        if (lane < LPK) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sh.warp_o[warp][h][sub * 8 + i] = o_run[h][i];
+        }
+        if (lane == 0) { sh.warp_m[warp][h] = m_run[h]; sh.warp_l[warp][h] = l_run[h]; }
+    }
+    __syncthreads();
+    for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
+        const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, sh.warp_m[w][h]);
+        float l = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = sh.warp_m[w][h] == -INFINITY ? 0.0f : __expf(sh.warp_m[w][h] - m);
+            l += sh.warp_l[w][h] * f;
+            o += sh.warp_o[w][h][dim] * f;
+        }
+        if (split == own_split) {               // the new token itself, from shared memory
+            float dot = 0.0f;
+            for (int i = 0; i < HEAD_DIM; ++i) dot = __fmaf_rn(sh.q[h][i], sh.k_new[i], dot);
+            const float s = __fmul_rn(dot, scale);
+            const float new_max = fmaxf(m, s);
+            const float f_old = m == -INFINITY ? 0.0f : __expf(m - new_max);
+            const float f_new = __expf(s - new_max);
+            l = l * f_old + f_new;
+            o = o * f_old + f_new * sh.v_new[dim];
+            m = new_max;
+        }
+        sh.part_o[h][dim] = o;
+        if (dim == 0) { sh.part_m[h] = m; sh.part_l[h] = l; }
+    }
+
+    // ---- merge the splits of the cluster in rank order
+    cluster.sync();
+    if (split == 0) {
+        for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
+            const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
+            float m = -INFINITY;
+            for (int r = 0; r < splits; ++r) {
+                const DecodeShared<HEAD_DIM, HPB>* other = cluster.map_shared_rank(&sh, r);
+                m = fmaxf(m, other->part_m[h]);
+            }
+            float l = 0.0f, o = 0.0f;
+            for (int r = 0; r < splits; ++r) {
+                const DecodeShared<HEAD_DIM, HPB>* other = cluster.map_shared_rank(&sh, r);
+                const float pm = other->part_m[h];
+                const float f = pm == -INFINITY ? 0.0f : __expf(pm - m);
+                l += other->part_l[h] * f;
+                o += other->part_o[h][dim] * f;
+            }
+            out_row[index] = __float2bfloat16_rn(o / l);
+        }
+    }
+    cluster.sync();                             // nobody leaves while rank 0 still reads its memory
+}
+
+template <int HEAD_DIM, int HPB, typename W>
+static int launch_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
+                         const float* cos_table, const float* sin_table, int table_positions,
+                         const int* positions, const int* token_row, const int* slots, void* key_cache,
+                         void* value_cache, const int* block_tables, int table_stride, int page_size,
+                         void* out, int requests, int num_q, int num_kv, int window, float scale,
+                         int split_keys, int splits, int write_cache, cudaStream_t stream) {
+    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, W>;
+    const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB>);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(splits, num_kv * ((num_q / num_kv) / HPB), requests);
+    config.blockDim = dim3(DEC_WARPS * 32);
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = splits;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    e = cudaLaunchKernelEx(&config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
+                           cos_table, sin_table, table_positions, positions, token_row, slots,
+                           (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
+                           (bf16*)out, num_q, num_kv, window, scale, split_keys, write_cache);
+    return e == cudaSuccess ? tvb_last_error() : (int)e;
+}
+
+// 1 if the kernel takes this shape: head sizes 64, 128, 256; groups of 1, 2, 4 or a multiple of 4.
+extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv, int splits) {
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return 0;
+    if (num_kv <= 0 || num_q % num_kv) return 0;
+    const int group = num_q / num_kv;
+    if (!(group == 1 || group == 2 || group % 4 == 0)) return 0;
+    return splits >= 1 && splits <= 8;
+}
+
+// qkv: [requests, (num_q + 2 num_kv) * head_dim] bfloat16, the raw projection of one token per
+// request.  weight_dtype: TVB_BF16 or TVB_F32 (norm weights; null pointers skip the norm).
+// splits = ceil(context limit / split_keys) <= 8 is the cluster size.
+extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
+                                    const float* cos_table, const float* sin_table, int table_positions,
+                                    const int* positions, const int* token_row, const int* slots,
+                                    void* key_cache, void* value_cache, const int* block_tables,
+                                    int table_stride, int page_size, void* out, int requests, int num_q,
+                                    int num_kv, int head_dim, int window, float scale, int split_keys,
+                                    int splits, int write_cache, int weight_dtype, void* stream) {
+    if (requests <= 0) return 0;
+    if (!tvb_attention_decode_supports(head_dim, num_q, num_kv, splits) || split_keys <= 0 ||
+        page_size <= 0 || requests > 65535)
+        return TVB_BAD_ARGUMENT;
+    const int group = num_q / num_kv;
+    const int hpb = group % 4 == 0 ? 4 : group;
+    cudaStream_t s = (cudaStream_t)stream;
+#define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
+                    token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
+                    requests, num_q, num_kv, window, scale, split_keys, splits, write_cache, s
+#define DECODE_BY_HPB(D, WT)                                            \
+    do {                                                                \
+        if (hpb == 1) return launch_decode<D, 1, WT>(DECODE_ARGS);      \
+        if (hpb == 2) return launch_decode<D, 2, WT>(DECODE_ARGS);      \
+        return launch_decode<D, 4, WT>(DECODE_ARGS);                    \
+    } while (0)
+#define DECODE_BY_DIM(WT)                                               \
+    do {                                                                \
+        if (head_dim == 64) DECODE_BY_HPB(64, WT);                      \
+        if (head_dim == 128) DECODE_BY_HPB(128, WT);                    \
+        DECODE_BY_HPB(256, WT);                                         \
+    } while (0)
+    if (weight_dtype == TVB_F32) DECODE_BY_DIM(float);
+    if (weight_dtype == TVB_BF16) DECODE_BY_DIM(bf16);
+    return TVB_BAD_ARGUMENT;
+}

@@ -62,6 +62,12 @@ class StepContext:
     max_position: int                    # largest position in the step (bounds the split of attention)
     split_chunks: int                    # 0: walk the keys per row; n: spread n chunks over the grid
     workspace_of: object = None          # callable(floats) -> float32 scratch tensor
+    decode_only: bool = False            # every entry is a single token
+    decode_split_keys: int = 0           # keys per split of the fused decode attention
+    decode_splits: int = 0               # its number of splits (0: not used)
+    tile_row: torch.Tensor | None = None     # tiles of consecutive query tokens for the tile kernel:
+    tile_first: torch.Tensor | None = None   # request row, first flat token and token count of each
+    tile_count: torch.Tensor | None = None
     # host copies, for parts that plan on the host (and for tests)
     host_rows: tuple = ()                # (request_id, first position, count, state_slot, fresh) per entry
 
@@ -71,8 +77,6 @@ class StepContext:
     def workspace(self, floats: int) -> torch.Tensor:
         return self.workspace_of(floats)
 
-    def attend(self, mixer, qkv, keys, values, group: int):
-        return attention_ops.paged_attention(self, mixer, qkv, keys, values, group)
 
 
 class StepRunner:
@@ -98,6 +102,7 @@ class StepRunner:
         self._pinned: torch.Tensor | None = None
         self._pinned_free: torch.cuda.Event | None = None
         self._workspace: torch.Tensor | None = None
+        self.decode_split_keys, self.decode_splits = attention_ops.decode_split(self.max_model_len)
 
     # ------------------------------------------------------------- sizing
     @staticmethod
@@ -161,9 +166,13 @@ class StepRunner:
         wanted = sum(len(e.want) for e in entries)
         groups = len(self.manager.groups)
         blocks = [max(1, max(len(p.tables[g]) for p in plan.entries)) for g in range(groups)]
+        decode_only = all(count == 1 for count in counts)
+        tile_lists = ([], [], []) if decode_only else attention_ops.prefill_tiles(counts)
         sizes = [tokens, tokens, tokens, wanted, rows, rows + 1]
         for g in range(groups):
             sizes += [tokens, rows * blocks[g]]
+        tiles_at = len(sizes)
+        sizes += [len(tile_lists[0])] * 3
         offsets = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
         host = np.zeros(int(offsets[-1]), dtype=np.int32)
 
@@ -189,6 +198,8 @@ class StepRunner:
             max_position = max(max_position, planned.start + n - 1)
             cursor += n
         row_starts[rows] = cursor
+        for i in range(3):
+            view(tiles_at + i)[:] = tile_lists[i]
 
         device = self._upload(host)
 
@@ -206,7 +217,11 @@ class StepRunner:
             slots=[dview(6 + 2 * g) for g in range(groups)],
             block_tables=[dview(7 + 2 * g).view(rows, blocks[g]) for g in range(groups)],
             cache_sources=self.cache_sources, max_position=max_position, split_chunks=split_chunks,
-            workspace_of=self._workspace_of,
+            workspace_of=self._workspace_of, decode_only=decode_only,
+            decode_split_keys=self.decode_split_keys, decode_splits=self.decode_splits,
+            tile_row=None if decode_only else dview(tiles_at),
+            tile_first=None if decode_only else dview(tiles_at + 1),
+            tile_count=None if decode_only else dview(tiles_at + 2),
             host_rows=tuple((p.request_id, p.start, p.count, p.state_slot, p.fresh_state)
                             for p in plan.entries),
         )

@@ -2,7 +2,7 @@
 
 from .build import KernelBuildError, compile_all, compile_library, load_library, source_names
 from .kernels import KernelError
-from .linear import linear
+from .linear import linear, linear_silu
 
-__all__ = ["KernelBuildError", "KernelError", "compile_all", "compile_library", "linear",
+__all__ = ["KernelBuildError", "KernelError", "compile_all", "compile_library", "linear", "linear_silu",
            "load_library", "source_names"]

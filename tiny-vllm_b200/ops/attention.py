@@ -1,38 +1,96 @@
-"""Attention over the paged cache: which kernel runs a step.
+"""Attention over the paged cache: which kernels run a mixer's step.
 
-Every kernel computes the same thing: the query at position p attends the keys
-of its request from max(0, p - window + 1) to p through the block table.  The
-row kernel (one warp per token and head) takes every size and dtype; tiled
-kernels take over for the shapes they are written for.
+Every path computes the same thing: q and k are normalised per head and rotated, k and v
+go to their cache pages, and the query at position p attends the keys of its request from
+max(0, p - window + 1) to p through the block table.
+
+* bfloat16, every entry one token, head size 64/128/256: one fused launch
+  (``attention_decode``): norm, rotation, cache write and attention split over a cluster.
+* bfloat16, head size 64/128: ``qk_norm_rope_store`` then the tensor-core tile kernel
+  (``attention_prefill``).
+* everything else (float32, other head sizes): ``qk_norm_rope_store`` then the row kernel,
+  one warp per token and head.
 """
 
 from __future__ import annotations
 
+import torch
+
 from . import kernels
 
-# rows (tokens * heads) up to which the chunks of a row are spread over the grid
+# tokens up to which the row kernel spreads the chunks of a row over the grid
 SPLIT_MAX_TOKENS = 256
+DECODE_MAX_SPLITS = 8
+DECODE_SPLIT_GRAIN = 64
 
 
 def choose_split(tokens: int, max_position: int) -> int:
-    """Number of key chunks to spread over the grid, or 0 to walk them per row.
+    """Number of key chunks the row kernel spreads over the grid, or 0 to walk them per row.
 
-    Both ways give a row the same arithmetic, so the choice only trades
-    parallelism against scratch memory: few tokens with long contexts split."""
+    Both ways give a row the same arithmetic, so the choice only trades parallelism
+    against scratch memory: few tokens with long contexts split."""
     chunk = kernels.attention_chunk_keys()
     if tokens <= SPLIT_MAX_TOKENS and max_position + 1 > chunk:
         return -(-(max_position + 1) // chunk)
     return 0
 
 
-def paged_attention(ctx, mixer, qkv, keys, values, group: int):
-    """Attention output [tokens, heads * head_dim] for the step ``ctx``; the
-    query heads are read in place from the packed projection ``qkv``."""
+def decode_split(max_model_len: int) -> tuple[int, int]:
+    """(keys per split, number of splits) of the fused decode kernel: fixed by the context
+    limit alone, so that a request's sums do not depend on the batch it is in."""
+    keys = -(-max_model_len // DECODE_MAX_SPLITS)
+    keys = -(-keys // DECODE_SPLIT_GRAIN) * DECODE_SPLIT_GRAIN
+    return keys, -(-max_model_len // keys)
+
+
+def prefill_tiles(counts) -> tuple[list[int], list[int], list[int]]:
+    """Cut every entry into tiles of consecutive tokens: (row, first flat token, count) lists."""
+    size = kernels.attention_prefill_tile_tokens()
+    rows, firsts, sizes = [], [], []
+    cursor = 0
+    for row, count in enumerate(counts):
+        for start in range(0, count, size):
+            rows.append(row)
+            firsts.append(cursor + start)
+            sizes.append(min(size, count - start))
+        cursor += count
+    return rows, firsts, sizes
+
+
+def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
+    """From the packed projection ``qkv`` [tokens, (q + 2 kv) * head_dim] of a step to the
+    attention output [tokens, q * head_dim]; writes the step's keys and values."""
+    keys, values = ctx.storage.kv_of(run)
+    group = ctx.storage.group_of(run)
+    writes = ctx.writes_cache(run)
+    position = mixer.position
+    cos = sin = None
+    if position is not None:
+        cos, sin = position.cos, position.sin
+    heads = dict(num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.head_dim)
+    tiled = qkv.dtype == torch.bfloat16
+    if (tiled and ctx.decode_only and writes and ctx.decode_splits > 0
+            and kernels.attention_decode_supports(mixer.head_dim, mixer.num_heads, mixer.num_kv_heads,
+                                                  ctx.decode_splits)):
+        return kernels.attention_decode(
+            qkv, **heads, positions=ctx.positions, token_row=ctx.token_row, slots=ctx.slots[group],
+            q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0,
+            cos=cos, sin=sin, key_cache=keys, value_cache=values, block_tables=ctx.block_tables[group],
+            window=mixer.window, scale=mixer.scale, split_keys=ctx.decode_split_keys,
+            splits=ctx.decode_splits)
+    kernels.qk_norm_rope_store(
+        qkv, **heads, positions=ctx.positions, q_weight=mixer.q_norm_weight,
+        k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0, cos=cos, sin=sin,
+        slots=ctx.slots[group] if writes else None, key_cache=keys, value_cache=values)
+    if (tiled and ctx.tile_row is not None
+            and kernels.attention_prefill_supports(mixer.head_dim, mixer.num_heads, mixer.num_kv_heads)):
+        return kernels.attention_prefill(
+            qkv, qkv.shape[1], keys, values, ctx.block_tables[group], ctx.positions, ctx.tile_row,
+            ctx.tile_first, ctx.tile_count, **heads, window=mixer.window, scale=mixer.scale)
     scratch = None
     if ctx.split_chunks > 0:
         scratch = ctx.workspace(kernels.attention_rows_scratch_floats(
             ctx.num_tokens, mixer.num_heads, mixer.head_dim, ctx.split_chunks))
     return kernels.attention_rows(
         qkv, qkv.shape[1], keys, values, ctx.block_tables[group], ctx.token_row, ctx.positions,
-        num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.head_dim,
-        window=mixer.window, scale=mixer.scale, scratch=scratch, max_chunks=ctx.split_chunks)
+        **heads, window=mixer.window, scale=mixer.scale, scratch=scratch, max_chunks=ctx.split_chunks)

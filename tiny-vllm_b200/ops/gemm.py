@@ -1,4 +1,9 @@
-"""bfloat16 matrix products: which kernel takes which shape."""
+"""bfloat16 matrix products: which kernel takes which shape.
+
+Up to 32 rows (decode): the package's weight-streaming kernel.  More rows: cuBLAS
+through ``torch.nn.functional.linear``, the library call the reference's engine makes
+for every projection (tinyvllm/layers.py:84-85).
+"""
 
 from __future__ import annotations
 
@@ -7,15 +12,36 @@ import torch
 from . import kernels
 
 
+def _small(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.shape[0] <= kernels.SMALL_M_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0)
+
+
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype,
                 out: torch.Tensor | None = None) -> torch.Tensor:
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise kernels.KernelError("linear_bf16 wants bfloat16 operands")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise kernels.KernelError(f"linear_bf16 cannot produce {out_dtype}")
+    if _small(x, weight):
+        mode = kernels.GEMM_BF16 if out_dtype == torch.bfloat16 else kernels.GEMM_F32
+        return kernels.gemm_small_m(x, weight, mode, out=out)
     if out_dtype == torch.bfloat16:
         if out is not None:
             return torch.mm(x, weight.t(), out=out)
         return torch.nn.functional.linear(x, weight)
-    if out_dtype == torch.float32:
+    if x.shape[0] <= 256:
         # float32 results (logits) keep the float32 accumulator unrounded
         return kernels.gemm_nt_simt(x, weight, out=out, out_dtype=torch.float32)
-    raise kernels.KernelError(f"linear_bf16 cannot produce {out_dtype}")
+    result = torch.nn.functional.linear(x, weight).float()
+    if out is not None:
+        out.copy_(result)
+        return out
+    return result
+
+
+def linear_silu_bf16(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
+    """silu(x . gate^T) * (x . up^T) for a packed [gate | up] weight."""
+    if _small(x, gate_up_weight):
+        return kernels.gemm_small_m(x, gate_up_weight, kernels.GEMM_SILU)
+    return kernels.silu_mul(torch.nn.functional.linear(x, gate_up_weight))

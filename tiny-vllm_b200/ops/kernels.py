@@ -304,3 +304,142 @@ def sample_rows(logits: torch.Tensor, packed: torch.Tensor, out: torch.Tensor | 
     _check(fn(logits.data_ptr(), logits.stride(0), rows, vocab, packed.data_ptr(), packed.shape[1],
               out.data_ptr(), dtype_tag(logits.dtype), _stream()), "sample_rows")
     return out
+
+
+# ------------------------------------------------- tiled attention (bfloat16)
+def attention_decode_supports(head_dim: int, num_q: int, num_kv: int, splits: int) -> bool:
+    fn = _fn("attention_decode", "tvb_attention_decode_supports", [c_int, c_int, c_int, c_int])
+    return bool(fn(head_dim, num_q, num_kv, splits))
+
+
+def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: int,
+                     positions: torch.Tensor, token_row: torch.Tensor, slots: torch.Tensor | None,
+                     q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
+                     cos: torch.Tensor | None, sin: torch.Tensor | None, key_cache: torch.Tensor,
+                     value_cache: torch.Tensor, block_tables: torch.Tensor, window: int | None,
+                     scale: float, split_keys: int, splits: int,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """One new token per request, from the raw packed projection to the attention output:
+    q/k norm and rotation, cache write (unless ``slots`` is None) and attention in one launch.
+    Request i is row ``token_row[i]`` of ``block_tables`` (-1: padding) and stands at
+    ``positions[i]``.  The context is cut into ``splits`` pieces of ``split_keys`` keys."""
+    _need_cuda(qkv, positions, token_row, slots, q_weight, k_weight, cos, sin, key_cache, value_cache,
+               block_tables)
+    requests = qkv.shape[0]
+    if qkv.dtype != torch.bfloat16 or not qkv.is_contiguous() or \
+            qkv.shape[1] != (num_q + 2 * num_kv) * head_dim:
+        raise KernelError("attention_decode wants contiguous bfloat16 [requests, (q + 2 kv) * head_dim]")
+    if not attention_decode_supports(head_dim, num_q, num_kv, splits):
+        raise KernelError(f"attention_decode does not take head_dim {head_dim}, {num_q}/{num_kv} heads, "
+                          f"{splits} splits")
+    if key_cache.dtype != torch.bfloat16 or tuple(key_cache.shape[2:]) != (num_kv, head_dim) or \
+            value_cache.shape != key_cache.shape or not key_cache.is_contiguous():
+        raise KernelError("attention_decode: caches must be contiguous bfloat16 "
+                          "[pages, page_size, num_kv, head_dim]")
+    for t in (positions, token_row, block_tables) + ((slots,) if slots is not None else ()):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError("attention_decode: index tensors must be contiguous int32")
+    if splits * split_keys <= 0:
+        raise KernelError("attention_decode: splits and split_keys must be positive")
+    weight_tag = BF16
+    if q_weight is not None:
+        if k_weight is None or q_weight.dtype != k_weight.dtype or q_weight.shape != (head_dim,):
+            raise KernelError("attention_decode: norm weights come together, [head_dim], one dtype")
+        weight_tag = dtype_tag(q_weight.dtype)
+    table_positions = cos.shape[0] if cos is not None else 0
+    if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != head_dim // 2):
+        raise KernelError("attention_decode: tables must be float32 [positions, head_dim / 2]")
+    if out is None:
+        out = torch.empty((requests, num_q * head_dim), dtype=qkv.dtype, device=qkv.device)
+    fn = _fn("attention_decode", "tvb_attention_decode",
+             [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+              c_int, c_float, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos), _ptr(sin), table_positions,
+              positions.data_ptr(), token_row.data_ptr(), _ptr(slots), key_cache.data_ptr(),
+              value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
+              key_cache.shape[1], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
+              split_keys, splits, 1 if slots is not None else 0, weight_tag, _stream()),
+           "attention_decode")
+    return out
+
+
+def attention_prefill_supports(head_dim: int, num_q: int, num_kv: int) -> bool:
+    fn = _fn("attention_prefill", "tvb_attention_prefill_supports", [c_int, c_int, c_int])
+    return bool(fn(head_dim, num_q, num_kv))
+
+
+_prefill_tile: int | None = None
+
+
+def attention_prefill_tile_tokens() -> int:
+    global _prefill_tile
+    if _prefill_tile is None:
+        _prefill_tile = _fn("attention_prefill", "tvb_attention_prefill_tile_tokens", [])()
+    return _prefill_tile
+
+
+def attention_prefill(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor,
+                      value_cache: torch.Tensor, block_tables: torch.Tensor, positions: torch.Tensor,
+                      tile_row: torch.Tensor, tile_first: torch.Tensor, tile_count: torch.Tensor, *,
+                      num_q: int, num_kv: int, head_dim: int, window: int | None, scale: float,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """Paged causal attention on the tensor cores for tiles of up to 64 consecutive query
+    tokens of one request (bfloat16).  Tile i holds ``tile_count[i]`` tokens from flat index
+    ``tile_first[i]`` on of request row ``tile_row[i]``."""
+    _need_cuda(q, key_cache, value_cache, block_tables, positions, tile_row, tile_first, tile_count)
+    if q.dtype != torch.bfloat16 or key_cache.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill is a bfloat16 kernel")
+    if not attention_prefill_supports(head_dim, num_q, num_kv):
+        raise KernelError(f"attention_prefill does not take head_dim {head_dim}, {num_q}/{num_kv} heads")
+    if tuple(key_cache.shape[2:]) != (num_kv, head_dim) or value_cache.shape != key_cache.shape or \
+            not key_cache.is_contiguous() or not value_cache.is_contiguous():
+        raise KernelError("attention_prefill: caches must be contiguous [pages, page_size, num_kv, head_dim]")
+    for t in (block_tables, positions, tile_row, tile_first, tile_count):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError("attention_prefill: index tensors must be contiguous int32")
+    tokens, tiles = positions.shape[0], tile_row.shape[0]
+    if out is None:
+        out = torch.empty((tokens, num_q * head_dim), dtype=q.dtype, device=q.device)
+    fn = _fn("attention_prefill", "tvb_attention_prefill",
+             [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(q.data_ptr(), q_token_stride, key_cache.data_ptr(), value_cache.data_ptr(),
+              block_tables.data_ptr(), block_tables.shape[1], positions.data_ptr(), tile_row.data_ptr(),
+              tile_first.data_ptr(), tile_count.data_ptr(), out.data_ptr(), tiles, num_q, num_kv,
+              head_dim, key_cache.shape[1], window or 0, scale, _stream()), "attention_prefill")
+    return out
+
+
+# ------------------------------------------------ weight-streaming small-M GEMM
+SMALL_M_MAX_ROWS = 32
+GEMM_BF16, GEMM_F32, GEMM_SILU = 0, 1, 2
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
+                 out: torch.Tensor | None = None, pdl: bool = False) -> torch.Tensor:
+    """x [m <= 32, k] . w [n, k]^T, bfloat16 operands.  mode GEMM_BF16 / GEMM_F32: result
+    [m, n] in that dtype; GEMM_SILU: w is [gate | up] with 2 n rows and the result is
+    silu(x . gate^T) * (x . up^T), bfloat16 [m, n]."""
+    _need_cuda(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2:
+        raise KernelError("gemm_small_m wants bfloat16 matrices")
+    m, k = x.shape
+    rows = w.shape[0]
+    if w.shape[1] != k or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("gemm_small_m: x [m, k] and w [n, k] with contiguous rows")
+    if m > SMALL_M_MAX_ROWS or k % 8 or x.stride(0) % 8 or w.stride(0) % 8:
+        raise KernelError(f"gemm_small_m takes up to {SMALL_M_MAX_ROWS} rows, k and row strides "
+                          f"multiples of 8 (m {m}, k {k})")
+    if mode == GEMM_SILU and rows % 2:
+        raise KernelError("gemm_small_m: a [gate | up] weight has an even number of rows")
+    n = rows // 2 if mode == GEMM_SILU else rows
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32 if mode == GEMM_F32 else torch.bfloat16,
+                          device=x.device)
+    fn = _fn("gemm_small_m", "tvb_gemm_small_m",
+             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
+              c_int, c_int, c_void_p])
+    _check(fn(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+              m, n, k, mode, 1 if pdl else 0, _stream()), "gemm_small_m")
+    return out

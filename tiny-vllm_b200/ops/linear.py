@@ -27,3 +27,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype | No
     from . import gemm
 
     return gemm.linear_bf16(x, weight, out_dtype=out_dtype, out=out)
+
+
+def linear_silu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
+    """round(round(silu(x . gate^T)) * (x . up^T)) for a packed [gate | up] weight, [m, inter]."""
+    if not x.is_cuda:
+        raise kernels.KernelError("linear_silu runs on CUDA tensors only; there is no CPU path")
+    if x.dtype == torch.float32:
+        return kernels.silu_mul(kernels.gemm_nt_simt(x, gate_up_weight))
+    from . import gemm
+
+    return gemm.linear_silu_bf16(x, gate_up_weight)

@@ -11,7 +11,8 @@ are parameters; the position encoding is a part of its own.
 
 from __future__ import annotations
 
-from ..ops import kernels, linear
+from ..ops import attention as attention_ops
+from ..ops import linear
 from .base import BuildContext, KVNeed, ParamSpec, Part
 from .registry import register_part
 
@@ -64,18 +65,7 @@ class GQAAttention(Part):
     # ---------------------------------------------------------------- running
     def forward(self, x, ctx, run: int):
         qkv = linear(x, self.qkv_weight)
-        keys, values = ctx.storage.kv_of(run)
-        group = ctx.storage.group_of(run)
-        cos = sin = None
-        if self.position is not None:
-            cos, sin = self.position.cos, self.position.sin
-        kernels.qk_norm_rope_store(
-            qkv, num_q=self.num_heads, num_kv=self.num_kv_heads, head_dim=self.head_dim,
-            positions=ctx.positions, q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
-            eps=self.qk_norm_eps or 0.0, cos=cos, sin=sin,
-            slots=ctx.slots[group] if ctx.writes_cache(run) else None,
-            key_cache=keys, value_cache=values)
-        attended = ctx.attend(self, qkv, keys, values, group)
+        attended = attention_ops.mixer_attention(ctx, self, qkv, run)
         return linear(attended, self.o_weight)
 
 

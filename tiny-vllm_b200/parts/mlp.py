@@ -6,7 +6,7 @@ gate and up are one packed projection [gate | up]
 
 from __future__ import annotations
 
-from ..ops import kernels, linear
+from ..ops import linear, linear_silu
 from .base import BuildContext, ParamSpec, Part
 from .registry import register_part
 
@@ -31,7 +31,7 @@ class SwiGLU(Part):
         ]
 
     def forward(self, x, ctx):
-        return linear(kernels.silu_mul(linear(x, self.gate_up_weight)), self.down_weight)
+        return linear(linear_silu(x, self.gate_up_weight), self.down_weight)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
