@@ -361,12 +361,12 @@ def test_attention_prefill_window_edge_and_far_key():
 
 
 @pytest.mark.parametrize("window", [None, 150])
-@pytest.mark.parametrize("shape", [(4, 2, 64, 16, 128), (8, 2, 128, 16, 128), (2, 2, 128, 7, 192),
-                                   (8, 1, 256, 32, 256), (16, 8, 128, 16, 512)])
+@pytest.mark.parametrize("shape", [(4, 2, 64, 16, 8), (8, 2, 128, 16, 4), (2, 2, 128, 7, 1),
+                                   (8, 1, 256, 32, 5), (16, 8, 128, 16, 8)])
 def test_attention_decode_fused(shape, window):
     """Raw projection in, attention out: against q/k norm + rotation + attention of the plain
     functions, with the new key and value checked in the cache."""
-    nq, nkv, d, page, split_keys = shape
+    nq, nkv, d, page, splits = shape
     dtype = torch.bfloat16
     lengths = [1, 2, 63, 64, 65, 300, 511, 1000]
     case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=lengths, queries=[1] * len(lengths),
@@ -381,13 +381,11 @@ def test_attention_decode_fused(shape, window):
     slots = torch.tensor([int(case["tables"][r, int(p) // page]) * page + int(p) % page
                           for r, p in enumerate(positions)], dtype=torch.int32)
     kc, vc = case["kc"].to(DEV).clone(), case["vc"].to(DEV).clone()
-    splits = -(-1024 // split_keys)
     got = k().attention_decode(
         qkv.to(DEV), num_q=nq, num_kv=nkv, head_dim=d, positions=positions.to(DEV),
         token_row=case["token_row"].to(DEV), slots=slots.to(DEV), q_weight=qw.to(DEV), k_weight=kw.to(DEV),
         eps=1e-6, cos=cos.to(DEV), sin=sin.to(DEV), key_cache=kc, value_cache=vc,
-        block_tables=case["tables"].to(DEV), window=window, scale=d ** -0.5, split_keys=split_keys,
-        splits=splits).view(requests, nq, d)
+        block_tables=case["tables"].to(DEV), window=window, scale=d ** -0.5, splits=splits).view(requests, nq, d)
     q = qkv[:, :nq * d].float().view(requests, nq, d)
     kn = qkv[:, nq * d:(nq + nkv) * d].float().view(requests, nkv, d)
     vn = qkv[:, (nq + nkv) * d:].float().view(requests, nkv, d)
@@ -415,7 +413,7 @@ def test_attention_decode_padding_and_unsupported():
         k().attention_decode(torch.zeros(1, 4 * 48, dtype=torch.bfloat16, device=DEV), num_q=2, num_kv=1,
                              head_dim=48, positions=None, token_row=None, slots=None, q_weight=None,
                              k_weight=None, eps=0.0, cos=None, sin=None, key_cache=None, value_cache=None,
-                             block_tables=None, window=None, scale=1.0, split_keys=64, splits=1)
+                             block_tables=None, window=None, scale=1.0, splits=1)
 
 
 @pytest.mark.parametrize("shape", [(1, 64, 128), (8, 1024, 4096), (8, 3072, 1024), (5, 1000, 136),

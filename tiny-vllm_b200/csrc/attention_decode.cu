@@ -11,11 +11,11 @@
 // up to 8 CTAs whose partial (max, sum, output) are merged through distributed
 // shared memory: no scratch in global memory and no second kernel.
 //
-// Keys of a split are walked in tiles of 64 (16 per warp); LPK = head_dim / 8 lanes
-// share a key, each lane holding 8 dimensions (one 16-byte load).  Scores, softmax
-// and output sums are float32.  Splits start at multiples of `split_keys`, which
-// the host fixes from the context limit, so a request's result does not depend on
-// the batch it is in.
+// LPK = head_dim / 8 lanes share a key, each lane holding 8 dimensions (one 16-byte
+// copy).  Every warp walks its keys through a ring of cp.async stages of its own in
+// shared memory, so that the loads of the next keys fly while these are used.  Scores,
+// softmax and output sums are float32.  The size of a split follows from the request's
+// own position (and window) alone, so its result does not depend on the batch it is in.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -23,7 +23,8 @@
 namespace cg = cooperative_groups;
 
 #define DEC_WARPS 4
-#define DEC_UNROLL 8
+#define DEC_UNROLL 4        // key rows a warp loads per stage and matrix
+#define DEC_STAGES 3        // stages of each warp's ring of keys and values in shared memory
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
@@ -43,6 +44,7 @@ struct DecodeShared {
     float part_o[HPB][HEAD_DIM];       // this CTA's partial, read by rank 0 of the cluster
     float part_m[HPB];
     float part_l[HPB];
+    uint4 ring[DEC_WARPS][DEC_STAGES][2][DEC_UNROLL][32];   // per warp: stages of (keys, values), 16 B a lane
 };
 
 // RMSNorm + half-split rotation of one head by one warp; result rounded to bfloat16, as float.
@@ -101,7 +103,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
                         const int* __restrict__ slots, bf16* __restrict__ key_cache,
                         bf16* __restrict__ value_cache, const int* __restrict__ block_tables,
                         int table_stride, int page_size, bf16* __restrict__ out, int num_q, int num_kv,
-                        int window, float scale, int split_keys, int write_cache) {
+                        int window, float scale, int write_cache) {
     constexpr int LPK = HEAD_DIM / 8;          // lanes that share one key
     constexpr int KPI = 32 / LPK;              // keys per warp instruction
     constexpr int WARP_KEYS = KPI * DEC_UNROLL;
@@ -149,8 +151,12 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
     }
     __syncthreads();
 
+    // ---- the keys [lo, position] are cut into `splits` pieces of a size that depends on this
+    // request alone; piece `split` is this CTA's
     const int lo = window > 0 ? max(0, position - window + 1) : 0;
-    const int own_split = position / split_keys;          // the split that holds the new token
+    const int range_first = lo - lo % 64;
+    const int split_keys = ((position - range_first + splits) / splits + 63) / 64 * 64;
+    const int own_split = (position - range_first) / split_keys;     // holds the new token
     if (split == own_split && write_cache && (blockIdx.y % blocks_per_kv) == 0) {
         const int slot = slots[request];
         if (slot >= 0) {
@@ -163,9 +169,10 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
         }
     }
 
-    // ---- keys of this split that are already in the cache: [first, last]
-    const int first = max(lo, split * split_keys);
-    const int last = min(position - 1, split * split_keys + split_keys - 1);
+    // keys of this piece that are already in the cache: [first, last]
+    const int base = range_first + split * split_keys;
+    const int first = max(lo, base);
+    const int last = min(position - 1, base + split_keys - 1);
     const int sub = lane % LPK;                 // which 8 dimensions of a key this lane holds
     const int key_in_instr = lane / LPK;
     float q_reg[HPB][8];
@@ -187,45 +194,61 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
     const bf16* k_base = key_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
     const bf16* v_base = value_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
 
-    for (int tile = first - first % TILE_KEYS; tile <= last; tile += TILE_KEYS) {
-        const int warp_first = tile + warp * WARP_KEYS;
-        if (warp_first > last || warp_first + WARP_KEYS <= first) continue;
-        // slots of this warp's keys: lane i < WARP_KEYS looks up key warp_first + i
-        int my_slot = 0;
+    // The piece is walked in sub-tiles of WARP_KEYS keys; warp w takes sub-tiles w, w + 4, ...
+    // and keeps DEC_STAGES - 1 of them in flight in its own ring (cp.async, one group a stage).
+    const int sub_tiles = last >= first ? (last - base) / WARP_KEYS + 1 : 0;
+    int first_tile = max(0, (first - base) / WARP_KEYS);
+    first_tile += (warp - first_tile % DEC_WARPS + DEC_WARPS) % DEC_WARPS;
+    const int mine = first_tile < sub_tiles ? (sub_tiles - 1 - first_tile) / DEC_WARPS + 1 : 0;
+
+    auto issue = [&](int i) {                   // the i-th sub-tile of this warp into stage i % DEC_STAGES
+        const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
+        int my_slot = -1;
         {
-            const int key = warp_first + lane;
-            if (lane < WARP_KEYS && key >= first && key <= last)
-                my_slot = table[key / page_size] * page_size + key % page_size;
+            const int key = key0 + lane;
+            if (lane < WARP_KEYS && key >= first && key <= last) {
+                const int page = table[key / page_size];
+                if (page >= 0) my_slot = page * page_size + key % page_size;
+            }
         }
-        uint4 raw[DEC_UNROLL];
-        bool valid[DEC_UNROLL];
-        int slot_of[DEC_UNROLL];
+        uint4(*stage)[DEC_UNROLL][32] = sh.ring[warp][i % DEC_STAGES];
 #pragma unroll
         for (int u = 0; u < DEC_UNROLL; ++u) {
-            const int index = u * KPI + key_in_instr;
-            const int key = warp_first + index;
-            valid[u] = key >= first && key <= last;
-            slot_of[u] = __shfl_sync(0xffffffffu, my_slot, index);
-            raw[u] = *reinterpret_cast<const uint4*>(k_base + (int64_t)slot_of[u] * row_stride);
+            const int slot = __shfl_sync(0xffffffffu, my_slot, u * KPI + key_in_instr);
+            const int64_t offset = (int64_t)max(slot, 0) * row_stride;
+            cp_async_16(&stage[0][u][lane], k_base + offset, slot >= 0);
+            cp_async_16(&stage[1][u][lane], v_base + offset, slot >= 0);
         }
+    };
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; ++i) {
+        if (i < mine) issue(i);
+        cp_async_commit();
+    }
+    for (int i = 0; i < mine; ++i) {
+        if (i + DEC_STAGES - 1 < mine) issue(i + DEC_STAGES - 1);
+        cp_async_commit();
+        cp_async_wait<DEC_STAGES - 1>();        // sub-tile i has landed (a lane reads only what it copied)
+        const uint4(*stage)[DEC_UNROLL][32] = sh.ring[warp][i % DEC_STAGES];
+        const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
+        bool valid[DEC_UNROLL];
         float score[HPB][DEC_UNROLL];
 #pragma unroll
         for (int u = 0; u < DEC_UNROLL; ++u) {
+            const int key = key0 + u * KPI + key_in_instr;
+            valid[u] = key >= first && key <= last;
             float kf[8];
-            unpack8(raw[u], kf);
+            unpack8(stage[0][u][lane], kf);
 #pragma unroll
             for (int h = 0; h < HPB; ++h) {
                 float dot = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) dot = __fmaf_rn(q_reg[h][i], kf[i], dot);
+                for (int j = 0; j < 8; ++j) dot = __fmaf_rn(q_reg[h][j], kf[j], dot);
 #pragma unroll
                 for (int delta = LPK / 2; delta > 0; delta >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, delta);
                 score[h][u] = valid[u] ? __fmul_rn(dot, scale) : -INFINITY;
             }
         }
-#pragma unroll
-        for (int u = 0; u < DEC_UNROLL; ++u)      // values: issue the loads before the softmax arithmetic
-            raw[u] = *reinterpret_cast<const uint4*>(v_base + (int64_t)slot_of[u] * row_stride);
         float prob[HPB][DEC_UNROLL];
 #pragma unroll
         for (int h = 0; h < HPB; ++h) {
@@ -235,7 +258,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
 #pragma unroll
             for (int delta = LPK; delta < 32; delta <<= 1)
                 tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, delta));
-            const float new_max = fmaxf(m_run[h], tile_max);      // finite: the tile has a valid key
+            const float new_max = fmaxf(m_run[h], tile_max);      // finite: the sub-tile has a valid key
             const float rescale = m_run[h] == -INFINITY ? 0.0f : __expf(m_run[h] - new_max);
             m_run[h] = new_max;
             float sum = 0.0f;
@@ -246,20 +269,16 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
             }
             l_run[h] = l_run[h] * rescale + sum;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o_run[h][i] *= rescale;
+            for (int j = 0; j < 8; ++j) o_run[h][j] *= rescale;
         }
 #pragma unroll
         for (int u = 0; u < DEC_UNROLL; ++u) {
             float vf[8];
-            unpack8(raw[u], vf);
-            if (!valid[u]) {                      // whatever lies in a foreign slot must not reach the sum
-#pragma unroll
-                for (int i = 0; i < 8; ++i) vf[i] = 0.0f;
-            }
+            unpack8(stage[1][u][lane], vf);        // zero where there is no key
 #pragma unroll
             for (int h = 0; h < HPB; ++h)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o_run[h][i] = __fmaf_rn(prob[h][u], vf[i], o_run[h][i]);
+                for (int j = 0; j < 8; ++j) o_run[h][j] = __fmaf_rn(prob[h][u], vf[j], o_run[h][j]);
         }
     }
 
@@ -336,7 +355,7 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
                          void* value_cache, const int* block_tables, int table_stride, int page_size,
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
-                         int split_keys, int splits, int write_cache, cudaStream_t stream) {
+                         int splits, int write_cache, cudaStream_t stream) {
     auto kernel = decode_attention_kernel<HEAD_DIM, HPB, W>;
     const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
@@ -356,7 +375,7 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
     e = cudaLaunchKernelEx(&config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
                            cos_table, sin_table, table_positions, positions, token_row, slots,
                            (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
-                           (bf16*)out, num_q, num_kv, window, scale, split_keys, write_cache);
+                           (bf16*)out, num_q, num_kv, window, scale, write_cache);
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
@@ -371,16 +390,16 @@ extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv
 
 // qkv: [requests, (num_q + 2 num_kv) * head_dim] bfloat16, the raw projection of one token per
 // request.  weight_dtype: TVB_BF16 or TVB_F32 (norm weights; null pointers skip the norm).
-// splits = ceil(context limit / split_keys) <= 8 is the cluster size.
+// splits (1..8) is the cluster size: the number of pieces every request's keys are cut into.
 extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                                     const float* cos_table, const float* sin_table, int table_positions,
                                     const int* positions, const int* token_row, const int* slots,
                                     void* key_cache, void* value_cache, const int* block_tables,
                                     int table_stride, int page_size, void* out, int requests, int num_q,
-                                    int num_kv, int head_dim, int window, float scale, int split_keys,
+                                    int num_kv, int head_dim, int window, float scale,
                                     int splits, int write_cache, int weight_dtype, void* stream) {
     if (requests <= 0) return 0;
-    if (!tvb_attention_decode_supports(head_dim, num_q, num_kv, splits) || split_keys <= 0 ||
+    if (!tvb_attention_decode_supports(head_dim, num_q, num_kv, splits) ||
         page_size <= 0 || requests > 65535)
         return TVB_BAD_ARGUMENT;
     const int group = num_q / num_kv;
@@ -388,7 +407,7 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
     cudaStream_t s = (cudaStream_t)stream;
 #define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
                     token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
-                    requests, num_q, num_kv, window, scale, split_keys, splits, write_cache, s
+                    requests, num_q, num_kv, window, scale, splits, write_cache, s
 #define DECODE_BY_HPB(D, WT)                                            \
     do {                                                                \
         if (hpb == 1) return launch_decode<D, 1, WT>(DECODE_ARGS);      \

@@ -54,6 +54,20 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return warp_sum(total);
 }
 
+// ---- asynchronous 16-byte copies from global to shared memory
+__device__ __forceinline__ uint32_t smem_address(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+// With valid == false nothing is read and the 16 destination bytes become zero.
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_address(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
 static inline int tvb_last_error() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;

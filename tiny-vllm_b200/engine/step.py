@@ -63,8 +63,7 @@ class StepContext:
     split_chunks: int                    # 0: walk the keys per row; n: spread n chunks over the grid
     workspace_of: object = None          # callable(floats) -> float32 scratch tensor
     decode_only: bool = False            # every entry is a single token
-    decode_split_keys: int = 0           # keys per split of the fused decode attention
-    decode_splits: int = 0               # its number of splits (0: not used)
+    decode_splits: int = 0               # pieces the fused decode attention cuts a context into
     tile_row: torch.Tensor | None = None     # tiles of consecutive query tokens for the tile kernel:
     tile_first: torch.Tensor | None = None   # request row, first flat token and token count of each
     tile_count: torch.Tensor | None = None
@@ -102,7 +101,7 @@ class StepRunner:
         self._pinned: torch.Tensor | None = None
         self._pinned_free: torch.cuda.Event | None = None
         self._workspace: torch.Tensor | None = None
-        self.decode_split_keys, self.decode_splits = attention_ops.decode_split(self.max_model_len)
+        self.decode_splits = attention_ops.decode_splits(self.max_model_len)
 
     # ------------------------------------------------------------- sizing
     @staticmethod
@@ -218,7 +217,7 @@ class StepRunner:
             block_tables=[dview(7 + 2 * g).view(rows, blocks[g]) for g in range(groups)],
             cache_sources=self.cache_sources, max_position=max_position, split_chunks=split_chunks,
             workspace_of=self._workspace_of, decode_only=decode_only,
-            decode_split_keys=self.decode_split_keys, decode_splits=self.decode_splits,
+            decode_splits=self.decode_splits,
             tile_row=None if decode_only else dview(tiles_at),
             tile_first=None if decode_only else dview(tiles_at + 1),
             tile_count=None if decode_only else dview(tiles_at + 2),

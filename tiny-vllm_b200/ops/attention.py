@@ -35,12 +35,11 @@ def choose_split(tokens: int, max_position: int) -> int:
     return 0
 
 
-def decode_split(max_model_len: int) -> tuple[int, int]:
-    """(keys per split, number of splits) of the fused decode kernel: fixed by the context
-    limit alone, so that a request's sums do not depend on the batch it is in."""
-    keys = -(-max_model_len // DECODE_MAX_SPLITS)
-    keys = -(-keys // DECODE_SPLIT_GRAIN) * DECODE_SPLIT_GRAIN
-    return keys, -(-max_model_len // keys)
+def decode_splits(max_model_len: int) -> int:
+    """Cluster size of the fused decode kernel: into how many pieces a request's keys are cut.
+    The size of a piece follows from the request's own position inside the kernel, so that
+    its sums do not depend on the batch it is in."""
+    return max(1, min(DECODE_MAX_SPLITS, -(-max_model_len // DECODE_SPLIT_GRAIN)))
 
 
 def prefill_tiles(counts) -> tuple[list[int], list[int], list[int]]:
@@ -76,8 +75,7 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
             qkv, **heads, positions=ctx.positions, token_row=ctx.token_row, slots=ctx.slots[group],
             q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0,
             cos=cos, sin=sin, key_cache=keys, value_cache=values, block_tables=ctx.block_tables[group],
-            window=mixer.window, scale=mixer.scale, split_keys=ctx.decode_split_keys,
-            splits=ctx.decode_splits)
+            window=mixer.window, scale=mixer.scale, splits=ctx.decode_splits)
     kernels.qk_norm_rope_store(
         qkv, **heads, positions=ctx.positions, q_weight=mixer.q_norm_weight,
         k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0, cos=cos, sin=sin,

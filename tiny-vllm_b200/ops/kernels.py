@@ -317,12 +317,12 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
                      q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
                      cos: torch.Tensor | None, sin: torch.Tensor | None, key_cache: torch.Tensor,
                      value_cache: torch.Tensor, block_tables: torch.Tensor, window: int | None,
-                     scale: float, split_keys: int, splits: int,
+                     scale: float, splits: int,
                      out: torch.Tensor | None = None) -> torch.Tensor:
     """One new token per request, from the raw packed projection to the attention output:
     q/k norm and rotation, cache write (unless ``slots`` is None) and attention in one launch.
     Request i is row ``token_row[i]`` of ``block_tables`` (-1: padding) and stands at
-    ``positions[i]``.  The context is cut into ``splits`` pieces of ``split_keys`` keys."""
+    ``positions[i]``.  Every request's keys are cut into ``splits`` pieces, one per CTA of a cluster."""
     _need_cuda(qkv, positions, token_row, slots, q_weight, k_weight, cos, sin, key_cache, value_cache,
                block_tables)
     requests = qkv.shape[0]
@@ -339,8 +339,6 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     for t in (positions, token_row, block_tables) + ((slots,) if slots is not None else ()):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError("attention_decode: index tensors must be contiguous int32")
-    if splits * split_keys <= 0:
-        raise KernelError("attention_decode: splits and split_keys must be positive")
     weight_tag = BF16
     if q_weight is not None:
         if k_weight is None or q_weight.dtype != k_weight.dtype or q_weight.shape != (head_dim,):
@@ -354,12 +352,12 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     fn = _fn("attention_decode", "tvb_attention_decode",
              [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
-              c_int, c_float, c_int, c_int, c_int, c_int, c_void_p])
+              c_int, c_float, c_int, c_int, c_int, c_void_p])
     _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos), _ptr(sin), table_positions,
               positions.data_ptr(), token_row.data_ptr(), _ptr(slots), key_cache.data_ptr(),
               value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
               key_cache.shape[1], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
-              split_keys, splits, 1 if slots is not None else 0, weight_tag, _stream()),
+              splits, 1 if slots is not None else 0, weight_tag, _stream()),
            "attention_decode")
     return out
 
