@@ -445,3 +445,27 @@ def test_gemm_small_m_refuses():
     with pytest.raises(KernelError, match="multiples of 8"):
         k().gemm_small_m(torch.zeros(2, 60, dtype=torch.bfloat16, device=DEV),
                          torch.zeros(16, 60, dtype=torch.bfloat16, device=DEV))
+
+
+@pytest.mark.parametrize("weight_dtype", [torch.float32, torch.bfloat16], ids=["w32", "w16"])
+@pytest.mark.parametrize("shape", [(8, 1024, 512), (1, 256, 48), (19, 1000, 272), (32, 2048, 64)])
+def test_gemm_small_m_with_norm_prologue(shape, weight_dtype):
+    m, kk, n = shape
+    torch.manual_seed(m + n)
+    h, res = (torch.randn(m, kk) * 2).bfloat16(), torch.randn(m, kk).bfloat16()
+    w = (torch.randn(n, kk) * 0.05).bfloat16()
+    nw = (1 + 0.1 * torch.randn(kk)).to(weight_dtype)
+    x, stream = plain.add_rms_norm(h.float(), res.float(), nw.float(), 1e-5, torch.bfloat16)
+    got, new_stream = k().gemm_small_m(h.to(DEV), w.to(DEV), 1, norm_weight=nw.to(DEV),
+                                       residual=res.to(DEV), eps=1e-5)
+    assert torch.equal(new_stream.float().cpu(), stream)
+    close(got, x @ w.float().T, torch.bfloat16, bf16=6e-3)
+    # without a residual: plain norm, no new stream
+    got, none = k().gemm_small_m(h.to(DEV), w.to(DEV), 0, norm_weight=nw.to(DEV), eps=1e-5)
+    assert none is None
+    close(got, plain.rms_norm(h.float(), nw.float(), 1e-5, torch.bfloat16) @ w.float().T,
+          torch.bfloat16, bf16=8e-3)
+    if n % 2 == 0:
+        act, _ = k().gemm_small_m(h.to(DEV), w.to(DEV), 2, norm_weight=nw.to(DEV),
+                                  residual=res.to(DEV), eps=1e-5)
+        close(act, plain.swiglu(x @ w.float().T, torch.bfloat16), torch.bfloat16, bf16=1.2e-2)

@@ -49,7 +49,7 @@ struct DecodeShared {
 
 // RMSNorm + half-split rotation of one head by one warp; result rounded to bfloat16, as float.
 template <int HEAD_DIM, typename W>
-__device__ __forceinline__ void norm_rotate_head(const bf16* __restrict__ src, const W* __restrict__ weight,
+__device__ __forceinline__ void norm_rotate_head(const volatile bf16* src, const W* __restrict__ weight,
                                                  float eps, const float* __restrict__ cos_row,
                                                  const float* __restrict__ sin_row, float* __restrict__ dst,
                                                  int lane) {
@@ -62,8 +62,8 @@ __device__ __forceinline__ void norm_rotate_head(const bf16* __restrict__ src, c
         const int j = lane + 32 * i;
         a[i] = b[i] = 0.0f;
         if (j < HALF) {
-            a[i] = __bfloat162float(src[j]);
-            b[i] = __bfloat162float(src[j + HALF]);
+            a[i] = bf16_bits_to_float(reinterpret_cast<const volatile unsigned short*>(src)[j]);
+            b[i] = bf16_bits_to_float(reinterpret_cast<const volatile unsigned short*>(src)[j + HALF]);
             squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(a[i], a[i]), __fmul_rn(b[i], b[i])));
         }
     }
@@ -96,7 +96,7 @@ __device__ __forceinline__ void norm_rotate_head(const bf16* __restrict__ src, c
 
 template <int HEAD_DIM, int HPB, typename W>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_weight,
+decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_table,
                         const float* __restrict__ sin_table, int table_positions,
                         const int* __restrict__ positions, const int* __restrict__ token_row,
@@ -131,6 +131,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
     }
 
     // ---- the new token: q heads of this CTA, and k, v of its kv head
+    pdl_wait();                                 // the projection comes from the kernel before this one
     {
         const bf16* token = qkv + (int64_t)request * heads * HEAD_DIM;
         const int table_row = min(position, table_positions - 1);
@@ -145,7 +146,8 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
                                               cos_row, sin_row, sh.k_new, lane);
             } else {
                 const bf16* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
-                for (int i = lane; i < HEAD_DIM; i += 32) sh.v_new[i] = __bfloat162float(v[i]);
+                for (int i = lane; i < HEAD_DIM; i += 32)
+                    sh.v_new[i] = bf16_bits_to_float(reinterpret_cast<const volatile unsigned short*>(v)[i]);
             }
         }
     }
@@ -282,6 +284,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const W* __restrict__ q_we
         }
     }
 
+    pdl_launch_dependents();
     // ---- lanes that hold the same dimensions for different keys, then the warps, in a fixed order
 #pragma unroll
     for (int h = 0; h < HPB; ++h) {
@@ -355,24 +358,14 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
                          void* value_cache, const int* block_tables, int table_stride, int page_size,
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
-                         int splits, int write_cache, cudaStream_t stream) {
+                         int splits, int write_cache, int pdl, cudaStream_t stream) {
     auto kernel = decode_attention_kernel<HEAD_DIM, HPB, W>;
     const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (e != cudaSuccess) return (int)e;
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(splits, num_kv * ((num_q / num_kv) / HPB), requests);
-    config.blockDim = dim3(DEC_WARPS * 32);
-    config.dynamicSmemBytes = shared;
-    config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeClusterDimension;
-    attribute[0].val.clusterDim.x = splits;
-    attribute[0].val.clusterDim.y = 1;
-    attribute[0].val.clusterDim.z = 1;
-    config.attrs = attribute;
-    config.numAttrs = 1;
-    e = cudaLaunchKernelEx(&config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
+    TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / HPB), requests), dim3(DEC_WARPS * 32), shared,
+                     stream, pdl, splits);
+    e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
                            cos_table, sin_table, table_positions, positions, token_row, slots,
                            (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
                            (bf16*)out, num_q, num_kv, window, scale, write_cache);
@@ -397,7 +390,7 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
                                     void* key_cache, void* value_cache, const int* block_tables,
                                     int table_stride, int page_size, void* out, int requests, int num_q,
                                     int num_kv, int head_dim, int window, float scale,
-                                    int splits, int write_cache, int weight_dtype, void* stream) {
+                                    int splits, int write_cache, int weight_dtype, int pdl, void* stream) {
     if (requests <= 0) return 0;
     if (!tvb_attention_decode_supports(head_dim, num_q, num_kv, splits) ||
         page_size <= 0 || requests > 65535)
@@ -407,7 +400,7 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
     cudaStream_t s = (cudaStream_t)stream;
 #define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
                     token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
-                    requests, num_q, num_kv, window, scale, splits, write_cache, s
+                    requests, num_q, num_kv, window, scale, splits, write_cache, pdl, s
 #define DECODE_BY_HPB(D, WT)                                            \
     do {                                                                \
         if (hpb == 1) return launch_decode<D, 1, WT>(DECODE_ARGS);      \

@@ -68,6 +68,72 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
+// ---- eight bfloat16 in one 16-byte word
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float* f) {
+    return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
+                      pack_bf16x2(f[6], f[7]));
+}
+
+// ---- programmatic dependent launch: a kernel launched with the attribute may start while the
+// kernel before it in the stream still runs.  It must call pdl_wait() before it reads what that
+// kernel wrote and before its own first write to global memory; pdl_launch_dependents() lets
+// the kernel after it start.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+// A kernel that runs under programmatic dependent launch must not read what its predecessor
+// writes through pointers the compiler may treat as read-only for the kernel's whole life
+// (const __restrict__ turns loads into ld.global.nc, which may be hoisted above the wait or be
+// served from a stale read-only cache).  Such inputs are plain pointers, read with these.
+__device__ __forceinline__ float bf16_bits_to_float(unsigned short bits) {
+    return __uint_as_float((uint32_t)bits << 16);
+}
+__device__ __forceinline__ uint4 ld_global_16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Launch configuration with the optional attributes: cluster size along x, programmatic
+// stream serialisation.
+struct TvbLaunch {
+    cudaLaunchConfig_t config;
+    cudaLaunchAttribute attributes[2];
+    TvbLaunch(dim3 grid, dim3 block, size_t shared, cudaStream_t stream, int pdl, int cluster_x = 0) {
+        config = cudaLaunchConfig_t{};
+        config.gridDim = grid;
+        config.blockDim = block;
+        config.dynamicSmemBytes = shared;
+        config.stream = stream;
+        int count = 0;
+        if (cluster_x > 0) {
+            attributes[count].id = cudaLaunchAttributeClusterDimension;
+            attributes[count].val.clusterDim.x = cluster_x;
+            attributes[count].val.clusterDim.y = 1;
+            attributes[count].val.clusterDim.z = 1;
+            ++count;
+        }
+        if (pdl) {
+            attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attributes[count].val.programmaticStreamSerializationAllowed = 1;
+            ++count;
+        }
+        config.attrs = attributes;
+        config.numAttrs = count;
+    }
+};
+
 static inline int tvb_last_error() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;

@@ -10,14 +10,17 @@
 // in both operands, which a dot product does not notice, so the 16-byte loads feed two
 // instructions without any shuffle.
 //
-// Work is cut as (N / 16 row tiles) x (k blocks dealt round-robin to the 4 warps of the KS CTAs
+// Work is cut as (N / 16 row tiles) x (k blocks dealt round-robin to the 4 warps of the CTAs
 // of a thread-block cluster).  Warps, then CTAs (through distributed shared memory, in rank
 // order) add their partial tiles, so the sum order is fixed and nothing is staged in global
 // memory.  Loads of W are issued before the wait on the previous kernel of the stream
 // (programmatic dependent launch), since weights do not depend on it.
 //
-// Epilogues: bfloat16 or float32 result, or SiLU(gate) * up for a packed [gate | up] weight
-// (tinyvllm/kernels/pointwise.cu:274-285) so that the activation never goes to memory.
+// Prologue (optional): x = RMSNorm(h + residual) computed by every CTA for itself into
+// shared memory while its weights are in flight (tinyvllm/kernels/pointwise.cu:153-211);
+// the first CTA also stores the new residual stream.  Epilogues: bfloat16 or float32
+// result, or SiLU(gate) * up for a packed [gate | up] weight (:274-285), so that neither
+// the normalised input nor the activation goes through memory.
 // Stands where the reference calls F.linear (tinyvllm/layers.py:84-85).
 #include <cooperative_groups.h>
 
@@ -27,6 +30,7 @@ namespace cg = cooperative_groups;
 
 #define SM_WARPS 4
 #define SM_BATCH 4            // k blocks a warp has in flight
+#define SM_PAD 32             // bfloat16 of padding per row of x in shared memory (no bank conflicts)
 
 #define MODE_BF16 0
 #define MODE_F32 1
@@ -43,15 +47,24 @@ __device__ __forceinline__ uint4 load_16(const bf16* p, bool ok) {
     return ok ? *reinterpret_cast<const uint4*>(p) : make_uint4(0u, 0u, 0u, 0u);
 }
 
-// NT: number of 8-row groups of x (M <= 8 NT).  SETS: 1, or 2 for the gate and up rows.
-template <int NT, int MODE>
+struct NormArgs {
+    const bf16* residual;       // null: x = RMSNorm(h), the stream is h itself (written by an earlier kernel)
+    const void* weight;         // [k], bfloat16 or float32
+    bf16* residual_out;         // null: not stored
+    float eps;
+};
+
+// NT: number of 8-row groups of x (M <= 8 NT).  NORM: 0 none, 1 bfloat16 weight, 2 float32 weight.
+template <int NT, int MODE, int NORM>
 __global__ void __launch_bounds__(SM_WARPS * 32)
-gemm_small_m_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restrict__ w, int64_t ldw,
-                    void* __restrict__ out, int64_t ldo, int m, int n, int k, int up_offset) {
+gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int64_t ldw,
+                    void* __restrict__ out, int64_t ldo, int m, int n, int k, int up_offset, NormArgs norm) {
     constexpr int SETS = MODE == MODE_SILU ? 2 : 1;
     constexpr int MP = 8 * NT;
     __shared__ float warp_part[SM_WARPS][SETS][16][MP];
     __shared__ float cta_part[SETS][16][MP];
+    extern __shared__ __align__(16) unsigned char dynamic_shared[];
+    bf16* x_s = reinterpret_cast<bf16*>(dynamic_shared);       // [MP][k + SM_PAD] when NORM
 
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = blockIdx.x, ranks = gridDim.x;
@@ -60,6 +73,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restr
     const int g = lane >> 2, t4 = lane & 3;
     const int k_blocks = (k + 31) / 32;
     const int stride = ranks * SM_WARPS;
+    const int x_row = k + SM_PAD;
 
     const bf16* w_lo[SETS];
     const bf16* w_hi[SETS];
@@ -80,8 +94,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restr
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.0f;
 
-    bool waited = false;
-    for (int kb0 = rank * SM_WARPS + warp; kb0 < k_blocks; kb0 += stride * SM_BATCH) {
+    bool ready = false;          // the previous kernel's output may be read (and the norm is done)
+    for (int kb0 = rank * SM_WARPS + warp; kb0 < k_blocks || !ready; kb0 += stride * SM_BATCH) {
         uint4 a_lo[SM_BATCH][SETS], a_hi[SM_BATCH][SETS];
 #pragma unroll
         for (int u = 0; u < SM_BATCH; ++u) {
@@ -93,9 +107,52 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restr
                 a_hi[u][s] = load_16(w_hi[s] + kb * 32, k_ok && hi_ok[s]);
             }
         }
-        if (!waited) {               // the weights are on their way; now the previous kernel's output
-            asm volatile("griddepcontrol.wait;\n" ::: "memory");
-            waited = true;
+        if (!ready) {                // the weights are on their way; now the previous kernel's output
+            pdl_wait();
+            if (NORM) {
+                // every CTA normalises all rows for itself: warp w takes rows w, w + 4, ...
+                for (int row = warp; row < MP; row += SM_WARPS) {
+                    bf16* dst = x_s + row * x_row;
+                    if (row >= m) {
+                        for (int i = lane * 8; i < k; i += 256) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0, 0, 0, 0);
+                        continue;
+                    }
+                    const bf16* h = x + (int64_t)row * ldx;
+                    const bf16* r = norm.residual ? norm.residual + (int64_t)row * k : nullptr;
+                    float squares = 0.0f;
+                    for (int i = lane * 8; i < k; i += 256) {
+                        float v[8], rv[8];
+                        unpack_bf16x8(ld_global_16(h + i), v);
+                        if (r) {
+                            unpack_bf16x8(ld_global_16(r + i), rv);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = round_to<bf16>(__fadd_rn(v[e], rv[e]));
+                        }
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) squares = __fadd_rn(squares, __fmul_rn(v[e], v[e]));
+                        const uint4 merged = pack_bf16x8(v);
+                        *reinterpret_cast<uint4*>(dst + i) = merged;      // the stream, normalised below
+                        if (norm.residual_out && rank == 0 && blockIdx.y == 0)
+                            *reinterpret_cast<uint4*>(norm.residual_out + (int64_t)row * k + i) = merged;
+                    }
+                    squares = warp_sum(squares);
+                    const float inverse_rms =
+                        __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(squares, 1.0f / (float)k), norm.eps)));
+                    for (int i = lane * 8; i < k; i += 256) {
+                        float v[8];
+                        unpack_bf16x8(*reinterpret_cast<const uint4*>(dst + i), v);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float weight = NORM == 2 ? reinterpret_cast<const float*>(norm.weight)[i + e]
+                                                           : __bfloat162float(reinterpret_cast<const bf16*>(norm.weight)[i + e]);
+                            v[e] = __fmul_rn(round_to<bf16>(__fmul_rn(v[e], inverse_rms)), weight);
+                        }
+                        *reinterpret_cast<uint4*>(dst + i) = pack_bf16x8(v);
+                    }
+                }
+                __syncthreads();
+            }
+            ready = true;
         }
 #pragma unroll
         for (int u = 0; u < SM_BATCH; ++u) {
@@ -104,7 +161,11 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restr
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int row = 8 * j + g;
-                const uint4 b = load_16(x + (int64_t)row * ldx + kb * 32 + 8 * t4, k_ok && row < m);
+                uint4 b;
+                if (NORM) b = k_ok ? *reinterpret_cast<const uint4*>(x_s + row * x_row + kb * 32 + 8 * t4)
+                                   : make_uint4(0u, 0u, 0u, 0u);
+                else b = k_ok && row < m ? ld_global_16(x + (int64_t)row * ldx + kb * 32 + 8 * t4)
+                                         : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
                 for (int s = 0; s < SETS; ++s) {
                     mma_16816(acc[s][j], a_lo[u][s].x, a_hi[u][s].x, a_lo[u][s].y, a_hi[u][s].y, b.x, b.y);
@@ -113,8 +174,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restr
             }
         }
     }
-    if (!waited) asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;\n" ::);
+    pdl_launch_dependents();
 
     // ---- warps of the CTA, then CTAs of the cluster, in a fixed order
 #pragma unroll
@@ -165,29 +225,21 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restr
     cluster.sync();
 }
 
-template <int NT, int MODE>
+template <int NT, int MODE, int NORM>
 static int launch_small_m(const void* x, long long ldx, const void* w, long long ldw, void* out,
                           long long ldo, int m, int n, int k, int up_offset, int ranks, int pdl,
-                          cudaStream_t stream) {
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(ranks, (n + 15) / 16);
-    config.blockDim = dim3(SM_WARPS * 32);
-    config.dynamicSmemBytes = 0;
-    config.stream = stream;
-    cudaLaunchAttribute attributes[2];
-    attributes[0].id = cudaLaunchAttributeClusterDimension;
-    attributes[0].val.clusterDim.x = ranks;
-    attributes[0].val.clusterDim.y = 1;
-    attributes[0].val.clusterDim.z = 1;
-    config.numAttrs = 1;
-    if (pdl) {
-        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attributes[1].val.programmaticStreamSerializationAllowed = 1;
-        config.numAttrs = 2;
+                          NormArgs norm, cudaStream_t stream) {
+    auto kernel = gemm_small_m_kernel<NT, MODE, NORM>;
+    size_t dynamic = 0;
+    if (NORM) {
+        dynamic = (size_t)8 * NT * (k + SM_PAD) * sizeof(bf16);
+        if (dynamic > 160 * 1024) return TVB_BAD_ARGUMENT;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dynamic);
+        if (e != cudaSuccess) return (int)e;
     }
-    config.attrs = attributes;
-    cudaError_t e = cudaLaunchKernelEx(&config, gemm_small_m_kernel<NT, MODE>, (const bf16*)x, (int64_t)ldx,
-                                       (const bf16*)w, (int64_t)ldw, out, (int64_t)ldo, m, n, k, up_offset);
+    TvbLaunch launch(dim3(ranks, (n + 15) / 16), dim3(SM_WARPS * 32), dynamic, stream, pdl, ranks);
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)x, (int64_t)ldx, (const bf16*)w,
+                                       (int64_t)ldw, out, (int64_t)ldo, m, n, k, up_offset, norm);
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
@@ -195,30 +247,47 @@ extern "C" int tvb_gemm_small_m_max_rows() { return 32; }
 
 // mode: 0 bfloat16 result [m, n]; 1 float32 result [m, n]; 2 SiLU(gate) * up, w = [gate (n rows) |
 // up (n rows)] and the result is [m, n].  k must be a multiple of 8 and rows 16-byte aligned.
-// pdl != 0 launches with programmatic stream serialisation (the kernel before it in the stream
-// must then be one that tolerates an early start of this one: this kernel only reads weights
-// before it waits).
+//
+// norm_weight != null: x is replaced by RMSNorm(x + residual) * norm_weight (residual may be null;
+// both are contiguous [m, k]); residual_out (may be null) receives the rounded sum.
+// norm_weight_dtype: TVB_BF16 or TVB_F32.
+//
+// pdl != 0 launches with programmatic stream serialisation: the kernel may start while the kernel
+// before it in the stream still runs; it reads nothing but weights before it waits for that kernel.
 extern "C" int tvb_gemm_small_m(const void* x, long long ldx, const void* w, long long ldw, void* out,
-                                long long ldo, int m, int n, int k, int mode, int pdl, void* stream) {
+                                long long ldo, int m, int n, int k, int mode, const void* residual,
+                                const void* norm_weight, void* residual_out, float eps,
+                                int norm_weight_dtype, int pdl, void* stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 32 || k <= 0 || k % 8 || ldx % 8 || ldw % 8 || mode < 0 || mode > 2 || n > 65535 * 16)
         return TVB_BAD_ARGUMENT;
+    if (norm_weight && ldx != k) return TVB_BAD_ARGUMENT;
     const int k_blocks = (k + 31) / 32;
-    // enough CTAs per row tile that every warp has about one batch of k blocks, at most 8 per cluster
-    // (a power of two)
+    // enough CTAs per row tile that every warp has about one batch of k blocks, at most 8 per
+    // cluster (a power of two)
     const int wanted = (k_blocks + SM_WARPS * SM_BATCH - 1) / (SM_WARPS * SM_BATCH);
     int ranks = 1;
     while (ranks < wanted && ranks < 8) ranks *= 2;
     const int up_offset = mode == MODE_SILU ? n : 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = (m + 7) / 8;
-#define SMALL_M(NT, MODE) launch_small_m<NT, MODE>(x, ldx, w, ldw, out, ldo, m, n, k, up_offset, ranks, pdl, s)
+    NormArgs norm = {(const bf16*)residual, norm_weight, (bf16*)residual_out, eps};
+    const int norm_kind = !norm_weight ? 0 : (norm_weight_dtype == TVB_F32 ? 2 : 1);
+    if (norm_weight && norm_weight_dtype != TVB_F32 && norm_weight_dtype != TVB_BF16) return TVB_BAD_ARGUMENT;
+#define SMALL_M(NT, MODE, NORM) \
+    launch_small_m<NT, MODE, NORM>(x, ldx, w, ldw, out, ldo, m, n, k, up_offset, ranks, pdl, norm, s)
+#define BY_NORM(NT, MODE)                                   \
+    do {                                                    \
+        if (norm_kind == 0) return SMALL_M(NT, MODE, 0);    \
+        if (norm_kind == 1) return SMALL_M(NT, MODE, 1);    \
+        return SMALL_M(NT, MODE, 2);                        \
+    } while (0)
 #define BY_NT(MODE)                                  \
     do {                                             \
-        if (nt == 1) return SMALL_M(1, MODE);        \
-        if (nt == 2) return SMALL_M(2, MODE);        \
-        if (nt == 3) return SMALL_M(3, MODE);        \
-        return SMALL_M(4, MODE);                     \
+        if (nt == 1) BY_NORM(1, MODE);               \
+        if (nt == 2) BY_NORM(2, MODE);               \
+        if (nt == 3) BY_NORM(3, MODE);               \
+        BY_NORM(4, MODE);                            \
     } while (0)
     if (mode == MODE_BF16) BY_NT(MODE_BF16);
     if (mode == MODE_F32) BY_NT(MODE_F32);

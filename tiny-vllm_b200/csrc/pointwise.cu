@@ -42,12 +42,15 @@ extern "C" int tvb_embed_rows(const void* table, const int* ids, void* out, int 
 // the rounded sum x + residual is normalised and, if `residual_out` is given,
 // stored as the new residual stream.
 template <typename T, typename W>
-__global__ void rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+__global__ void rms_norm_kernel(const T* x, const T* residual,   // written by the kernel before
+                                
                                 const W* __restrict__ weight, T* __restrict__ y,
                                 T* __restrict__ residual_out, const int* __restrict__ gather,
                                 int width, float eps) {
     extern __shared__ float row_values[];
     __shared__ float scratch[32];
+    pdl_wait();
+    pdl_launch_dependents();
     const int out_row = blockIdx.x;
     const int in_row = gather ? gather[out_row] : out_row;
     const T* xr = x + (int64_t)in_row * width;
@@ -73,7 +76,7 @@ __global__ void rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ r
 template <typename T, typename W>
 static int launch_rms_norm(const void* x, const void* residual, const void* weight, void* y,
                            void* residual_out, const int* gather, int rows, int width, float eps,
-                           cudaStream_t s) {
+                           int pdl, cudaStream_t s) {
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return TVB_BAD_ARGUMENT;
     auto kernel = rms_norm_kernel<T, W>;
@@ -82,24 +85,25 @@ static int launch_rms_norm(const void* x, const void* residual, const void* weig
         if (e != cudaSuccess) return (int)e;
     }
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : (width >= 128 ? 128 : 32));
-    kernel<<<rows, threads, smem, s>>>((const T*)x, (const T*)residual, (const W*)weight, (T*)y,
-                                       (T*)residual_out, gather, width, eps);
-    return tvb_last_error();
+    TvbLaunch launch(dim3(rows), dim3(threads), smem, s, pdl);
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, (const T*)x, (const T*)residual,
+                                       (const W*)weight, (T*)y, (T*)residual_out, gather, width, eps);
+    return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
 // weight_dtype may differ from dtype: a norm weight stored in 32-bit stays 32-bit.
 extern "C" int tvb_rms_norm(const void* x, const void* residual, const void* weight, void* y,
                             void* residual_out, const int* gather, int rows, int width, float eps,
-                            int dtype, int weight_dtype, void* stream) {
+                            int dtype, int weight_dtype, int pdl, void* stream) {
     if (rows <= 0) return 0;
     if (width <= 0) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == TVB_F32 && weight_dtype == TVB_F32)
-        return launch_rms_norm<float, float>(x, residual, weight, y, residual_out, gather, rows, width, eps, s);
+        return launch_rms_norm<float, float>(x, residual, weight, y, residual_out, gather, rows, width, eps, pdl, s);
     if (dtype == TVB_BF16 && weight_dtype == TVB_BF16)
-        return launch_rms_norm<bf16, bf16>(x, residual, weight, y, residual_out, gather, rows, width, eps, s);
+        return launch_rms_norm<bf16, bf16>(x, residual, weight, y, residual_out, gather, rows, width, eps, pdl, s);
     if (dtype == TVB_BF16 && weight_dtype == TVB_F32)
-        return launch_rms_norm<bf16, float>(x, residual, weight, y, residual_out, gather, rows, width, eps, s);
+        return launch_rms_norm<bf16, float>(x, residual, weight, y, residual_out, gather, rows, width, eps, pdl, s);
     return TVB_BAD_ARGUMENT;
 }
 

@@ -75,10 +75,11 @@ __device__ __forceinline__ void block_argmax(float& value, int& index, float* va
 
 template <typename T>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
+sample_rows_kernel(const T* logits, int64_t row_stride, int vocab,   // logits: from the kernel before
                    const int* __restrict__ packed, int capacity, int* __restrict__ tokens) {
     __shared__ float fscratch[32];
     __shared__ int iscratch[32];
+    pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const T* x = logits + (int64_t)row * row_stride;
 
@@ -180,17 +181,20 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
 // packed: int32 [7, capacity], field-major: temperature and top_p as float bits, top_k,
 // seed low/high word, draw-counter low/high word; row r reads column r.
 extern "C" int tvb_sample_rows(const void* logits, long long row_stride, int rows, int vocab,
-                               const int* packed, int capacity, int* tokens, int dtype, void* stream) {
+                               const int* packed, int capacity, int* tokens, int dtype, int pdl,
+                               void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || capacity < rows) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
+    TvbLaunch launch(dim3(rows), dim3(SAMPLE_THREADS), 0, s, pdl);
+    cudaError_t e;
     if (dtype == TVB_F32)
-        sample_rows_kernel<float><<<rows, SAMPLE_THREADS, 0, s>>>(
-            (const float*)logits, row_stride, vocab, packed, capacity, tokens);
+        e = cudaLaunchKernelEx(&launch.config, sample_rows_kernel<float>, (const float*)logits,
+                               (int64_t)row_stride, vocab, packed, capacity, tokens);
     else if (dtype == TVB_BF16)
-        sample_rows_kernel<bf16><<<rows, SAMPLE_THREADS, 0, s>>>(
-            (const bf16*)logits, row_stride, vocab, packed, capacity, tokens);
+        e = cudaLaunchKernelEx(&launch.config, sample_rows_kernel<bf16>, (const bf16*)logits,
+                               (int64_t)row_stride, vocab, packed, capacity, tokens);
     else
         return TVB_BAD_ARGUMENT;
-    return tvb_last_error();
+    return e == cudaSuccess ? tvb_last_error() : (int)e;
 }

@@ -12,7 +12,8 @@ import torch
 from . import kernels
 
 
-def _small(x: torch.Tensor, weight: torch.Tensor) -> bool:
+def small(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the weight-streaming kernel takes this product."""
     return (x.shape[0] <= kernels.SMALL_M_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
             and x.stride(0) % 8 == 0 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0)
 
@@ -23,7 +24,7 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype
         raise kernels.KernelError("linear_bf16 wants bfloat16 operands")
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise kernels.KernelError(f"linear_bf16 cannot produce {out_dtype}")
-    if _small(x, weight):
+    if small(x, weight):
         mode = kernels.GEMM_BF16 if out_dtype == torch.bfloat16 else kernels.GEMM_F32
         return kernels.gemm_small_m(x, weight, mode, out=out)
     if out_dtype == torch.bfloat16:
@@ -42,6 +43,6 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype
 
 def linear_silu_bf16(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
     """silu(x . gate^T) * (x . up^T) for a packed [gate | up] weight."""
-    if _small(x, gate_up_weight):
+    if small(x, gate_up_weight):
         return kernels.gemm_small_m(x, gate_up_weight, kernels.GEMM_SILU)
     return kernels.silu_mul(torch.nn.functional.linear(x, gate_up_weight))

@@ -9,6 +9,7 @@ library they raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -35,6 +36,18 @@ def _stream() -> int:
 
 
 _launches = 0
+
+# Programmatic dependent launch for the kernels that wait for their predecessor themselves
+# (griddepcontrol.wait): they may start, and fetch weights, while the kernel before them ends.
+# TINYVLLM_B200_PDL=0 turns it off; a comma-separated list (gemm,norm,attention,sample) keeps it
+# for those kernels only.
+_PDL_ALL = ("gemm", "norm", "attention", "sample")
+_setting = os.environ.get("TINYVLLM_B200_PDL", "1")
+PDL = frozenset() if _setting == "0" else frozenset(_PDL_ALL if _setting == "1" else _setting.split(","))
+
+
+def _pdl(kind: str) -> int:
+    return 1 if kind in PDL else 0
 
 
 def launch_count() -> int:
@@ -121,10 +134,10 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual: tor
         residual_out = None
     fn = _fn("pointwise", "tvb_rms_norm",
              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
-              c_int, c_int, c_void_p])
+              c_int, c_int, c_int, c_void_p])
     _check(fn(x.data_ptr(), _ptr(residual), weight.data_ptr(), out.data_ptr(), _ptr(residual_out),
-              _ptr(rows), count, width, eps, dtype_tag(x.dtype), dtype_tag(weight.dtype), _stream()),
-           "rms_norm")
+              _ptr(rows), count, width, eps, dtype_tag(x.dtype), dtype_tag(weight.dtype), _pdl("norm"),
+              _stream()), "rms_norm")
     if residual is not None and rows is None:
         return out, residual_out
     return out
@@ -300,9 +313,9 @@ def sample_rows(logits: torch.Tensor, packed: torch.Tensor, out: torch.Tensor | 
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     fn = _fn("sampling", "tvb_sample_rows",
-             [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
+             [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
     _check(fn(logits.data_ptr(), logits.stride(0), rows, vocab, packed.data_ptr(), packed.shape[1],
-              out.data_ptr(), dtype_tag(logits.dtype), _stream()), "sample_rows")
+              out.data_ptr(), dtype_tag(logits.dtype), _pdl("sample"), _stream()), "sample_rows")
     return out
 
 
@@ -352,12 +365,12 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     fn = _fn("attention_decode", "tvb_attention_decode",
              [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
-              c_int, c_float, c_int, c_int, c_int, c_void_p])
+              c_int, c_float, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos), _ptr(sin), table_positions,
               positions.data_ptr(), token_row.data_ptr(), _ptr(slots), key_cache.data_ptr(),
               value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
               key_cache.shape[1], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
-              splits, 1 if slots is not None else 0, weight_tag, _stream()),
+              splits, 1 if slots is not None else 0, weight_tag, _pdl("attention"), _stream()),
            "attention_decode")
     return out
 
@@ -415,11 +428,16 @@ GEMM_BF16, GEMM_F32, GEMM_SILU = 0, 1, 2
 
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
-                 out: torch.Tensor | None = None, pdl: bool = False) -> torch.Tensor:
+                 out: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
+                 residual: torch.Tensor | None = None, eps: float = 0.0, want_residual: bool = True):
     """x [m <= 32, k] . w [n, k]^T, bfloat16 operands.  mode GEMM_BF16 / GEMM_F32: result
     [m, n] in that dtype; GEMM_SILU: w is [gate | up] with 2 n rows and the result is
-    silu(x . gate^T) * (x . up^T), bfloat16 [m, n]."""
-    _need_cuda(x, w)
+    silu(x . gate^T) * (x . up^T), bfloat16 [m, n].
+
+    With ``norm_weight`` the product is taken of RMSNorm(x + residual) * norm_weight instead
+    of x (``residual`` may be None), and (result, rounded sum x + residual) is returned; the
+    sum is None without a residual or with ``want_residual=False``."""
+    _need_cuda(x, w, norm_weight, residual)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2:
         raise KernelError("gemm_small_m wants bfloat16 matrices")
     m, k = x.shape
@@ -432,12 +450,34 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
     if mode == GEMM_SILU and rows % 2:
         raise KernelError("gemm_small_m: a [gate | up] weight has an even number of rows")
     n = rows // 2 if mode == GEMM_SILU else rows
+    residual_out = None
+    weight_tag = BF16
+    if norm_weight is not None:
+        if norm_weight.shape != (k,) or not x.is_contiguous() or not gemm_small_m_takes_norm(m, k):
+            raise KernelError("gemm_small_m: the fused norm wants contiguous x, a weight [k] and "
+                              "rows that fit into shared memory")
+        if residual is not None:
+            if residual.shape != x.shape or residual.dtype != x.dtype or not residual.is_contiguous():
+                raise KernelError("gemm_small_m: residual must match x")
+            if want_residual:
+                residual_out = torch.empty_like(x)
+        weight_tag = dtype_tag(norm_weight.dtype)
+    elif residual is not None:
+        raise KernelError("gemm_small_m: a residual needs a norm weight")
     if out is None:
         out = torch.empty((m, n), dtype=torch.float32 if mode == GEMM_F32 else torch.bfloat16,
                           device=x.device)
     fn = _fn("gemm_small_m", "tvb_gemm_small_m",
              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
-              c_int, c_int, c_void_p])
+              c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p])
     _check(fn(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-              m, n, k, mode, 1 if pdl else 0, _stream()), "gemm_small_m")
+              m, n, k, mode, _ptr(residual), _ptr(norm_weight), _ptr(residual_out), eps, weight_tag,
+              _pdl("gemm"), _stream()), "gemm_small_m")
+    if norm_weight is not None:
+        return out, residual_out
     return out
+
+
+def gemm_small_m_takes_norm(m: int, k: int) -> bool:
+    """Whether the normalised rows [m rounded up to 8, k] fit into the kernel's shared memory."""
+    return m <= SMALL_M_MAX_ROWS and k % 8 == 0 and (-(-m // 8) * 8) * (k + 32) * 2 <= 160 * 1024

@@ -38,3 +38,26 @@ def linear_silu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
     from . import gemm
 
     return gemm.linear_silu_bf16(x, gate_up_weight)
+
+
+def linear_norm(hidden: torch.Tensor, residual: torch.Tensor | None, norm, weight: torch.Tensor, *,
+                silu: bool = False):
+    """(linear(norm(hidden + residual), weight), hidden + residual): a pre-norm and the
+    projection behind it as one operation.  ``norm`` is a norm part (``weight``, ``eps``,
+    ``forward``, ``add``).  Without a residual the stream is ``hidden`` itself.  ``silu``
+    applies SiLU(gate) * up to a packed [gate | up] weight.  Small bfloat16 batches run as
+    one kernel; everything else as the norm kernel and the product."""
+    from . import gemm
+
+    if (hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and hidden.is_contiguous()
+            and type(norm).__name__ == "RMSNorm" and gemm.small(hidden, weight)
+            and kernels.gemm_small_m_takes_norm(hidden.shape[0], hidden.shape[1])):
+        mode = kernels.GEMM_SILU if silu else kernels.GEMM_BF16
+        out, stream = kernels.gemm_small_m(hidden, weight, mode, norm_weight=norm.weight,
+                                           residual=residual, eps=norm.eps)
+        return out, (hidden if residual is None else stream)
+    if residual is None:
+        x, stream = norm.forward(hidden), hidden
+    else:
+        x, stream = norm.add(hidden, residual)
+    return (linear_silu(x, weight) if silu else linear(x, weight)), stream

@@ -12,7 +12,7 @@ are parameters; the position encoding is a part of its own.
 from __future__ import annotations
 
 from ..ops import attention as attention_ops
-from ..ops import linear
+from ..ops import linear, linear_norm
 from .base import BuildContext, KVNeed, ParamSpec, Part
 from .registry import register_part
 
@@ -67,6 +67,12 @@ class GQAAttention(Part):
         qkv = linear(x, self.qkv_weight)
         attended = attention_ops.mixer_attention(ctx, self, qkv, run)
         return linear(attended, self.o_weight)
+
+    def forward_normed(self, hidden, residual, norm, ctx, run: int):
+        """forward(norm(hidden + residual)) and the new residual stream."""
+        qkv, residual = linear_norm(hidden, residual, norm, self.qkv_weight)
+        attended = attention_ops.mixer_attention(ctx, self, qkv, run)
+        return linear(attended, self.o_weight), residual
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -24,12 +24,18 @@ class PreNormResidualBlock(Part):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
     def forward(self, hidden, residual, ctx, run: int):
-        if residual is None:
-            residual = hidden
-            x = self.mixer_norm.forward(hidden)
+        # a part that can take its norm into its first projection does so (forward_normed
+        # returns its output and the new residual stream); the others get a normalised input
+        if hasattr(self.mixer, "forward_normed"):
+            mixed, residual = self.mixer.forward_normed(hidden, residual, self.mixer_norm, ctx, run)
         else:
-            x, residual = self.mixer_norm.add(hidden, residual)
-        mixed = self.mixer.forward(x, ctx, run)
+            if residual is None:
+                residual, x = hidden, self.mixer_norm.forward(hidden)
+            else:
+                x, residual = self.mixer_norm.add(hidden, residual)
+            mixed = self.mixer.forward(x, ctx, run)
+        if hasattr(self.feed_forward, "forward_normed"):
+            return self.feed_forward.forward_normed(mixed, residual, self.feed_forward_norm, ctx)
         x, residual = self.feed_forward_norm.add(mixed, residual)
         return self.feed_forward.forward(x, ctx), residual
 

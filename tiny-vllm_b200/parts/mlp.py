@@ -6,7 +6,7 @@ gate and up are one packed projection [gate | up]
 
 from __future__ import annotations
 
-from ..ops import linear, linear_silu
+from ..ops import linear, linear_norm, linear_silu
 from .base import BuildContext, ParamSpec, Part
 from .registry import register_part
 
@@ -32,6 +32,11 @@ class SwiGLU(Part):
 
     def forward(self, x, ctx):
         return linear(linear_silu(x, self.gate_up_weight), self.down_weight)
+
+    def forward_normed(self, hidden, residual, norm, ctx):
+        """forward(norm(hidden + residual)) and the new residual stream."""
+        activated, residual = linear_norm(hidden, residual, norm, self.gate_up_weight, silu=True)
+        return linear(activated, self.down_weight), residual
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
