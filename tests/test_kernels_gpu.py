@@ -385,7 +385,8 @@ def test_attention_decode_fused(shape, window):
         qkv.to(DEV), num_q=nq, num_kv=nkv, head_dim=d, positions=positions.to(DEV),
         token_row=case["token_row"].to(DEV), slots=slots.to(DEV), q_weight=qw.to(DEV), k_weight=kw.to(DEV),
         eps=1e-6, cos=cos.to(DEV), sin=sin.to(DEV), key_cache=kc, value_cache=vc,
-        block_tables=case["tables"].to(DEV), window=window, scale=d ** -0.5, splits=splits).view(requests, nq, d)
+        block_tables=case["tables"].to(DEV), window=window, scale=d ** -0.5, splits=splits,
+        max_context=1024).view(requests, nq, d)
     q = qkv[:, :nq * d].float().view(requests, nq, d)
     kn = qkv[:, nq * d:(nq + nkv) * d].float().view(requests, nkv, d)
     vn = qkv[:, (nq + nkv) * d:].float().view(requests, nkv, d)
@@ -413,7 +414,7 @@ def test_attention_decode_padding_and_unsupported():
         k().attention_decode(torch.zeros(1, 4 * 48, dtype=torch.bfloat16, device=DEV), num_q=2, num_kv=1,
                              head_dim=48, positions=None, token_row=None, slots=None, q_weight=None,
                              k_weight=None, eps=0.0, cos=None, sin=None, key_cache=None, value_cache=None,
-                             block_tables=None, window=None, scale=1.0, splits=1)
+                             block_tables=None, window=None, scale=1.0, splits=1, max_context=64)
 
 
 @pytest.mark.parametrize("shape", [(1, 64, 128), (8, 1024, 4096), (8, 3072, 1024), (5, 1000, 136),

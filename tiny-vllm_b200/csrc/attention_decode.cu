@@ -8,14 +8,17 @@
 // reference kernel (one CTA per request and q head, no split over the context,
 // :586-590) a CTA serves HPB q heads that share one kv head, so keys and values
 // are read once per group, and the context is split over a thread-block cluster of
-// up to 8 CTAs whose partial (max, sum, output) are merged through distributed
-// shared memory: no scratch in global memory and no second kernel.
+// up to 8 CTAs.  Every CTA stores its partial (max, sum, output) into the shared
+// memory of the cluster's first CTA (distributed shared memory), which merges them
+// in rank order: no scratch in global memory and no second kernel.
 //
 // LPK = head_dim / 8 lanes share a key, each lane holding 8 dimensions (one 16-byte
 // copy).  Every warp walks its keys through a ring of cp.async stages of its own in
-// shared memory, so that the loads of the next keys fly while these are used.  Scores,
-// softmax and output sums are float32.  The size of a split follows from the request's
-// own position (and window) alone, so its result does not depend on the batch it is in.
+// shared memory; the cache slots of its keys are looked up once, up front, and the
+// first stage is in flight before the kernel waits for the projection (keys and
+// values already in the cache do not depend on it).  Scores, softmax and output sums
+// are float32.  The size of a split follows from the request's own position (and
+// window) alone, so its result does not depend on the batch it is in.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -24,32 +27,31 @@ namespace cg = cooperative_groups;
 
 #define DEC_WARPS 4
 #define DEC_UNROLL 4        // key rows a warp loads per stage and matrix
-#define DEC_STAGES 3        // stages of each warp's ring of keys and values in shared memory
-
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
-    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
-    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
-    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
-}
+#define DEC_STAGES 2        // stages of each warp's ring of keys and values in shared memory
+#define DEC_MAX_SPLITS 8
 
 template <int HEAD_DIM, int HPB>
 struct DecodeShared {
     float q[HPB][HEAD_DIM];            // normalised, rotated, rounded q heads
     float k_new[HEAD_DIM];             // the new key and value as stored (rounded)
     float v_new[HEAD_DIM];
+    float s_new[HPB];                  // score of the new key for each head
     float warp_o[DEC_WARPS][HPB][HEAD_DIM];
     float warp_m[DEC_WARPS][HPB];
     float warp_l[DEC_WARPS][HPB];
-    float part_o[HPB][HEAD_DIM];       // this CTA's partial, read by rank 0 of the cluster
-    float part_m[HPB];
-    float part_l[HPB];
+    // partials of every CTA of the cluster; only the first CTA's copy is used, the others
+    // write theirs into it
+    float part_o[DEC_MAX_SPLITS][HPB][HEAD_DIM];
+    float part_m[DEC_MAX_SPLITS][HPB];
+    float part_l[DEC_MAX_SPLITS][HPB];
     uint4 ring[DEC_WARPS][DEC_STAGES][2][DEC_UNROLL][32];   // per warp: stages of (keys, values), 16 B a lane
+    // int slot[DEC_WARPS][warp_slot_capacity] follows
 };
 
 // RMSNorm + half-split rotation of one head by one warp; result rounded to bfloat16, as float.
+// `src` was written by the kernel before this one: read through volatile loads.
 template <int HEAD_DIM, typename W>
-__device__ __forceinline__ void norm_rotate_head(const volatile bf16* src, const W* __restrict__ weight,
+__device__ __forceinline__ void norm_rotate_head(const volatile unsigned short* src, const W* __restrict__ weight,
                                                  float eps, const float* __restrict__ cos_row,
                                                  const float* __restrict__ sin_row, float* __restrict__ dst,
                                                  int lane) {
@@ -62,8 +64,8 @@ __device__ __forceinline__ void norm_rotate_head(const volatile bf16* src, const
         const int j = lane + 32 * i;
         a[i] = b[i] = 0.0f;
         if (j < HALF) {
-            a[i] = bf16_bits_to_float(reinterpret_cast<const volatile unsigned short*>(src)[j]);
-            b[i] = bf16_bits_to_float(reinterpret_cast<const volatile unsigned short*>(src)[j + HALF]);
+            a[i] = bf16_bits_to_float(src[j]);
+            b[i] = bf16_bits_to_float(src[j + HALF]);
             squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(a[i], a[i]), __fmul_rn(b[i], b[i])));
         }
     }
@@ -103,13 +105,13 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const int* __restrict__ slots, bf16* __restrict__ key_cache,
                         bf16* __restrict__ value_cache, const int* __restrict__ block_tables,
                         int table_stride, int page_size, bf16* __restrict__ out, int num_q, int num_kv,
-                        int window, float scale, int write_cache) {
+                        int window, float scale, int write_cache, int warp_slot_capacity) {
     constexpr int LPK = HEAD_DIM / 8;          // lanes that share one key
     constexpr int KPI = 32 / LPK;              // keys per warp instruction
     constexpr int WARP_KEYS = KPI * DEC_UNROLL;
-    constexpr int TILE_KEYS = WARP_KEYS * DEC_WARPS;
     extern __shared__ __align__(16) unsigned char shared_raw[];
     DecodeShared<HEAD_DIM, HPB>& sh = *reinterpret_cast<DecodeShared<HEAD_DIM, HPB>*>(shared_raw);
+    int* slot_s = reinterpret_cast<int*>(shared_raw + sizeof(DecodeShared<HEAD_DIM, HPB>));
 
     cg::cluster_group cluster = cg::this_cluster();
     const int split = blockIdx.x;              // = rank in the cluster
@@ -125,15 +127,69 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     const int row = token_row[request];
     bf16* out_row = out + ((int64_t)request * num_q + first_q_head) * HEAD_DIM;
     if (row < 0 || position < 0) {              // padding: the whole cluster leaves together
+        pdl_wait();
         if (split == 0)
             for (int i = threadIdx.x; i < HPB * HEAD_DIM; i += blockDim.x) out_row[i] = __float2bfloat16_rn(0.0f);
         return;
     }
 
+    // ---- the keys [lo, position] are cut into `splits` pieces of a size that depends on this
+    // request alone; piece `split` is this CTA's.  Keys [first, last] of it are in the cache.
+    const int lo = window > 0 ? max(0, position - window + 1) : 0;
+    const int range_first = lo - lo % 64;
+    const int split_keys = ((position - range_first + splits) / splits + 63) / 64 * 64;
+    const int own_split = (position - range_first) / split_keys;     // holds the new token
+    const int base = range_first + split * split_keys;
+    const int first = max(lo, base);
+    const int last = min(position - 1, base + split_keys - 1);
+    const int sub = lane % LPK;                 // which 8 dimensions of a key this lane holds
+    const int key_in_instr = lane / LPK;
+    const int* table = block_tables + (int64_t)row * table_stride;
+    const int64_t row_stride = (int64_t)num_kv * HEAD_DIM;
+    const bf16* k_base = key_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
+    const bf16* v_base = value_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
+
+    // The piece is walked in sub-tiles of WARP_KEYS keys; warp w takes sub-tiles w, w + 4, ...
+    const int sub_tiles = last >= first ? (last - base) / WARP_KEYS + 1 : 0;
+    int first_tile = max(0, (first - base) / WARP_KEYS);
+    first_tile += (warp - first_tile % DEC_WARPS + DEC_WARPS) % DEC_WARPS;
+    int mine = first_tile < sub_tiles ? (sub_tiles - 1 - first_tile) / DEC_WARPS + 1 : 0;
+    mine = min(mine, warp_slot_capacity / WARP_KEYS);     // the host sizes the list for the context limit
+
+    // cache slots of all keys of this warp, looked up once (-1: no key there)
+    int* my_slots = slot_s + warp * warp_slot_capacity;
+    for (int e = lane; e < mine * WARP_KEYS; e += 32) {
+        const int key = base + (first_tile + (e / WARP_KEYS) * DEC_WARPS) * WARP_KEYS + e % WARP_KEYS;
+        int slot = -1;
+        if (key >= first && key <= last) {
+            const int page = table[key / page_size];
+            if (page >= 0) slot = page * page_size + key % page_size;
+        }
+        my_slots[e] = slot;
+    }
+    __syncwarp();
+
+    auto issue = [&](int i) {                   // the i-th sub-tile of this warp into stage i % DEC_STAGES
+        uint4(*stage)[DEC_UNROLL][32] = sh.ring[warp][i % DEC_STAGES];
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            const int slot = my_slots[i * WARP_KEYS + u * KPI + key_in_instr];
+            const int64_t offset = (int64_t)max(slot, 0) * row_stride;
+            cp_async_16(&stage[0][u][lane], k_base + offset, slot >= 0);
+            cp_async_16(&stage[1][u][lane], v_base + offset, slot >= 0);
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; ++i) {  // in flight before anything of this step is needed
+        if (i < mine) issue(i);
+        cp_async_commit();
+    }
+
     // ---- the new token: q heads of this CTA, and k, v of its kv head
     pdl_wait();                                 // the projection comes from the kernel before this one
     {
-        const bf16* token = qkv + (int64_t)request * heads * HEAD_DIM;
+        const volatile unsigned short* token =
+            reinterpret_cast<const volatile unsigned short*>(qkv) + (int64_t)request * heads * HEAD_DIM;
         const int table_row = min(position, table_positions - 1);
         const float* cos_row = cos_table ? cos_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
         const float* sin_row = sin_table ? sin_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
@@ -145,44 +201,38 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                 norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(num_q + kv_head) * HEAD_DIM, k_weight, eps,
                                               cos_row, sin_row, sh.k_new, lane);
             } else {
-                const bf16* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
-                for (int i = lane; i < HEAD_DIM; i += 32)
-                    sh.v_new[i] = bf16_bits_to_float(reinterpret_cast<const volatile unsigned short*>(v)[i]);
+                const volatile unsigned short* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
+                for (int i = lane; i < HEAD_DIM; i += 32) sh.v_new[i] = bf16_bits_to_float(v[i]);
             }
         }
     }
     __syncthreads();
 
-    // ---- the keys [lo, position] are cut into `splits` pieces of a size that depends on this
-    // request alone; piece `split` is this CTA's
-    const int lo = window > 0 ? max(0, position - window + 1) : 0;
-    const int range_first = lo - lo % 64;
-    const int split_keys = ((position - range_first + splits) / splits + 63) / 64 * 64;
-    const int own_split = (position - range_first) / split_keys;     // holds the new token
-    if (split == own_split && write_cache && (blockIdx.y % blocks_per_kv) == 0) {
-        const int slot = slots[request];
-        if (slot >= 0) {
-            bf16* kd = key_cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM;
-            bf16* vd = value_cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM;
-            for (int i = threadIdx.x; i < HEAD_DIM; i += blockDim.x) {
-                kd[i] = __float2bfloat16_rn(sh.k_new[i]);
-                vd[i] = __float2bfloat16_rn(sh.v_new[i]);
+    if (split == own_split) {
+        if (write_cache && (blockIdx.y % blocks_per_kv) == 0) {
+            const int slot = slots[request];
+            if (slot >= 0) {
+                bf16* kd = key_cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM;
+                bf16* vd = value_cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM;
+                for (int i = threadIdx.x; i < HEAD_DIM; i += blockDim.x) {
+                    kd[i] = __float2bfloat16_rn(sh.k_new[i]);
+                    vd[i] = __float2bfloat16_rn(sh.v_new[i]);
+                }
             }
+        }
+        for (int h = warp; h < HPB; h += DEC_WARPS) {       // score of the new key, one warp a head
+            float dot = 0.0f;
+            for (int i = lane; i < HEAD_DIM; i += 32) dot = __fmaf_rn(sh.q[h][i], sh.k_new[i], dot);
+            dot = warp_sum(dot);
+            if (lane == 0) sh.s_new[h] = __fmul_rn(dot, scale);
         }
     }
 
-    // keys of this piece that are already in the cache: [first, last]
-    const int base = range_first + split * split_keys;
-    const int first = max(lo, base);
-    const int last = min(position - 1, base + split_keys - 1);
-    const int sub = lane % LPK;                 // which 8 dimensions of a key this lane holds
-    const int key_in_instr = lane / LPK;
     float q_reg[HPB][8];
 #pragma unroll
     for (int h = 0; h < HPB; ++h)
 #pragma unroll
         for (int i = 0; i < 8; ++i) q_reg[h][i] = sh.q[h][sub * 8 + i];
-
     float m_run[HPB], l_run[HPB], o_run[HPB][8];
 #pragma unroll
     for (int h = 0; h < HPB; ++h) {
@@ -191,42 +241,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
 #pragma unroll
         for (int i = 0; i < 8; ++i) o_run[h][i] = 0.0f;
     }
-    const int* table = block_tables + (int64_t)row * table_stride;
-    const int64_t row_stride = (int64_t)num_kv * HEAD_DIM;
-    const bf16* k_base = key_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
-    const bf16* v_base = value_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
 
-    // The piece is walked in sub-tiles of WARP_KEYS keys; warp w takes sub-tiles w, w + 4, ...
-    // and keeps DEC_STAGES - 1 of them in flight in its own ring (cp.async, one group a stage).
-    const int sub_tiles = last >= first ? (last - base) / WARP_KEYS + 1 : 0;
-    int first_tile = max(0, (first - base) / WARP_KEYS);
-    first_tile += (warp - first_tile % DEC_WARPS + DEC_WARPS) % DEC_WARPS;
-    const int mine = first_tile < sub_tiles ? (sub_tiles - 1 - first_tile) / DEC_WARPS + 1 : 0;
-
-    auto issue = [&](int i) {                   // the i-th sub-tile of this warp into stage i % DEC_STAGES
-        const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
-        int my_slot = -1;
-        {
-            const int key = key0 + lane;
-            if (lane < WARP_KEYS && key >= first && key <= last) {
-                const int page = table[key / page_size];
-                if (page >= 0) my_slot = page * page_size + key % page_size;
-            }
-        }
-        uint4(*stage)[DEC_UNROLL][32] = sh.ring[warp][i % DEC_STAGES];
-#pragma unroll
-        for (int u = 0; u < DEC_UNROLL; ++u) {
-            const int slot = __shfl_sync(0xffffffffu, my_slot, u * KPI + key_in_instr);
-            const int64_t offset = (int64_t)max(slot, 0) * row_stride;
-            cp_async_16(&stage[0][u][lane], k_base + offset, slot >= 0);
-            cp_async_16(&stage[1][u][lane], v_base + offset, slot >= 0);
-        }
-    };
-#pragma unroll
-    for (int i = 0; i < DEC_STAGES - 1; ++i) {
-        if (i < mine) issue(i);
-        cp_async_commit();
-    }
     for (int i = 0; i < mine; ++i) {
         if (i + DEC_STAGES - 1 < mine) issue(i + DEC_STAGES - 1);
         cp_async_commit();
@@ -240,7 +255,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
             const int key = key0 + u * KPI + key_in_instr;
             valid[u] = key >= first && key <= last;
             float kf[8];
-            unpack8(stage[0][u][lane], kf);
+            unpack_bf16x8(stage[0][u][lane], kf);
 #pragma unroll
             for (int h = 0; h < HPB; ++h) {
                 float dot = 0.0f;
@@ -276,15 +291,15 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
 #pragma unroll
         for (int u = 0; u < DEC_UNROLL; ++u) {
             float vf[8];
-            unpack8(stage[1][u][lane], vf);        // zero where there is no key
+            unpack_bf16x8(stage[1][u][lane], vf);   // zero where there is no key
 #pragma unroll
             for (int h = 0; h < HPB; ++h)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) o_run[h][j] = __fmaf_rn(prob[h][u], vf[j], o_run[h][j]);
         }
     }
-
     pdl_launch_dependents();
+
     // ---- lanes that hold the same dimensions for different keys, then the warps, in a fixed order
 #pragma unroll
     for (int h = 0; h < HPB; ++h) {
@@ -301,6 +316,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         if (lane == 0) { sh.warp_m[warp][h] = m_run[h]; sh.warp_l[warp][h] = l_run[h]; }
     }
     __syncthreads();
+    DecodeShared<HEAD_DIM, HPB>* first_cta = cluster.map_shared_rank(&sh, 0);
     for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
         const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
         float m = -INFINITY;
@@ -314,9 +330,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
             o += sh.warp_o[w][h][dim] * f;
         }
         if (split == own_split) {               // the new token itself, from shared memory
-            float dot = 0.0f;
-            for (int i = 0; i < HEAD_DIM; ++i) dot = __fmaf_rn(sh.q[h][i], sh.k_new[i], dot);
-            const float s = __fmul_rn(dot, scale);
+            const float s = sh.s_new[h];
             const float new_max = fmaxf(m, s);
             const float f_old = m == -INFINITY ? 0.0f : __expf(m - new_max);
             const float f_new = __expf(s - new_max);
@@ -324,32 +338,34 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
             o = o * f_old + f_new * sh.v_new[dim];
             m = new_max;
         }
-        sh.part_o[h][dim] = o;
-        if (dim == 0) { sh.part_m[h] = m; sh.part_l[h] = l; }
+        first_cta->part_o[split][h][dim] = o;   // a store into the first CTA's shared memory
+        if (dim == 0) { first_cta->part_m[split][h] = m; first_cta->part_l[split][h] = l; }
     }
 
-    // ---- merge the splits of the cluster in rank order
+    // ---- the first CTA merges the pieces in rank order
     cluster.sync();
     if (split == 0) {
         for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
             const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
             float m = -INFINITY;
-            for (int r = 0; r < splits; ++r) {
-                const DecodeShared<HEAD_DIM, HPB>* other = cluster.map_shared_rank(&sh, r);
-                m = fmaxf(m, other->part_m[h]);
-            }
+            for (int r = 0; r < splits; ++r) m = fmaxf(m, sh.part_m[r][h]);
             float l = 0.0f, o = 0.0f;
             for (int r = 0; r < splits; ++r) {
-                const DecodeShared<HEAD_DIM, HPB>* other = cluster.map_shared_rank(&sh, r);
-                const float pm = other->part_m[h];
+                const float pm = sh.part_m[r][h];
                 const float f = pm == -INFINITY ? 0.0f : __expf(pm - m);
-                l += other->part_l[h] * f;
-                o += other->part_o[h][dim] * f;
+                l += sh.part_l[r][h] * f;
+                o += sh.part_o[r][h][dim] * f;
             }
             out_row[index] = __float2bfloat16_rn(o / l);
         }
     }
-    cluster.sync();                             // nobody leaves while rank 0 still reads its memory
+}
+
+template <int HEAD_DIM>
+static int decode_warp_slot_capacity(int max_context, int splits) {
+    constexpr int WARP_KEYS = (32 / (HEAD_DIM / 8)) * DEC_UNROLL;
+    const int split_keys = ((max_context + splits - 1) / splits + 63) / 64 * 64 + 64;
+    return (split_keys / (WARP_KEYS * DEC_WARPS) + 2) * WARP_KEYS;
 }
 
 template <int HEAD_DIM, int HPB, typename W>
@@ -358,9 +374,11 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
                          void* value_cache, const int* block_tables, int table_stride, int page_size,
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
-                         int splits, int write_cache, int pdl, cudaStream_t stream) {
+                         int splits, int write_cache, int max_context, int pdl, cudaStream_t stream) {
     auto kernel = decode_attention_kernel<HEAD_DIM, HPB, W>;
-    const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB>);
+    const int warp_slots = decode_warp_slot_capacity<HEAD_DIM>(max_context, splits);
+    const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB>) + (size_t)DEC_WARPS * warp_slots * sizeof(int);
+    if (shared > 200 * 1024) return TVB_BAD_ARGUMENT;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (e != cudaSuccess) return (int)e;
     TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / HPB), requests), dim3(DEC_WARPS * 32), shared,
@@ -368,7 +386,7 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
     e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
                            cos_table, sin_table, table_positions, positions, token_row, slots,
                            (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
-                           (bf16*)out, num_q, num_kv, window, scale, write_cache);
+                           (bf16*)out, num_q, num_kv, window, scale, write_cache, warp_slots);
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
@@ -378,29 +396,31 @@ extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv
     if (num_kv <= 0 || num_q % num_kv) return 0;
     const int group = num_q / num_kv;
     if (!(group == 1 || group == 2 || group % 4 == 0)) return 0;
-    return splits >= 1 && splits <= 8;
+    return splits >= 1 && splits <= DEC_MAX_SPLITS;
 }
 
 // qkv: [requests, (num_q + 2 num_kv) * head_dim] bfloat16, the raw projection of one token per
 // request.  weight_dtype: TVB_BF16 or TVB_F32 (norm weights; null pointers skip the norm).
 // splits (1..8) is the cluster size: the number of pieces every request's keys are cut into.
+// max_context bounds position + 1 of every request (it sizes the list of cache slots a warp keeps).
 extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                                     const float* cos_table, const float* sin_table, int table_positions,
                                     const int* positions, const int* token_row, const int* slots,
                                     void* key_cache, void* value_cache, const int* block_tables,
                                     int table_stride, int page_size, void* out, int requests, int num_q,
-                                    int num_kv, int head_dim, int window, float scale,
-                                    int splits, int write_cache, int weight_dtype, int pdl, void* stream) {
+                                    int num_kv, int head_dim, int window, float scale, int splits,
+                                    int write_cache, int max_context, int weight_dtype, int pdl,
+                                    void* stream) {
     if (requests <= 0) return 0;
-    if (!tvb_attention_decode_supports(head_dim, num_q, num_kv, splits) ||
-        page_size <= 0 || requests > 65535)
+    if (!tvb_attention_decode_supports(head_dim, num_q, num_kv, splits) || page_size <= 0 ||
+        requests > 65535 || max_context <= 0)
         return TVB_BAD_ARGUMENT;
     const int group = num_q / num_kv;
     const int hpb = group % 4 == 0 ? 4 : group;
     cudaStream_t s = (cudaStream_t)stream;
 #define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
                     token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
-                    requests, num_q, num_kv, window, scale, splits, write_cache, pdl, s
+                    requests, num_q, num_kv, window, scale, splits, write_cache, max_context, pdl, s
 #define DECODE_BY_HPB(D, WT)                                            \
     do {                                                                \
         if (hpb == 1) return launch_decode<D, 1, WT>(DECODE_ARGS);      \

@@ -80,7 +80,8 @@ class DecodeGraphs:
                           for g in range(groups)],
             cache_sources=self.runner.cache_sources, max_position=self.max_model_len - 1,
             split_chunks=self.split_chunks, workspace_of=self.runner._workspace_of,
-            decode_only=True, decode_splits=self.runner.decode_splits)
+            decode_only=True, decode_splits=self.runner.decode_splits,
+            max_context=self.max_model_len)
 
     def _fill_padding(self, bucket: _Bucket) -> None:
         bucket.host_np[:] = 0

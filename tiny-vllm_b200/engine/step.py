@@ -64,6 +64,7 @@ class StepContext:
     workspace_of: object = None          # callable(floats) -> float32 scratch tensor
     decode_only: bool = False            # every entry is a single token
     decode_splits: int = 0               # pieces the fused decode attention cuts a context into
+    max_context: int = 0                 # no request grows beyond this many tokens
     tile_row: torch.Tensor | None = None     # tiles of consecutive query tokens for the tile kernel:
     tile_first: torch.Tensor | None = None   # request row, first flat token and token count of each
     tile_count: torch.Tensor | None = None
@@ -217,7 +218,7 @@ class StepRunner:
             block_tables=[dview(7 + 2 * g).view(rows, blocks[g]) for g in range(groups)],
             cache_sources=self.cache_sources, max_position=max_position, split_chunks=split_chunks,
             workspace_of=self._workspace_of, decode_only=decode_only,
-            decode_splits=self.decode_splits,
+            decode_splits=self.decode_splits, max_context=self.max_model_len,
             tile_row=None if decode_only else dview(tiles_at),
             tile_first=None if decode_only else dview(tiles_at + 1),
             tile_count=None if decode_only else dview(tiles_at + 2),

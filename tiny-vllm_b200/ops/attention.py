@@ -75,7 +75,8 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
             qkv, **heads, positions=ctx.positions, token_row=ctx.token_row, slots=ctx.slots[group],
             q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0,
             cos=cos, sin=sin, key_cache=keys, value_cache=values, block_tables=ctx.block_tables[group],
-            window=mixer.window, scale=mixer.scale, splits=ctx.decode_splits)
+            window=mixer.window, scale=mixer.scale, splits=ctx.decode_splits,
+            max_context=ctx.max_context)
     kernels.qk_norm_rope_store(
         qkv, **heads, positions=ctx.positions, q_weight=mixer.q_norm_weight,
         k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0, cos=cos, sin=sin,

@@ -41,9 +41,9 @@ _launches = 0
 # (griddepcontrol.wait): they may start, and fetch weights, while the kernel before them ends.
 # TINYVLLM_B200_PDL=0 turns it off; a comma-separated list (gemm,norm,attention,sample) keeps it
 # for those kernels only.
-_PDL_ALL = ("gemm", "norm", "attention", "sample")
+_PDL_DEFAULT = ("gemm",)
 _setting = os.environ.get("TINYVLLM_B200_PDL", "1")
-PDL = frozenset() if _setting == "0" else frozenset(_PDL_ALL if _setting == "1" else _setting.split(","))
+PDL = frozenset() if _setting == "0" else frozenset(_PDL_DEFAULT if _setting == "1" else _setting.split(","))
 
 
 def _pdl(kind: str) -> int:
@@ -330,12 +330,13 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
                      q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
                      cos: torch.Tensor | None, sin: torch.Tensor | None, key_cache: torch.Tensor,
                      value_cache: torch.Tensor, block_tables: torch.Tensor, window: int | None,
-                     scale: float, splits: int,
+                     scale: float, splits: int, max_context: int,
                      out: torch.Tensor | None = None) -> torch.Tensor:
     """One new token per request, from the raw packed projection to the attention output:
     q/k norm and rotation, cache write (unless ``slots`` is None) and attention in one launch.
     Request i is row ``token_row[i]`` of ``block_tables`` (-1: padding) and stands at
-    ``positions[i]``.  Every request's keys are cut into ``splits`` pieces, one per CTA of a cluster."""
+    ``positions[i]``.  Every request's keys are cut into ``splits`` pieces, one per CTA of a cluster;
+    ``max_context`` bounds ``positions + 1``."""
     _need_cuda(qkv, positions, token_row, slots, q_weight, k_weight, cos, sin, key_cache, value_cache,
                block_tables)
     requests = qkv.shape[0]
@@ -365,12 +366,13 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     fn = _fn("attention_decode", "tvb_attention_decode",
              [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
-              c_int, c_float, c_int, c_int, c_int, c_int, c_void_p])
+              c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos), _ptr(sin), table_positions,
               positions.data_ptr(), token_row.data_ptr(), _ptr(slots), key_cache.data_ptr(),
               value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
               key_cache.shape[1], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
-              splits, 1 if slots is not None else 0, weight_tag, _pdl("attention"), _stream()),
+              splits, 1 if slots is not None else 0, max_context, weight_tag, _pdl("attention"),
+              _stream()),
            "attention_decode")
     return out
 

@@ -8,6 +8,8 @@ reference's engine calls for every projection (tinyvllm/layers.py:84-85).
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import kernels
@@ -40,6 +42,11 @@ def linear_silu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
     return gemm.linear_silu_bf16(x, gate_up_weight)
 
 
+# Every CTA of the fused kernel reads all rows of the input to normalise them for itself; beyond
+# a few rows those reads cost more (in L2 bandwidth) than the separate norm kernel they replace.
+FUSED_NORM_MAX_ROWS = int(os.environ.get("TINYVLLM_B200_FUSED_NORM_ROWS", "2"))
+
+
 def linear_norm(hidden: torch.Tensor, residual: torch.Tensor | None, norm, weight: torch.Tensor, *,
                 silu: bool = False):
     """(linear(norm(hidden + residual), weight), hidden + residual): a pre-norm and the
@@ -51,6 +58,7 @@ def linear_norm(hidden: torch.Tensor, residual: torch.Tensor | None, norm, weigh
 
     if (hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and hidden.is_contiguous()
             and type(norm).__name__ == "RMSNorm" and gemm.small(hidden, weight)
+            and hidden.shape[0] <= FUSED_NORM_MAX_ROWS
             and kernels.gemm_small_m_takes_norm(hidden.shape[0], hidden.shape[1])):
         mode = kernels.GEMM_SILU if silu else kernels.GEMM_BF16
         out, stream = kernels.gemm_small_m(hidden, weight, mode, norm_weight=norm.weight,
