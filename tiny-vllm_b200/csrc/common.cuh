@@ -105,6 +105,18 @@ __device__ __forceinline__ uint4 ld_global_16(const void* p) {
     return v;
 }
 
+// Ask for the 128-byte line at p to be brought into L2; nothing waits for it.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p)); }
+
+// Every thread of the grid takes its share of the lines of [p, p + bytes).
+__device__ __forceinline__ void prefetch_l2_range(const void* p, long long bytes) {
+    if (!p || bytes <= 0) return;
+    const long long threads = (long long)gridDim.x * gridDim.y * gridDim.z * blockDim.x;
+    const long long me = ((long long)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
+    for (long long line = me; line * 128 < bytes; line += threads)
+        prefetch_l2(reinterpret_cast<const char*>(p) + line * 128);
+}
+
 // Launch configuration with the optional attributes: cluster size along x, programmatic
 // stream serialisation.
 struct TvbLaunch {

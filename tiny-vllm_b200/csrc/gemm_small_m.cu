@@ -58,7 +58,8 @@ struct NormArgs {
 template <int NT, int MODE, int NORM>
 __global__ void __launch_bounds__(SM_WARPS * 32)
 gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int64_t ldw,
-                    void* __restrict__ out, int64_t ldo, int m, int n, int k, int up_offset, NormArgs norm) {
+                    void* __restrict__ out, int64_t ldo, int m, int n, int k, int up_offset, NormArgs norm,
+                    const void* __restrict__ next_weight, long long next_bytes) {
     constexpr int SETS = MODE == MODE_SILU ? 2 : 1;
     constexpr int MP = 8 * NT;
     __shared__ float warp_part[SM_WARPS][SETS][16][MP];
@@ -108,6 +109,7 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
             }
         }
         if (!ready) {                // the weights are on their way; now the previous kernel's output
+            prefetch_l2_range(next_weight, next_bytes);   // and those of the product after this one
             pdl_wait();
             if (NORM) {
                 // every CTA normalises all rows for itself: warp w takes rows w, w + 4, ...
@@ -228,7 +230,7 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
 template <int NT, int MODE, int NORM>
 static int launch_small_m(const void* x, long long ldx, const void* w, long long ldw, void* out,
                           long long ldo, int m, int n, int k, int up_offset, int ranks, int pdl,
-                          NormArgs norm, cudaStream_t stream) {
+                          NormArgs norm, const void* next_weight, long long next_bytes, cudaStream_t stream) {
     auto kernel = gemm_small_m_kernel<NT, MODE, NORM>;
     size_t dynamic = 0;
     if (NORM) {
@@ -239,7 +241,8 @@ static int launch_small_m(const void* x, long long ldx, const void* w, long long
     }
     TvbLaunch launch(dim3(ranks, (n + 15) / 16), dim3(SM_WARPS * 32), dynamic, stream, pdl, ranks);
     cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)x, (int64_t)ldx, (const bf16*)w,
-                                       (int64_t)ldw, out, (int64_t)ldo, m, n, k, up_offset, norm);
+                                       (int64_t)ldw, out, (int64_t)ldo, m, n, k, up_offset, norm, next_weight,
+                                       next_bytes);
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
@@ -252,12 +255,16 @@ extern "C" int tvb_gemm_small_m_max_rows() { return 32; }
 // both are contiguous [m, k]); residual_out (may be null) receives the rounded sum.
 // norm_weight_dtype: TVB_BF16 or TVB_F32.
 //
+// next_weight / next_bytes (may be null / 0): memory the grid asks to be brought into L2 while it
+// works, typically the weight of the product that follows.
+//
 // pdl != 0 launches with programmatic stream serialisation: the kernel may start while the kernel
 // before it in the stream still runs; it reads nothing but weights before it waits for that kernel.
 extern "C" int tvb_gemm_small_m(const void* x, long long ldx, const void* w, long long ldw, void* out,
                                 long long ldo, int m, int n, int k, int mode, const void* residual,
                                 const void* norm_weight, void* residual_out, float eps,
-                                int norm_weight_dtype, int pdl, void* stream) {
+                                int norm_weight_dtype, const void* next_weight, long long next_bytes,
+                                int pdl, void* stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 32 || k <= 0 || k % 8 || ldx % 8 || ldw % 8 || mode < 0 || mode > 2 || n > 65535 * 16)
         return TVB_BAD_ARGUMENT;
@@ -275,7 +282,8 @@ extern "C" int tvb_gemm_small_m(const void* x, long long ldx, const void* w, lon
     const int norm_kind = !norm_weight ? 0 : (norm_weight_dtype == TVB_F32 ? 2 : 1);
     if (norm_weight && norm_weight_dtype != TVB_F32 && norm_weight_dtype != TVB_BF16) return TVB_BAD_ARGUMENT;
 #define SMALL_M(NT, MODE, NORM) \
-    launch_small_m<NT, MODE, NORM>(x, ldx, w, ldw, out, ldo, m, n, k, up_offset, ranks, pdl, norm, s)
+    launch_small_m<NT, MODE, NORM>(x, ldx, w, ldw, out, ldo, m, n, k, up_offset, ranks, pdl, norm, \
+                                   next_weight, next_bytes, s)
 #define BY_NORM(NT, MODE)                                   \
     do {                                                    \
         if (norm_kind == 0) return SMALL_M(NT, MODE, 0);    \

@@ -67,6 +67,16 @@ class Model:
             finalize = getattr(part, "finalize", None)
             if finalize is not None:
                 finalize()
+        if self.device.type == "cuda":
+            # the order in which a step streams the large weights: each product fetches the next
+            from ..ops.gemm import chain_weights
+            streamed = []
+            for step in self.order:
+                block = self.blocks[step.layer]
+                for part in block.all_parts():
+                    streamed.extend(getattr(part, "streamed_weights", lambda: [])())
+            streamed.extend(getattr(self.head, "streamed_weights", lambda: [])())
+            chain_weights(streamed)
 
     def _optional_names(self) -> tuple[str, ...]:
         # a tied head may still be stored beside the embedding (tinyvllm/models/qwen3.py:637-641)

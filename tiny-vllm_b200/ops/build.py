@@ -124,6 +124,9 @@ def compile_library(name: str, *, verbose: bool = True) -> Path:
         partial.unlink(missing_ok=True)
         raise KernelBuildError(f"nvcc failed on {source.name}:\n{output}")
     os.replace(partial, target)
+    for stale in folder.glob(f"tvb200_{name}_*.so"):       # builds of older versions of this source
+        if stale != target:
+            stale.unlink(missing_ok=True)
     if verbose:
         print(f"[tinyvllm_b200] built {target.name} in {time.time() - started:.1f} s",
               file=sys.stderr, flush=True)

@@ -12,6 +12,22 @@ import torch
 from . import kernels
 
 
+# weight (by address) -> the weight the model streams next in a decode step; the weight-streaming
+# kernel asks for it to be brought into L2 while it works on its own
+_next_weight: dict[int, torch.Tensor] = {}
+
+
+def chain_weights(weights) -> None:
+    """Declare the order in which a step streams ``weights`` (the last is followed by the first)."""
+    weights = [w for w in weights if w is not None and w.is_cuda and w.dtype == torch.bfloat16]
+    for current, following in zip(weights, weights[1:] + weights[:1]):
+        _next_weight[current.data_ptr()] = following
+
+
+def next_weight(weight: torch.Tensor) -> torch.Tensor | None:
+    return _next_weight.get(weight.data_ptr())
+
+
 def small(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether the weight-streaming kernel takes this product."""
     return (x.shape[0] <= kernels.SMALL_M_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
@@ -26,7 +42,7 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype
         raise kernels.KernelError(f"linear_bf16 cannot produce {out_dtype}")
     if small(x, weight):
         mode = kernels.GEMM_BF16 if out_dtype == torch.bfloat16 else kernels.GEMM_F32
-        return kernels.gemm_small_m(x, weight, mode, out=out)
+        return kernels.gemm_small_m(x, weight, mode, out=out, prefetch=next_weight(weight))
     if out_dtype == torch.bfloat16:
         if out is not None:
             return torch.mm(x, weight.t(), out=out)
@@ -44,5 +60,5 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype
 def linear_silu_bf16(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
     """silu(x . gate^T) * (x . up^T) for a packed [gate | up] weight."""
     if small(x, gate_up_weight):
-        return kernels.gemm_small_m(x, gate_up_weight, kernels.GEMM_SILU)
+        return kernels.gemm_small_m(x, gate_up_weight, kernels.GEMM_SILU, prefetch=next_weight(gate_up_weight))
     return kernels.silu_mul(torch.nn.functional.linear(x, gate_up_weight))

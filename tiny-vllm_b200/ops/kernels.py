@@ -426,19 +426,24 @@ def attention_prefill(q: torch.Tensor, q_token_stride: int, key_cache: torch.Ten
 
 # ------------------------------------------------ weight-streaming small-M GEMM
 SMALL_M_MAX_ROWS = 32
+PREFETCH_MAX_BYTES = 32 << 20
 GEMM_BF16, GEMM_F32, GEMM_SILU = 0, 1, 2
 
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
                  out: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
-                 residual: torch.Tensor | None = None, eps: float = 0.0, want_residual: bool = True):
+                 residual: torch.Tensor | None = None, eps: float = 0.0, want_residual: bool = True,
+                 prefetch: torch.Tensor | None = None):
     """x [m <= 32, k] . w [n, k]^T, bfloat16 operands.  mode GEMM_BF16 / GEMM_F32: result
     [m, n] in that dtype; GEMM_SILU: w is [gate | up] with 2 n rows and the result is
     silu(x . gate^T) * (x . up^T), bfloat16 [m, n].
 
     With ``norm_weight`` the product is taken of RMSNorm(x + residual) * norm_weight instead
     of x (``residual`` may be None), and (result, rounded sum x + residual) is returned; the
-    sum is None without a residual or with ``want_residual=False``."""
+    sum is None without a residual or with ``want_residual=False``.
+
+    ``prefetch``: a tensor (the weight of the product after this one) whose first
+    ``PREFETCH_MAX_BYTES`` the grid asks into L2 while it works."""
     _need_cuda(x, w, norm_weight, residual)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2:
         raise KernelError("gemm_small_m wants bfloat16 matrices")
@@ -471,10 +476,12 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
                           device=x.device)
     fn = _fn("gemm_small_m", "tvb_gemm_small_m",
              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
-              c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p])
+              c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_longlong, c_int, c_void_p])
+    next_bytes = 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(),
+                                                PREFETCH_MAX_BYTES)
     _check(fn(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
               m, n, k, mode, _ptr(residual), _ptr(norm_weight), _ptr(residual_out), eps, weight_tag,
-              _pdl("gemm"), _stream()), "gemm_small_m")
+              _ptr(prefetch), next_bytes, _pdl("gemm"), _stream()), "gemm_small_m")
     if norm_weight is not None:
         return out, residual_out
     return out

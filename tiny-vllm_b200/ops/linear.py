@@ -62,7 +62,8 @@ def linear_norm(hidden: torch.Tensor, residual: torch.Tensor | None, norm, weigh
             and kernels.gemm_small_m_takes_norm(hidden.shape[0], hidden.shape[1])):
         mode = kernels.GEMM_SILU if silu else kernels.GEMM_BF16
         out, stream = kernels.gemm_small_m(hidden, weight, mode, norm_weight=norm.weight,
-                                           residual=residual, eps=norm.eps)
+                                           residual=residual, eps=norm.eps,
+                                           prefetch=gemm.next_weight(weight))
         return out, (hidden if residual is None else stream)
     if residual is None:
         x, stream = norm.forward(hidden), hidden

@@ -59,6 +59,9 @@ class GQAAttention(Part):
     def children(self):
         return [self.position] if self.position is not None else []
 
+    def streamed_weights(self):
+        return [self.qkv_weight, self.o_weight]
+
     def cache_need(self):
         return KVNeed(self.num_kv_heads, self.head_dim, self.window)
 

@@ -36,6 +36,9 @@ class LMHead(Part):
             return []
         return [ParamSpec.single("weight", self.name, (self.vocab_size, self.width))]
 
+    def streamed_weights(self):
+        return [self.weight]
+
     def forward(self, hidden_rows):
         return linear(hidden_rows, self.weight, out_dtype=torch.float32)
 

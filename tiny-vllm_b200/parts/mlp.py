@@ -30,6 +30,9 @@ class SwiGLU(Part):
                              (self.hidden_size, self.intermediate_size)),
         ]
 
+    def streamed_weights(self):
+        return [self.gate_up_weight, self.down_weight]
+
     def forward(self, x, ctx):
         return linear(linear_silu(x, self.gate_up_weight), self.down_weight)
 
