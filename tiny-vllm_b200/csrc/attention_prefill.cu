@@ -8,7 +8,7 @@
 // every request of the step is one launch.
 //
 // A CTA of 4 warps takes one tile of queries and one q head; each warp owns 16 query
-// rows.  Keys are walked in tiles of 64 that start at absolute multiples of 64, so a
+// rows.  Keys are walked in tiles of 32 that start at absolute multiples of 32, so a
 // row's arithmetic does not depend on how the prompt was cut.  K and V tiles are
 // brought in with cp.async (two stages), S = Q K^T and O += P V are mma.sync
 // m16n8k16 with float32 accumulators, P is rounded to bfloat16 for the second
@@ -17,7 +17,7 @@
 #include "common.cuh"
 
 #define PF_BM 64
-#define PF_BN 64
+#define PF_BN 32
 #define PF_WARPS 4
 #define PF_PAD 8        // bfloat16 of padding per shared-memory row: ldmatrix without bank conflicts
 
@@ -40,7 +40,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HEAD_DIM>
-__global__ void __launch_bounds__(PF_WARPS * 32)
+__global__ void __launch_bounds__(PF_WARPS * 32, 3)
 prefill_attention_kernel(const bf16* __restrict__ q, int64_t q_token_stride,
                          const bf16* __restrict__ key_cache, const bf16* __restrict__ value_cache,
                          const int* __restrict__ block_tables, int table_stride,
@@ -56,7 +56,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int64_t q_token_stride,
     bf16* v_s = k_s + 2 * PF_BN * ROW;                                       // [2][64][ROW]
     int* slot_s = reinterpret_cast<int*>(v_s + 2 * PF_BN * ROW);             // [2][64]
 
-    const int tile = blockIdx.x, head = blockIdx.y;
+    // later tiles of a request see more keys: they are launched first, the short ones fill the tail
+    const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int request = tile_row[tile], first_token = tile_first[tile], count = tile_count[tile];
     const int first_position = positions[first_token];

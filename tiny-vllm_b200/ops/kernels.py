@@ -132,6 +132,16 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual: tor
         residual_out = torch.empty_like(x)
     if rows is not None or residual is None:
         residual_out = None
+    if x.dtype == torch.bfloat16 and width % 8 == 0 and width <= 8192:     # 16-byte accesses
+        fn = _fn("pointwise_bf16", "tvb_rms_norm_bf16",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                  c_int, c_int, c_void_p])
+        _check(fn(x.data_ptr(), _ptr(residual), weight.data_ptr(), out.data_ptr(), _ptr(residual_out),
+                  _ptr(rows), count, width, eps, dtype_tag(weight.dtype), _pdl("norm"), _stream()),
+               "rms_norm")
+        if residual is not None and rows is None:
+            return out, residual_out
+        return out
     fn = _fn("pointwise", "tvb_rms_norm",
              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
               c_int, c_int, c_int, c_void_p])
@@ -152,6 +162,10 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Te
     rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
     if out is None:
         out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    if gate_up.dtype == torch.bfloat16 and inter % 8 == 0:
+        fn = _fn("pointwise_bf16", "tvb_silu_mul_bf16", [c_void_p, c_void_p, c_int, c_int, c_void_p])
+        _check(fn(gate_up.data_ptr(), out.data_ptr(), rows, inter, _stream()), "silu_mul")
+        return out
     fn = _fn("pointwise", "tvb_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(gate_up.data_ptr(), out.data_ptr(), rows, inter, dtype_tag(gate_up.dtype), _stream()),
            "silu_mul")
@@ -212,6 +226,13 @@ def qk_norm_rope_store(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: 
                 or not key_cache.is_contiguous() or not value_cache.is_contiguous()):
             raise KernelError("qk_norm_rope_store: slots int32 [tokens]; caches contiguous "
                               "[pages, page_size, num_kv, head_dim] of the dtype of qkv")
+    if qkv.dtype == torch.bfloat16 and head_dim in (16, 32, 64, 128, 256):
+        fn = _fn("pointwise_bf16", "tvb_qk_norm_rope_store_bf16",
+                 [c_void_p] * 9 + [c_int] * 5 + [c_float, c_int, c_void_p])
+        _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
+                  positions.data_ptr(), _ptr(slots), _ptr(key_cache), _ptr(value_cache), tokens, num_q,
+                  num_kv, head_dim, table_positions, eps, weight_tag, _stream()), "qk_norm_rope_store")
+        return
     fn = _fn("pointwise", "tvb_qk_norm_rope_store",
              [c_void_p] * 9 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p])
     _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
