@@ -276,3 +276,63 @@ extern "C" int tvb_attention_rows(const void* q, long long q_token_stride, const
 #undef LAUNCH_ROWS
     return tvb_last_error();
 }
+
+// ------------------------------------------------ entry point that allocates nothing
+// See attention_rows_static.h for who needs this and how to use it.
+#include "attention_rows_static.h"
+
+// The scratch of the split mode, held by every GPU that loads this library until exit.
+static __device__ __align__(256) float tvb_static_scratch[TVB_STATIC_SCRATCH_FLOATS];
+
+// In host code `tvb_static_scratch` is only a stand-in for the symbol, not a device address:
+// the address is asked for once per device, with that device current, and kept here.
+#define TVB_STATIC_MAX_DEVICES 64
+static float* tvb_static_scratch_address[TVB_STATIC_MAX_DEVICES];
+
+static int tvb_static_scratch_of_current_device(float** address) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= TVB_STATIC_MAX_DEVICES) return TVB_BAD_ARGUMENT;
+    if (!tvb_static_scratch_address[device]) {
+        float* found = nullptr;
+        e = cudaGetSymbolAddress((void**)&found, tvb_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!found) return (int)cudaErrorInvalidSymbol;
+        tvb_static_scratch_address[device] = found;
+    }
+    *address = tvb_static_scratch_address[device];
+    return 0;
+}
+
+extern "C" long long tvb_attention_rows_static_capacity(void) { return TVB_STATIC_SCRATCH_FLOATS; }
+
+extern "C" const char* tvb_attention_rows_static_error(int code) {
+    if (code == 0) return "ok";
+    if (code == TVB_STATIC_SCRATCH_TOO_SMALL)
+        return "the partials of this batch (tokens * num_q * max_chunks * (head_dim + 2) floats) do not fit "
+               "into the library's built-in scratch of 4 Mi floats; use tvb_attention_rows with a buffer of "
+               "your own, or fewer tokens per call";
+    if (code == TVB_BAD_ARGUMENT)
+        return "sizes this kernel does not take (or max_chunks == 0, which needs no scratch: call "
+               "tvb_attention_rows)";
+    return cudaGetErrorString((cudaError_t)code);
+}
+
+extern "C" int tvb_attention_rows_static(const void* q, long long q_token_stride, const void* key_cache,
+                                         const void* value_cache, const int* block_tables, int table_stride,
+                                         const int* token_row, const int* positions, void* out,
+                                         int max_chunks, int tokens, int num_q, int num_kv, int head_dim,
+                                         int page_size, int window, float scale, int dtype, void* stream) {
+    if (tokens <= 0) return 0;
+    if (max_chunks <= 0 || num_q <= 0 || head_dim <= 0) return TVB_BAD_ARGUMENT;
+    if (tvb_attention_rows_scratch_floats(tokens, num_q, head_dim, max_chunks) > TVB_STATIC_SCRATCH_FLOATS)
+        return TVB_STATIC_SCRATCH_TOO_SMALL;
+    float* scratch = nullptr;
+    const int status = tvb_static_scratch_of_current_device(&scratch);
+    if (status != 0) return status;
+    // the launcher below only checks sizes and launches the two kernels
+    return tvb_attention_rows(q, q_token_stride, key_cache, value_cache, block_tables, table_stride,
+                              token_row, positions, out, scratch, max_chunks, tokens, num_q, num_kv,
+                              head_dim, page_size, window, scale, dtype, stream);
+}
