@@ -91,7 +91,7 @@ def test_qk_norm_rope_store(dtype, heads):
     positions = torch.randint(0, 3000, (tokens,), dtype=torch.int32)
     slots = torch.randperm(page * pages)[:tokens].to(torch.int32)
     cos, sin = plain.rope_tables(d, 3000, 10_000.0)
-    kc = torch.zeros(pages, page, nkv, d, dtype=dtype, device=DEV)
+    kc = torch.zeros(pages, nkv, page, d, dtype=dtype, device=DEV)
     vc = torch.zeros_like(kc)
     work = qkv.to(DEV).clone()
     k().qk_norm_rope_store(work, num_q=nq, num_kv=nkv, head_dim=d, positions=positions.to(DEV),
@@ -103,12 +103,12 @@ def test_qk_norm_rope_store(dtype, heads):
     pos = positions.long()
     want_q, want_k = plain.qk_norm_rope(q, kk, qw.float(), kw.float(), cos[pos], sin[pos], 1e-6, dtype)
     close(work[:, :nq * d].view(tokens, nq, d), want_q, dtype, bf16=1.6e-2)
-    flat_k = kc.view(-1, nkv, d)[slots.long().to(DEV)]
+    flat_k = by_slot(kc)[slots.long().to(DEV)]
     close(flat_k, want_k, dtype, bf16=1.6e-2)
-    assert torch.equal(vc.view(-1, nkv, d)[slots.long().to(DEV)].cpu(), vv)
+    assert torch.equal(by_slot(vc)[slots.long().to(DEV)].cpu(), vv)
     untouched = torch.ones(page * pages, dtype=torch.bool)
     untouched[slots.long()] = False
-    assert kc.view(-1, nkv * d)[untouched.to(DEV)].abs().sum().item() == 0   # no stray writes
+    assert by_slot(kc)[untouched.to(DEV)].abs().sum().item() == 0   # no stray writes
     # without slots nothing is written, q still is
     kc.zero_()
     k().qk_norm_rope_store(qkv.to(DEV).clone(), num_q=nq, num_kv=nkv, head_dim=d,
@@ -118,6 +118,12 @@ def test_qk_norm_rope_store(dtype, heads):
     assert kc.abs().sum().item() == 0
 
 
+def by_slot(cache):
+    """[pages, kv_heads, page, head_dim] seen as [pages * page, kv_heads, head_dim] (slot = page * size + offset)."""
+    pages, nkv, page, d = cache.shape
+    return cache.permute(0, 2, 1, 3).reshape(pages * page, nkv, d)
+
+
 def paged_case(dtype, *, nq, nkv, d, page, lengths, queries, seed, boost=None):
     """Requests with ``lengths`` keys each scattered over shuffled pages; the last ``queries[i]``
     positions of request i are query tokens.  ``boost`` = (request, key position, factor) scales one
@@ -125,7 +131,7 @@ def paged_case(dtype, *, nq, nkv, d, page, lengths, queries, seed, boost=None):
     g = torch.Generator().manual_seed(seed)
     total_pages = sum(-(-n // page) for n in lengths) + 3
     order = torch.randperm(total_pages, generator=g).tolist()
-    kc = torch.zeros(total_pages, page, nkv, d)
+    kc = torch.zeros(total_pages, nkv, page, d)
     vc = torch.zeros_like(kc)
     kc.fill_(float("nan")), vc.fill_(float("nan"))              # reading a foreign slot shows
     blocks = max(-(-n // page) for n in lengths)
@@ -140,8 +146,8 @@ def paged_case(dtype, *, nq, nkv, d, page, lengths, queries, seed, boost=None):
         for b in range(-(-n // page)):
             tables[r, b] = order.pop()
             span = slice(b * page, min(n, (b + 1) * page))
-            kc[tables[r, b], : span.stop - span.start] = kr[span]
-            vc[tables[r, b], : span.stop - span.start] = vr[span]
+            kc[tables[r, b], :, : span.stop - span.start] = kr[span].transpose(0, 1)
+            vc[tables[r, b], :, : span.stop - span.start] = vr[span].transpose(0, 1)
         for p in range(n - queries[r], n):
             q_rows.append(torch.randn(nq, d, generator=g))
             token_row.append(r), positions.append(p)
@@ -232,7 +238,7 @@ def test_attention_refuses_sizes_it_does_not_take():
     from tinyvllm_b200.ops.kernels import KernelError
     def call(nq, nkv, d):
         ints = torch.zeros(1, dtype=torch.int32, device=DEV)
-        cache = torch.zeros(1, 4, nkv, d, device=DEV)
+        cache = torch.zeros(1, nkv, 4, d, device=DEV)
         return k().attention_rows(torch.zeros(1, nq * d, device=DEV), nq * d, cache, cache,
                                   ints.view(1, 1), ints, ints, num_q=nq, num_kv=nkv, head_dim=d,
                                   window=None, scale=1.0)
@@ -399,9 +405,9 @@ def test_attention_decode_fused(shape, window):
         rows.append(plain.causal_attention(want_q[r:r + 1], keys, values, d ** -0.5, window, dtype,
                                            q_positions=torch.tensor([p]))[0])
     close(got, torch.stack(rows), dtype, bf16=1.2e-2)
-    stored_k = kc.view(-1, nkv, d)[slots.long().to(DEV)]
+    stored_k = by_slot(kc)[slots.long().to(DEV)]
     close(stored_k, want_k, dtype, bf16=1.6e-2)
-    assert torch.equal(vc.view(-1, nkv, d)[slots.long().to(DEV)].float().cpu(), vn)
+    assert torch.equal(by_slot(vc)[slots.long().to(DEV)].float().cpu(), vn)
 
 
 def test_attention_decode_padding_and_unsupported():

@@ -43,8 +43,8 @@ def make_case(dtype, seed, *, nq=6, nkv=2, d=48, page=8, lengths=(700, 33, 300),
     g = torch.Generator().manual_seed(seed)
     pages = sum(-(-n // page) for n in lengths) + 2
     order = torch.randperm(pages, generator=g).tolist()
-    kc = torch.randn(pages, page, nkv, d, generator=g).to(dtype)
-    vc = torch.randn(pages, page, nkv, d, generator=g).to(dtype)
+    kc = torch.randn(pages, nkv, page, d, generator=g).to(dtype)
+    vc = torch.randn(pages, nkv, page, d, generator=g).to(dtype)
     blocks = max(-(-n // page) for n in lengths)
     tables = torch.zeros(len(lengths), blocks, dtype=torch.int32)
     token_row, positions = [], []

@@ -1,9 +1,11 @@
 """Device side of the cache: page tensors of every group and state arenas.
 
-Group ``g`` owns two tensors ``[runs_in_group, pages, page_size, kv_heads,
-head_dim]`` (keys, values) in the storage dtype; token ``p`` of a request lies
-at slot ``block_table[p // page_size] * page_size + p % page_size`` of every
-run of the group.  A run that declares fixed-size state owns an arena
+Group ``g`` owns two tensors ``[runs_in_group, pages, kv_heads, page_size,
+head_dim]`` (keys, values) in the storage dtype: the keys of one kv head in one
+page are contiguous, so a kernel that serves one kv head reads whole runs of
+memory.  Token ``p`` of a request lies in page ``block_table[p // page_size]``
+at offset ``p % page_size`` of every run of the group (its *slot* is
+``page * page_size + offset``).  A run that declares fixed-size state owns an arena
 ``[state_slots, *shape]``; a request's row is zeroed when the request starts.
 The reference keeps one pair of tensors ``[layers, blocks * block_size,
 kv_heads, head_dim]`` (tinyvllm/paged_kv.py:53-65).
@@ -68,7 +70,7 @@ class CacheStorage:
         self.pages_per_group = tuple(pages_per_group)
         self.keys, self.values = [], []
         for group, pages in zip(self.groups, self.pages_per_group):
-            shape = (len(group.runs), pages, page_size, group.num_kv_heads, group.head_dim)
+            shape = (len(group.runs), pages, group.num_kv_heads, page_size, group.head_dim)
             self.keys.append(torch.zeros(shape, dtype=dtype, device=device))
             self.values.append(torch.zeros(shape, dtype=dtype, device=device))
         self.state: dict[int, torch.Tensor] = {}
@@ -81,7 +83,7 @@ class CacheStorage:
         return self.where[run][0]
 
     def kv_of(self, run: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """Keys and values ``[pages, page_size, kv_heads, head_dim]`` of one run."""
+        """Keys and values ``[pages, kv_heads, page_size, head_dim]`` of one run."""
         group, index = self.where[run]
         return self.keys[group][index], self.values[group][index]
 

@@ -25,8 +25,8 @@
 
 namespace cg = cooperative_groups;
 
-#define DEC_WARPS 4
-#define DEC_UNROLL 4        // key rows a warp loads per stage and matrix
+#define DEC_WARPS 8
+#define DEC_UNROLL 2        // key rows a warp loads per stage and matrix
 #define DEC_STAGES 2        // stages of each warp's ring of keys and values in shared memory
 #define DEC_MAX_SPLITS 8
 
@@ -145,9 +145,10 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     const int sub = lane % LPK;                 // which 8 dimensions of a key this lane holds
     const int key_in_instr = lane / LPK;
     const int* table = block_tables + (int64_t)row * table_stride;
-    const int64_t row_stride = (int64_t)num_kv * HEAD_DIM;
-    const bf16* k_base = key_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
-    const bf16* v_base = value_cache + (int64_t)kv_head * HEAD_DIM + sub * 8;
+    // the cache is [pages, num_kv, page, head_dim]: a key's row for this kv head
+    const int64_t row_stride = HEAD_DIM;
+    const bf16* k_base = key_cache + sub * 8;
+    const bf16* v_base = value_cache + sub * 8;
 
     // The piece is walked in sub-tiles of WARP_KEYS keys; warp w takes sub-tiles w, w + 4, ...
     const int sub_tiles = last >= first ? (last - base) / WARP_KEYS + 1 : 0;
@@ -156,14 +157,14 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     int mine = first_tile < sub_tiles ? (sub_tiles - 1 - first_tile) / DEC_WARPS + 1 : 0;
     mine = min(mine, warp_slot_capacity / WARP_KEYS);     // the host sizes the list for the context limit
 
-    // cache slots of all keys of this warp, looked up once (-1: no key there)
+    // cache rows of all keys of this warp, looked up once (-1: no key there)
     int* my_slots = slot_s + warp * warp_slot_capacity;
     for (int e = lane; e < mine * WARP_KEYS; e += 32) {
         const int key = base + (first_tile + (e / WARP_KEYS) * DEC_WARPS) * WARP_KEYS + e % WARP_KEYS;
         int slot = -1;
         if (key >= first && key <= last) {
             const int page = table[key / page_size];
-            if (page >= 0) slot = page * page_size + key % page_size;
+            if (page >= 0) slot = (page * num_kv + kv_head) * page_size + key % page_size;
         }
         my_slots[e] = slot;
     }
@@ -212,8 +213,9 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         if (write_cache && (blockIdx.y % blocks_per_kv) == 0) {
             const int slot = slots[request];
             if (slot >= 0) {
-                bf16* kd = key_cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM;
-                bf16* vd = value_cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM;
+                const int64_t at = (((int64_t)(slot / page_size) * num_kv + kv_head) * page_size + slot % page_size) * HEAD_DIM;
+                bf16* kd = key_cache + at;
+                bf16* vd = value_cache + at;
                 for (int i = threadIdx.x; i < HEAD_DIM; i += blockDim.x) {
                     kd[i] = __float2bfloat16_rn(sh.k_new[i]);
                     vd[i] = __float2bfloat16_rn(sh.v_new[i]);
@@ -400,7 +402,7 @@ extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv
 }
 
 // qkv: [requests, (num_q + 2 num_kv) * head_dim] bfloat16, the raw projection of one token per
-// request.  weight_dtype: TVB_BF16 or TVB_F32 (norm weights; null pointers skip the norm).
+// request.  Caches: [pages, num_kv, page_size, head_dim].  weight_dtype: TVB_BF16 or TVB_F32 (norm weights; null pointers skip the norm).
 // splits (1..8) is the cluster size: the number of pieces every request's keys are cut into.
 // max_context bounds position + 1 of every request (it sizes the list of cache slots a warp keeps).
 extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,

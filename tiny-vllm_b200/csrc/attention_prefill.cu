@@ -67,7 +67,6 @@ prefill_attention_kernel(const bf16* __restrict__ q, int64_t q_token_stride,
     const int lo_first = window > 0 ? max(0, first_position - window + 1) : 0;
     const int key_begin = lo_first / PF_BN * PF_BN;
     const int tiles = (last_position - key_begin) / PF_BN + 1;
-    const int64_t cache_row = (int64_t)num_kv * HEAD_DIM;
 
     // ---- Q tile (rows past `count` are zero)
     for (int index = tid; index < PF_BM * CHUNKS; index += PF_WARPS * 32) {
@@ -78,13 +77,14 @@ prefill_attention_kernel(const bf16* __restrict__ q, int64_t q_token_stride,
     }
     cp_async_commit();
 
-    auto stage_slots = [&](int t, int buffer) {       // cache slot of each key of tile t, -1 if none
+    // row of each key of tile t in the cache [pages, num_kv, page, head_dim] for this kv head, -1 if none
+    auto stage_slots = [&](int t, int buffer) {
         if (tid < PF_BN) {
             const int key = key_begin + t * PF_BN + tid;
             int slot = -1;
             if (key <= last_position) {
                 const int page = table[key / page_size];
-                if (page >= 0) slot = page * page_size + key % page_size;
+                if (page >= 0) slot = (page * num_kv + kv_head) * page_size + key % page_size;
             }
             slot_s[buffer * PF_BN + tid] = slot;
         }
@@ -93,7 +93,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int64_t q_token_stride,
         for (int index = tid; index < PF_BN * CHUNKS; index += PF_WARPS * 32) {
             const int r = index / CHUNKS, c = index % CHUNKS;
             const int slot = slot_s[buffer * PF_BN + r];
-            const int64_t offset = (int64_t)max(slot, 0) * cache_row + (int64_t)kv_head * HEAD_DIM + c * 8;
+            const int64_t offset = (int64_t)max(slot, 0) * HEAD_DIM + c * 8;
             cp_async_16(k_s + (buffer * PF_BN + r) * ROW + c * 8, key_cache + offset, slot >= 0);
             cp_async_16(v_s + (buffer * PF_BN + r) * ROW + c * 8, value_cache + offset, slot >= 0);
         }

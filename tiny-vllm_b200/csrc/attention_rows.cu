@@ -3,7 +3,8 @@
 //
 // The query at position p of a request attends the keys lo..p of that request
 // (lo = max(0, p - window + 1) with a window, else 0) through the request's
-// block table: key j lies at slot table[j / page] * page + j % page.  Query head
+// block table: key j of kv head g lies at row (table[j / page] * num_kv + g) * page + j % page
+// of the cache [pages, num_kv, page, head_dim].  Query head
 // h reads kv head h / (num_q / num_kv) (tinyvllm/kernels/paged_decode.cu:120).
 // Scores, softmax and the output sum are float32 (:302-356, :457-465).
 //
@@ -94,15 +95,14 @@ __device__ __forceinline__ void attend_chunk(
     part.sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < ATTN_MAX_DIMS; ++i) part.out[i] = 0.0f;
-    const int64_t head_stride = (int64_t)num_kv * head_dim;
     for (int base = first - first % 32; base <= last; base += 32) {
         const int j = base + lane;
         const bool valid = j >= first && j <= last;
         int64_t slot = 0;
         float score = -INFINITY;
         if (valid) {
-            slot = (int64_t)table[j / page_size] * page_size + j % page_size;
-            const T* k = key_cache + slot * head_stride + (int64_t)kv_head * head_dim;
+            slot = ((int64_t)table[j / page_size] * num_kv + kv_head) * page_size + j % page_size;
+            const T* k = key_cache + slot * head_dim;
             score = __fmul_rn(dot_head<T>(q_shared, k, head_dim), scale);
         }
         const float tile_max = warp_max(score);          // at least one key of a tile is valid
@@ -116,7 +116,7 @@ __device__ __forceinline__ void attend_chunk(
         for (int jj = max(0, first - base); jj < count; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int64_t sj = __shfl_sync(0xffffffffu, slot, jj);
-            const T* v = value_cache + sj * head_stride + (int64_t)kv_head * head_dim;
+            const T* v = value_cache + sj * head_dim;
 #pragma unroll
             for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
                 const int dim = lane + 32 * i;

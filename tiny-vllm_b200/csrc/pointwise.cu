@@ -165,8 +165,9 @@ extern "C" int tvb_rope_table(const float* inv_freq, float* cos_out, float* sin_
 // ------------------------------------- q/k norm + rotation + cache write, fused
 // One warp per (token, head) over the packed projection row
 // [q heads | k heads | v heads].  q heads are normalised and rotated in place;
-// k heads are normalised, rotated and written to the key cache at the token's
-// slot; v heads are copied to the value cache.  Lane l holds the pairs
+// k heads are normalised, rotated and written to the key cache [pages, num_kv, page,
+// head_dim] at the token's slot (page * page_size + offset); v heads are copied to the
+// value cache.  Lane l holds the pairs
 // (j, j + d/2) for j = l, l + 32, ...  Null norm weights skip the norm, null
 // tables skip the rotation, null slots (or a negative slot) skip the writes.
 #define QK_MAX_PAIRS 4   // head_dim <= 256
@@ -177,7 +178,7 @@ __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ cos_table, const float* __restrict__ sin_table,
     const int* __restrict__ positions, const int* __restrict__ slots,
     T* __restrict__ key_cache, T* __restrict__ value_cache,
-    int tokens, int num_q, int num_kv, int head_dim, int table_positions, float eps) {
+    int tokens, int num_q, int num_kv, int head_dim, int page_size, int table_positions, float eps) {
     const int heads = num_q + 2 * num_kv;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= (int64_t)tokens * heads) return;
@@ -189,7 +190,8 @@ __global__ void qk_norm_rope_store_kernel(
 
     if (head >= num_q + num_kv) {            // a value head: plain copy
         if (slot < 0) return;
-        T* dst = value_cache + ((int64_t)slot * num_kv + (head - num_q - num_kv)) * head_dim;
+        T* dst = value_cache + (((int64_t)(slot / page_size) * num_kv + (head - num_q - num_kv)) * page_size +
+                                slot % page_size) * head_dim;
         for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
         return;
     }
@@ -225,7 +227,9 @@ __global__ void qk_norm_rope_store_kernel(
             }
         }
     }
-    T* dst = is_key ? key_cache + ((int64_t)slot * num_kv + (head - num_q)) * head_dim : src;
+    T* dst = is_key ? key_cache + (((int64_t)(slot / page_size) * num_kv + (head - num_q)) * page_size +
+                                   slot % page_size) * head_dim
+                    : src;
     int position = positions[token];
     if (position < 0) position = 0;
     if (position >= table_positions) position = table_positions - 1;   // the host refuses these
@@ -251,13 +255,13 @@ __global__ void qk_norm_rope_store_kernel(
 template <typename T, typename W>
 static int launch_qk(void* qkv, const void* qw, const void* kw, const float* cos_table,
                      const float* sin_table, const int* positions, const int* slots, void* key_cache,
-                     void* value_cache, int tokens, int num_q, int num_kv, int head_dim,
+                     void* value_cache, int tokens, int num_q, int num_kv, int head_dim, int page_size,
                      int table_positions, float eps, cudaStream_t s) {
     const int64_t rows = (int64_t)tokens * (num_q + 2 * num_kv);
     const int warps = 4;
     qk_norm_rope_store_kernel<T, W><<<(unsigned)((rows + warps - 1) / warps), warps * 32, 0, s>>>(
         (T*)qkv, (const W*)qw, (const W*)kw, cos_table, sin_table, positions, slots, (T*)key_cache,
-        (T*)value_cache, tokens, num_q, num_kv, head_dim, table_positions, eps);
+        (T*)value_cache, tokens, num_q, num_kv, head_dim, page_size, table_positions, eps);
     return tvb_last_error();
 }
 
@@ -265,24 +269,25 @@ extern "C" int tvb_qk_norm_rope_store(void* qkv, const void* q_weight, const voi
                                       const float* cos_table, const float* sin_table,
                                       const int* positions, const int* slots, void* key_cache,
                                       void* value_cache, int tokens, int num_q, int num_kv,
-                                      int head_dim, int table_positions, float eps, int dtype,
-                                      int weight_dtype, void* stream) {
+                                      int head_dim, int page_size, int table_positions, float eps,
+                                      int dtype, int weight_dtype, void* stream) {
     if (tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim % 2 || head_dim > 64 * QK_MAX_PAIRS || num_q <= 0 || num_kv < 0)
+    if (head_dim <= 0 || head_dim % 2 || head_dim > 64 * QK_MAX_PAIRS || num_q <= 0 || num_kv < 0 ||
+        (slots && page_size <= 0))
         return TVB_BAD_ARGUMENT;
     if ((int64_t)tokens * (num_q + 2 * num_kv) / 4 + 1 > 2147483647LL) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == TVB_F32 && weight_dtype == TVB_F32)
         return launch_qk<float, float>(qkv, q_weight, k_weight, cos_table, sin_table, positions, slots,
-                                       key_cache, value_cache, tokens, num_q, num_kv, head_dim,
+                                       key_cache, value_cache, tokens, num_q, num_kv, head_dim, page_size,
                                        table_positions, eps, s);
     if (dtype == TVB_BF16 && weight_dtype == TVB_BF16)
         return launch_qk<bf16, bf16>(qkv, q_weight, k_weight, cos_table, sin_table, positions, slots,
-                                     key_cache, value_cache, tokens, num_q, num_kv, head_dim,
+                                     key_cache, value_cache, tokens, num_q, num_kv, head_dim, page_size,
                                      table_positions, eps, s);
     if (dtype == TVB_BF16 && weight_dtype == TVB_F32)
         return launch_qk<bf16, float>(qkv, q_weight, k_weight, cos_table, sin_table, positions, slots,
-                                      key_cache, value_cache, tokens, num_q, num_kv, head_dim,
+                                      key_cache, value_cache, tokens, num_q, num_kv, head_dim, page_size,
                                       table_positions, eps, s);
     return TVB_BAD_ARGUMENT;
 }

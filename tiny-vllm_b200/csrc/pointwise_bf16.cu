@@ -119,7 +119,7 @@ qk_norm_rope_store_bf16_kernel(bf16* __restrict__ qkv, const W* __restrict__ q_w
                                const float* __restrict__ sin_table, const int* __restrict__ positions,
                                const int* __restrict__ slots, bf16* __restrict__ key_cache,
                                bf16* __restrict__ value_cache, int tokens, int num_q, int num_kv,
-                               int table_positions, float eps) {
+                               int page_size, int table_positions, float eps) {
     constexpr int HALF = HEAD_DIM / 2;
     constexpr int LANES = HEAD_DIM / 8;
     const int heads = num_q + 2 * num_kv;
@@ -152,7 +152,8 @@ qk_norm_rope_store_bf16_kernel(bf16* __restrict__ qkv, const W* __restrict__ q_w
         if (slot < 0) return;
         bf16* cache = is_value ? value_cache : key_cache;
         const int kv_head = is_value ? head - num_q - num_kv : head - num_q;
-        dst = cache + ((int64_t)slot * num_kv + kv_head) * HEAD_DIM + 4 * lane;
+        dst = cache + (((int64_t)(slot / page_size) * num_kv + kv_head) * page_size + slot % page_size) * HEAD_DIM +
+              4 * lane;
     }
     if (!is_value) {
         if (weight) {
@@ -191,10 +192,11 @@ extern "C" int tvb_qk_norm_rope_store_bf16(void* qkv, const void* q_weight, cons
                                            const float* cos_table, const float* sin_table,
                                            const int* positions, const int* slots, void* key_cache,
                                            void* value_cache, int tokens, int num_q, int num_kv,
-                                           int head_dim, int table_positions, float eps,
+                                           int head_dim, int page_size, int table_positions, float eps,
                                            int weight_dtype, void* stream) {
     if (tokens <= 0) return 0;
-    if (!tvb_qk_norm_rope_store_bf16_supports(head_dim) || num_q <= 0 || num_kv < 0) return TVB_BAD_ARGUMENT;
+    if (!tvb_qk_norm_rope_store_bf16_supports(head_dim) || num_q <= 0 || num_kv < 0 || (slots && page_size <= 0))
+        return TVB_BAD_ARGUMENT;
     const int64_t threads = (int64_t)tokens * (num_q + 2 * num_kv) * (head_dim / 8);
     const int64_t blocks = (threads + 255) / 256;
     if (blocks > 2147483647LL) return TVB_BAD_ARGUMENT;
@@ -202,7 +204,7 @@ extern "C" int tvb_qk_norm_rope_store_bf16(void* qkv, const void* q_weight, cons
 #define QK_LAUNCH(D, WT)                                                                                   \
     qk_norm_rope_store_bf16_kernel<D, WT><<<(unsigned)blocks, 256, 0, s>>>(                                \
         (bf16*)qkv, (const WT*)q_weight, (const WT*)k_weight, cos_table, sin_table, positions, slots,      \
-        (bf16*)key_cache, (bf16*)value_cache, tokens, num_q, num_kv, table_positions, eps)
+        (bf16*)key_cache, (bf16*)value_cache, tokens, num_q, num_kv, page_size, table_positions, eps)
 #define QK_BY_DIM(WT)                                     \
     do {                                                  \
         if (head_dim == 16) QK_LAUNCH(16, WT);            \

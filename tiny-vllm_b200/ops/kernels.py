@@ -196,8 +196,9 @@ def qk_norm_rope_store(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: 
                        value_cache: torch.Tensor | None) -> None:
     """In place on the packed projection [tokens, (num_q + 2 num_kv) * head_dim]: q heads are
     normalised and rotated where they stand; k heads are normalised, rotated and written to
-    ``key_cache`` at ``slots``; v heads are copied to ``value_cache``.  Caches are
-    [pages, page_size, num_kv, head_dim]; without ``slots`` nothing is written."""
+    ``key_cache`` at ``slots`` (page * page_size + offset); v heads are copied to
+    ``value_cache``.  Caches are [pages, num_kv, page_size, head_dim]; without ``slots``
+    nothing is written."""
     _need_cuda(qkv, positions, q_weight, k_weight, cos, sin, slots, key_cache, value_cache)
     tokens = qkv.shape[0]
     if qkv.dim() != 2 or not qkv.is_contiguous() or qkv.shape[1] != (num_q + 2 * num_kv) * head_dim:
@@ -219,25 +220,28 @@ def qk_norm_rope_store(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: 
             raise KernelError("qk_norm_rope_store: tables must be float32 [positions, head_dim / 2]")
         table_positions = cos.shape[0]
     if slots is not None:
-        want = key_cache.shape[2:] if key_cache is not None else None
         if (slots.dtype != torch.int32 or slots.shape != (tokens,) or key_cache is None
-                or value_cache is None or tuple(want) != (num_kv, head_dim)
+                or value_cache is None or key_cache.dim() != 4
+                or (key_cache.shape[1], key_cache.shape[3]) != (num_kv, head_dim)
                 or key_cache.dtype != qkv.dtype or value_cache.shape != key_cache.shape
                 or not key_cache.is_contiguous() or not value_cache.is_contiguous()):
             raise KernelError("qk_norm_rope_store: slots int32 [tokens]; caches contiguous "
-                              "[pages, page_size, num_kv, head_dim] of the dtype of qkv")
+                              "[pages, num_kv, page_size, head_dim] of the dtype of qkv")
+    page_size = key_cache.shape[2] if slots is not None else 0
     if qkv.dtype == torch.bfloat16 and head_dim in (16, 32, 64, 128, 256):
         fn = _fn("pointwise_bf16", "tvb_qk_norm_rope_store_bf16",
-                 [c_void_p] * 9 + [c_int] * 5 + [c_float, c_int, c_void_p])
+                 [c_void_p] * 9 + [c_int] * 6 + [c_float, c_int, c_void_p])
         _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
                   positions.data_ptr(), _ptr(slots), _ptr(key_cache), _ptr(value_cache), tokens, num_q,
-                  num_kv, head_dim, table_positions, eps, weight_tag, _stream()), "qk_norm_rope_store")
+                  num_kv, head_dim, page_size, table_positions, eps, weight_tag, _stream()),
+               "qk_norm_rope_store")
         return
     fn = _fn("pointwise", "tvb_qk_norm_rope_store",
-             [c_void_p] * 9 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p])
+             [c_void_p] * 9 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p])
     _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
               positions.data_ptr(), _ptr(slots), _ptr(key_cache), _ptr(value_cache), tokens, num_q,
-              num_kv, head_dim, table_positions, eps, dtype_tag(qkv.dtype), weight_tag, _stream()),
+              num_kv, head_dim, page_size, table_positions, eps, dtype_tag(qkv.dtype), weight_tag,
+              _stream()),
            "qk_norm_rope_store")
 
 
@@ -272,10 +276,10 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
     if head_dim > 256 or num_q % num_kv:
         raise KernelError(f"attention_rows takes head sizes up to 256 and whole groups "
                           f"(head_dim {head_dim}, {num_q} / {num_kv} heads)")
-    if key_cache.dim() != 4 or tuple(key_cache.shape[2:]) != (num_kv, head_dim) or \
+    if key_cache.dim() != 4 or (key_cache.shape[1], key_cache.shape[3]) != (num_kv, head_dim) or \
             value_cache.shape != key_cache.shape or key_cache.dtype != q.dtype or \
             not key_cache.is_contiguous() or not value_cache.is_contiguous():
-        raise KernelError("attention_rows: caches must be contiguous [pages, page_size, num_kv, head_dim]")
+        raise KernelError("attention_rows: caches must be contiguous [pages, num_kv, page_size, head_dim]")
     for name, t in (("block_tables", block_tables), ("token_row", token_row), ("positions", positions)):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError(f"attention_rows: {name} must be contiguous int32")
@@ -293,7 +297,7 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
     _check(fn(q.data_ptr(), q_token_stride, key_cache.data_ptr(), value_cache.data_ptr(),
               block_tables.data_ptr(), block_tables.shape[1], token_row.data_ptr(),
               positions.data_ptr(), out.data_ptr(), _ptr(scratch), max_chunks, tokens, num_q, num_kv,
-              head_dim, key_cache.shape[1], window or 0, scale, dtype_tag(q.dtype), _stream()),
+              head_dim, key_cache.shape[2], window or 0, scale, dtype_tag(q.dtype), _stream()),
            "attention_rows", 2 if max_chunks > 0 else 1)
     return out
 
@@ -367,10 +371,11 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     if not attention_decode_supports(head_dim, num_q, num_kv, splits):
         raise KernelError(f"attention_decode does not take head_dim {head_dim}, {num_q}/{num_kv} heads, "
                           f"{splits} splits")
-    if key_cache.dtype != torch.bfloat16 or tuple(key_cache.shape[2:]) != (num_kv, head_dim) or \
+    if key_cache.dtype != torch.bfloat16 or key_cache.dim() != 4 or \
+            (key_cache.shape[1], key_cache.shape[3]) != (num_kv, head_dim) or \
             value_cache.shape != key_cache.shape or not key_cache.is_contiguous():
         raise KernelError("attention_decode: caches must be contiguous bfloat16 "
-                          "[pages, page_size, num_kv, head_dim]")
+                          "[pages, num_kv, page_size, head_dim]")
     for t in (positions, token_row, block_tables) + ((slots,) if slots is not None else ()):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError("attention_decode: index tensors must be contiguous int32")
@@ -391,7 +396,7 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos), _ptr(sin), table_positions,
               positions.data_ptr(), token_row.data_ptr(), _ptr(slots), key_cache.data_ptr(),
               value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
-              key_cache.shape[1], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
+              key_cache.shape[2], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
               splits, 1 if slots is not None else 0, max_context, weight_tag, _pdl("attention"),
               _stream()),
            "attention_decode")
@@ -426,9 +431,10 @@ def attention_prefill(q: torch.Tensor, q_token_stride: int, key_cache: torch.Ten
         raise KernelError("attention_prefill is a bfloat16 kernel")
     if not attention_prefill_supports(head_dim, num_q, num_kv):
         raise KernelError(f"attention_prefill does not take head_dim {head_dim}, {num_q}/{num_kv} heads")
-    if tuple(key_cache.shape[2:]) != (num_kv, head_dim) or value_cache.shape != key_cache.shape or \
-            not key_cache.is_contiguous() or not value_cache.is_contiguous():
-        raise KernelError("attention_prefill: caches must be contiguous [pages, page_size, num_kv, head_dim]")
+    if key_cache.dim() != 4 or (key_cache.shape[1], key_cache.shape[3]) != (num_kv, head_dim) or \
+            value_cache.shape != key_cache.shape or not key_cache.is_contiguous() or \
+            not value_cache.is_contiguous():
+        raise KernelError("attention_prefill: caches must be contiguous [pages, num_kv, page_size, head_dim]")
     for t in (block_tables, positions, tile_row, tile_first, tile_count):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError("attention_prefill: index tensors must be contiguous int32")
@@ -441,7 +447,7 @@ def attention_prefill(q: torch.Tensor, q_token_stride: int, key_cache: torch.Ten
     _check(fn(q.data_ptr(), q_token_stride, key_cache.data_ptr(), value_cache.data_ptr(),
               block_tables.data_ptr(), block_tables.shape[1], positions.data_ptr(), tile_row.data_ptr(),
               tile_first.data_ptr(), tile_count.data_ptr(), out.data_ptr(), tiles, num_q, num_kv,
-              head_dim, key_cache.shape[1], window or 0, scale, _stream()), "attention_prefill")
+              head_dim, key_cache.shape[2], window or 0, scale, _stream()), "attention_prefill")
     return out
 
 
