@@ -43,7 +43,7 @@ def test_plan_commit_tables_and_slots():
     plan = m.plan([("r", 6)])
     entry = plan.entries[0]
     assert entry.start == 0 and entry.count == 6 and entry.fresh_state
-    table = entry.tables[0]
+    table = list(entry.tables[0])                   # a copy: the plan hands out the live table
     assert len(table) == 2
     assert entry.slots[0] == tuple(table[p // 4] * 4 + p % 4 for p in range(6))
     assert m.length("r") == 0                       # not yet committed

@@ -139,7 +139,8 @@ class PlannedEntry:
     state_slot: int
     fresh_state: bool                         # first tokens of the request: state starts at zero
     slots: tuple[tuple[int, ...], ...]        # per group: cache slot of each new token
-    tables: tuple[tuple[int, ...], ...]       # per group: block table after the step
+    tables: tuple                             # per group: the request's block table (the live list:
+                                              # read it before the step is committed, do not change it)
 
 
 @dataclass
@@ -257,12 +258,18 @@ class CacheManager:
                     taken.append((group, request_id, pages))
                     request.tables[group].extend(pages)
                 table = request.tables[group]
-                positions = range(request.length, request.length + count)
-                row = tuple(table[p // size] * size + p % size for p in positions)
-                if any(table[p // size] < 0 for p in positions):
-                    raise CacheError("a token would be written to a page already given back")
+                if count == 1:
+                    p = request.length
+                    if table[p // size] < 0:
+                        raise CacheError("a token would be written to a page already given back")
+                    row = (table[p // size] * size + p % size,)
+                else:
+                    positions = range(request.length, request.length + count)
+                    row = tuple(table[p // size] * size + p % size for p in positions)
+                    if any(table[p // size] < 0 for p in positions):
+                        raise CacheError("a token would be written to a page already given back")
                 slots.append(row)
-                tables.append(tuple(table))
+                tables.append(table)
             request.planned = True
             entries.append(PlannedEntry(
                 request_id, request.length, count, request.state_slot,

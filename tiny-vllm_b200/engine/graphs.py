@@ -43,6 +43,8 @@ class _Bucket:
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits = None
         self.launches = 0
+        # per group and row: (request, entries written, leading entries given back) of the last step
+        self.row_tables = [[None] * size for _ in range(groups)]
         self.copied: torch.cuda.Event | None = None      # the last upload has left the pinned buffer
 
     def host_view(self, i: int) -> np.ndarray:
@@ -145,20 +147,43 @@ class DecodeGraphs:
             return None
         if bucket.copied is not None:
             bucket.copied.synchronize()
-        self._fill_padding(bucket)
-        self.runner.storage.clear_state([p.state_slot for p in plan.entries if p.fresh_state])
+        planned = plan.entries
+        self.runner.storage.clear_state([p.state_slot for p in planned if p.fresh_state])
         groups = len(self.runner.manager.groups)
-        for r, (entry, planned) in enumerate(zip(entries, plan.entries)):
-            bucket.host_view(0)[r] = entry.tokens[0]
-            bucket.host_view(1)[r] = planned.start
-            bucket.host_view(2)[r] = r
-            bucket.host_view(4)[r] = planned.state_slot
-            for g in range(groups):
-                bucket.host_view(6 + 2 * g)[r] = planned.slots[g][0]
-                table = planned.tables[g]
-                bucket.host_view(7 + 2 * g)[r * bucket.blocks[g]:r * bucket.blocks[g] + len(table)] = table
-        packed = bucket.host_view(len(bucket.sizes) - 1).reshape(ROW_WORDS, bucket.size)
-        packed[:] = pack_rows(params, draws, capacity=bucket.size)
+        # per-row fields, one array assignment each; rows past the step are padding
+        size = bucket.size
+        bucket.host_view(0)[:rows] = [entry.tokens[0] for entry in entries]
+        bucket.host_view(0)[rows:] = 0
+        bucket.host_view(1)[:rows] = [p.start for p in planned]
+        bucket.host_view(1)[rows:] = -1
+        bucket.host_view(2)[:rows] = np.arange(rows)
+        bucket.host_view(2)[rows:] = -1
+        bucket.host_view(4)[:rows] = [p.state_slot for p in planned]
+        for g in range(groups):
+            bucket.host_view(6 + 2 * g)[:rows] = [p.slots[g][0] for p in planned]
+            bucket.host_view(6 + 2 * g)[rows:] = -1
+            # block tables stay in the buffer from step to step: a row whose request is the one of
+            # the step before only gets the entries that were added or given back since
+            tables = bucket.host_view(7 + 2 * g).reshape(size, bucket.blocks[g])
+            known = bucket.row_tables[g]
+            for r, p in enumerate(planned):
+                table = p.tables[g]
+                before = known[r]
+                if before is None or before[0] != p.request_id or before[1] > len(table):
+                    tables[r, :len(table)] = table
+                    first_live = 0
+                else:
+                    tables[r, before[1]:len(table)] = table[before[1]:]
+                    first_live = before[2]
+                # pages a window gave back read -1 from the first live entry backwards
+                while first_live < len(table) and table[first_live] < 0:
+                    tables[r, first_live] = -1
+                    first_live += 1
+                known[r] = (p.request_id, len(table), first_live)
+            for r in range(rows, size):
+                known[r] = None
+        packed = bucket.host_view(len(bucket.sizes) - 1).reshape(ROW_WORDS, size)
+        packed[:] = pack_rows(params, draws, capacity=size)
         bucket.device.copy_(bucket.host, non_blocking=True)
         bucket.copied = torch.cuda.Event()
         bucket.copied.record()

@@ -190,6 +190,8 @@ class Scheduler:
     def _admit(self, now_ns: int) -> list[int]:
         """Waiting requests that fit now, in arrival order; those that do not are skipped."""
         admitted = []
+        if not self.waiting:
+            return admitted
         groups = range(len(self.cache.groups))
         room = [self.cache.free_pages(g) - self._outstanding(g) for g in groups]
         slots = min(self.cache.slots.free_count,

@@ -26,16 +26,19 @@ def pack_rows(params: Sequence[SamplingParams], draws: Sequence[int], capacity: 
     rows = len(params)
     capacity = capacity or rows
     packed = np.zeros((ROW_WORDS, capacity), dtype=np.int32)
-    temperature = np.zeros(capacity, dtype=np.float32)
-    top_p = np.ones(capacity, dtype=np.float32)
-    for i, (p, draw) in enumerate(zip(params, draws)):
-        temperature[i] = p.temperature
-        top_p[i] = p.top_p
-        packed[2, i] = min(p.top_k, 2**31 - 1)
-        packed[3:7, i] = np.array([p.seed & 0xFFFFFFFF, p.seed >> 32, draw & 0xFFFFFFFF, draw >> 32],
-                                  dtype=np.uint32).view(np.int32)
-    packed[0] = temperature.view(np.int32)
-    packed[1] = top_p.view(np.int32)
+    packed[1] = np.ones(capacity, dtype=np.float32).view(np.int32)
+    if rows == 0:
+        return packed
+    packed[0, :rows] = np.array([p.temperature for p in params], dtype=np.float32).view(np.int32)
+    packed[1, :rows] = np.array([p.top_p for p in params], dtype=np.float32).view(np.int32)
+    packed[2, :rows] = np.minimum(np.array([p.top_k for p in params], dtype=np.int64), 2**31 - 1)
+    seeds = np.array([p.seed for p in params], dtype=np.uint64)
+    counts = np.array(list(draws), dtype=np.uint64)
+    low = np.uint64(0xFFFFFFFF)
+    packed[3, :rows] = (seeds & low).astype(np.uint32).view(np.int32)
+    packed[4, :rows] = (seeds >> np.uint64(32)).astype(np.uint32).view(np.int32)
+    packed[5, :rows] = (counts & low).astype(np.uint32).view(np.int32)
+    packed[6, :rows] = (counts >> np.uint64(32)).astype(np.uint32).view(np.int32)
     return packed
 
 
