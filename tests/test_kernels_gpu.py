@@ -444,6 +444,55 @@ def test_gemm_small_m(shape):
         close(gate_up, plain.swiglu(want, torch.bfloat16), torch.bfloat16, bf16=1e-2)
 
 
+@pytest.mark.parametrize("tile", [0, 128, 256])
+@pytest.mark.parametrize("shape", [(128, 64, 128), (200, 72, 272), (333, 136, 400), (1000, 1032, 784),
+                                   (4099, 512, 1024)])
+def test_gemm_tc(shape, tile):
+    """The tcgen05 product alone: tiles cut by m, n and k edges, both tile widths, several tiles
+    per CTA (the last shape has more tiles than SMs), plain and with the activation."""
+    m, kk, n = shape
+    torch.manual_seed(m + n)
+    x, w = (torch.randn(m, kk) * 0.5).bfloat16(), (torch.randn(n, kk) * 0.05).bfloat16()
+    # make one row and one column stand out, so that a tile written to the wrong place shows
+    x[m // 2] *= 4
+    w[n // 3] *= 4
+    want = x.float() @ w.float().T
+    got = k().gemm_tc(x.to(DEV), w.to(DEV), 0, tile_n=tile)
+    assert got.dtype == torch.bfloat16 and got.shape == (m, n)
+    assert k().gemm_tc_status() == 0
+    close(got, want, torch.bfloat16, bf16=5e-3)
+    gate_up = k().gemm_tc(x.to(DEV), w.to(DEV), 2, tile_n=tile)
+    assert gate_up.shape == (m, n // 2)
+    assert k().gemm_tc_status() == 0
+    close(gate_up, plain.swiglu(want, torch.bfloat16), torch.bfloat16, bf16=1e-2)
+    # into a view with a row stride of its own, beside columns that must stay as they are
+    wide = torch.full((m, n + 16), 7.0, dtype=torch.bfloat16, device=DEV)
+    k().gemm_tc(x.to(DEV), w.to(DEV), 0, out=wide[:, 8:n + 8], tile_n=tile)
+    assert torch.equal(wide[:, 8:n + 8], got)
+    assert bool((wide[:, :8] == 7).all()) and bool((wide[:, n + 8:] == 7).all())
+
+
+def test_gemm_tc_rows_do_not_depend_on_the_batch():
+    torch.manual_seed(5)
+    x, w = torch.randn(700, 256).bfloat16().to(DEV), (torch.randn(384, 256) * 0.05).bfloat16().to(DEV)
+    whole = k().gemm_tc(x, w, 0)
+    part = k().gemm_tc(x[300:500], w, 0)
+    assert torch.equal(whole[300:500], part)
+    assert k().gemm_tc_status() == 0
+
+
+def test_gemm_tc_refuses():
+    from tinyvllm_b200.ops.kernels import KernelError
+    with pytest.raises(KernelError, match="multiples of 8"):
+        k().gemm_tc(torch.zeros(128, 60, dtype=torch.bfloat16, device=DEV),
+                    torch.zeros(16, 60, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(KernelError, match="multiples of 8"):
+        k().gemm_tc(torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV),
+                    torch.zeros(12, 64, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(KernelError, match="bfloat16"):
+        k().gemm_tc(torch.zeros(128, 64, device=DEV), torch.zeros(16, 64, device=DEV))
+
+
 def test_gemm_small_m_refuses():
     from tinyvllm_b200.ops.kernels import KernelError
     with pytest.raises(KernelError, match="up to 32 rows"):

@@ -20,6 +20,7 @@ from typing import Sequence
 import torch
 
 from ..config.engine import EngineConfig
+from ..ops import kernels
 from ..config.registry import read_model_config
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -217,6 +218,7 @@ class Engine:
         if tokens_device is None:
             return {}
         host = tokens_device.tolist()              # the step's one device-to-host read
+        kernels.check_finished_launches()
         return dict(zip(sample_ids, host))
 
     # ------------------------------------------------------------- generate

@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from ..config.registry import read_model_config
+from ..ops import kernels
 from .model import Model
 from .step import StepEntry, StepRunner
 
@@ -55,6 +56,7 @@ def replay(runner: StepRunner, lines, out_dir: Path, *, report=print) -> None:
             logits = runner.run(entries)
             if logits is not None:
                 array = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
+                kernels.check_finished_launches()
                 array.tofile(out_dir / f"{step}.f32")
         for request_id in record.get("end", []):
             if runner.manager.is_open(request_id):

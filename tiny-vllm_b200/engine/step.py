@@ -167,7 +167,9 @@ class StepRunner:
         groups = len(self.manager.groups)
         blocks = [max(1, max(len(p.tables[g]) for p in plan.entries)) for g in range(groups)]
         decode_only = all(count == 1 for count in counts)
-        tile_lists = ([], [], []) if decode_only else attention_ops.prefill_tiles(counts)
+        # only the bfloat16 tile kernel reads tile lists; the 32-bit path walks rows
+        tiled = not decode_only and self.storage.dtype == torch.bfloat16
+        tile_lists = attention_ops.prefill_tiles(counts) if tiled else ([], [], [])
         sizes = [tokens, tokens, tokens, wanted, rows, rows + 1]
         for g in range(groups):
             sizes += [tokens, rows * blocks[g]]
@@ -219,9 +221,9 @@ class StepRunner:
             cache_sources=self.cache_sources, max_position=max_position, split_chunks=split_chunks,
             workspace_of=self._workspace_of, decode_only=decode_only,
             decode_splits=self.decode_splits, max_context=self.max_model_len,
-            tile_row=None if decode_only else dview(tiles_at),
-            tile_first=None if decode_only else dview(tiles_at + 1),
-            tile_count=None if decode_only else dview(tiles_at + 2),
+            tile_row=dview(tiles_at) if tiled else None,
+            tile_first=dview(tiles_at + 1) if tiled else None,
+            tile_count=dview(tiles_at + 2) if tiled else None,
             host_rows=tuple((p.request_id, p.start, p.count, p.state_slot, p.fresh_state)
                             for p in plan.entries),
         )

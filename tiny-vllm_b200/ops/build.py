@@ -33,9 +33,7 @@ NVCC_FLAGS = (
     "--shared", "-Xcompiler", "-fPIC",
 )
 # libraries and the other linker inputs some sources need
-EXTRA_LINK = {
-    "gemm_tc": ("-lcuda",),
-}
+EXTRA_LINK: dict[str, tuple[str, ...]] = {}
 
 _lock = threading.Lock()
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -1,8 +1,10 @@
 """bfloat16 matrix products: which kernel takes which shape.
 
-Up to 32 rows (decode): the package's weight-streaming kernel.  More rows: cuBLAS
-through ``torch.nn.functional.linear``, the library call the reference's engine makes
-for every projection (tinyvllm/layers.py:84-85).
+Up to 32 rows (decode): the package's weight-streaming kernel.  The packed gate/up product
+with its activation at 128 rows and more (prefill): the package's tcgen05 kernel, which keeps
+the accumulator in tensor memory and applies SiLU(gate) * up on the way out.  The other
+products with more than 32 rows: cuBLAS through ``torch.nn.functional.linear``, the library
+call the reference's engine makes for every projection (tinyvllm/layers.py:84-85).
 """
 
 from __future__ import annotations
@@ -26,6 +28,10 @@ def chain_weights(weights) -> None:
 
 def next_weight(weight: torch.Tensor) -> torch.Tensor | None:
     return _next_weight.get(weight.data_ptr())
+
+
+# rows from which the tcgen05 kernel's tiles of 128 rows are mostly full
+TC_MIN_ROWS = 128
 
 
 def small(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -61,4 +67,6 @@ def linear_silu_bf16(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Ten
     """silu(x . gate^T) * (x . up^T) for a packed [gate | up] weight."""
     if small(x, gate_up_weight):
         return kernels.gemm_small_m(x, gate_up_weight, kernels.GEMM_SILU, prefetch=next_weight(gate_up_weight))
+    if x.shape[0] >= TC_MIN_ROWS and kernels.gemm_tc_takes(x, gate_up_weight, kernels.GEMM_SILU):
+        return kernels.gemm_tc(x, gate_up_weight, kernels.GEMM_SILU)
     return kernels.silu_mul(torch.nn.functional.linear(x, gate_up_weight))

@@ -517,3 +517,66 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
 def gemm_small_m_takes_norm(m: int, k: int) -> bool:
     """Whether the normalised rows [m rounded up to 8, k] fit into the kernel's shared memory."""
     return m <= SMALL_M_MAX_ROWS and k % 8 == 0 and (-(-m // 8) * 8) * (k + 32) * 2 <= 160 * 1024
+
+
+# ------------------------------------------- tcgen05 matrix product (many rows)
+def gemm_tc_takes(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16) -> bool:
+    """Whether :func:`gemm_tc` takes this product: bfloat16, rows contiguous and 16-byte aligned,
+    k and n multiples of 8."""
+    if (x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2
+            or x.shape[1] != w.shape[1] or x.stride(1) != 1 or w.stride(1) != 1):
+        return False
+    rows = w.shape[0]
+    if mode == GEMM_SILU and rows % 2:
+        return False
+    n = rows // 2 if mode == GEMM_SILU else rows
+    return (mode in (GEMM_BF16, GEMM_SILU) and x.shape[1] % 8 == 0 and n % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *, out: torch.Tensor | None = None,
+            tile_n: int = 0) -> torch.Tensor:
+    """x [m, k] . w [n, k]^T in bfloat16 on the tcgen05 tensor cores (float32 accumulation in
+    tensor memory).  GEMM_BF16: [m, n]; GEMM_SILU: w is [gate | up] with 2 n rows, the result is
+    silu(x . gate^T) * (x . up^T) [m, n].  ``tile_n`` 128 or 256 forces the width of a tile."""
+    _need_cuda(x, w)
+    if not gemm_tc_takes(x, w, mode):
+        raise KernelError("gemm_tc wants bfloat16 x [m, k] and w [n, k] with contiguous, 16-byte "
+                          "aligned rows, k and n multiples of 8")
+    m, k = x.shape
+    n = w.shape[0] // 2 if mode == GEMM_SILU else w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    elif (out.dtype != torch.bfloat16 or out.shape != (m, n) or out.stride(1) != 1 or out.stride(0) % 8
+          or out.data_ptr() % 16):
+        raise KernelError("gemm_tc: out must be bfloat16 [m, n] with 16-byte aligned rows")
+    fn = _fn("gemm_tc", "tvb_gemm_tc",
+             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
+              c_int, c_int, c_int, c_void_p])
+    global _gemm_tc_unchecked
+    _check(fn(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+              m, n, k, mode, tile_n, _pdl("gemm"), _stream()), "gemm_tc")
+    _gemm_tc_unchecked = True
+    return out
+
+
+_gemm_tc_unchecked = False
+
+
+def gemm_tc_status() -> int:
+    """0, or which bounded wait of a gemm_tc launch gave up since the last call (the results of
+    that launch are not valid).  Synchronises the device; reading clears the record."""
+    global _gemm_tc_unchecked
+    _gemm_tc_unchecked = False
+    return _fn("gemm_tc", "tvb_gemm_tc_status", [])()
+
+
+def check_finished_launches() -> None:
+    """Call after a step's results have reached the host: raises if a kernel with bounded waits
+    gave up in a launch since the last call.  Costs nothing when no such kernel was launched."""
+    if _gemm_tc_unchecked:
+        status = gemm_tc_status()
+        if status:
+            raise KernelError(f"gemm_tc: a wait inside the kernel ran out (code {status}); "
+                              "the results of this step are not valid")
