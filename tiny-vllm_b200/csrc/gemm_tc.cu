@@ -16,12 +16,10 @@
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT_CYCLES the waiting thread records which
 // wait gave up in tvb_gemm_tc_status, raises the CTA's abort flag, every role leaves its loop,
 // the CTA waits a fixed time for copies still in flight, frees its tensor memory and returns.
-#include <cuda.h>
-
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
+#include "tc5.cuh"
 
 namespace {
 
@@ -30,7 +28,6 @@ constexpr int BK = 64;                  // 64 bfloat16 = 128 bytes = one swizzle
 constexpr int UMMA_K = 16;              // k of one tcgen05.mma.kind::f16
 constexpr int THREADS = 192;            // warp 0 copies, warp 1 issues, warps 2..5 epilogue
 constexpr int EPILOGUE_WARPS = 4;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about a second of SM clock
 constexpr int STAGE_BUDGET = 196608;    // bytes of operand stages
 
 enum { MODE_BF16 = 0, MODE_SILU = 2 };
@@ -48,104 +45,8 @@ template <int BN> struct Tile {
     static constexpr int SHARED_BYTES = STAGES * STAGE_BYTES + BARRIERS * 8 + 16 + 1024;
 };
 
-// ---- mbarriers
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.b32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-}
-// True when the phase completed; false when the CTA gives up (this wait ran out or another did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    if (mbar_try(bar, parity)) return true;
-    const long long started = clock64();
-    for (uint32_t spins = 1;; ++spins) {
-        if (mbar_try(bar, parity)) return true;
-        if ((spins & 63u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - started > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicCAS(&tvb_gemm_tc_status_word, 0, code);
-                return false;
-            }
-        }
-    }
-}
-
-// ---- tensor-map copies: box {BK columns, rows} at (column x, row y) into shared memory
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
-
-// ---- tensor memory and tcgen05
-__device__ __forceinline__ void tmem_alloc(uint32_t result_in_shared, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                 ::"r"(result_in_shared), "r"(columns) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_free(uint32_t base, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(base), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-// All tcgen05.mma issued so far by this thread arrive on `bar` when they have finished.
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[smem] . B[smem]^T, 128 x N x 16, bfloat16 in, float32 out.
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 32 lanes x 32 consecutive float32 columns: thread i of the warp gets lane (base lane + i).
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a k-major tile whose rows are 128 bytes, stored in the
-// 128-byte swizzle: groups of 8 rows lie 1024 bytes apart (stride offset), the leading offset
-// is not used by this layout, descriptor version 1, layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t tile_descriptor(uint32_t shared_address) {
-    return (uint64_t)((shared_address >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor: float32 accumulator (1 at bit 4), bfloat16 a and b (1 at bits 7 and
-// 10), both k-major (bits 15, 16 zero), n / 8 at bit 17, m / 16 at bit 24.
 template <int BN> __device__ __forceinline__ constexpr uint32_t instruction_descriptor() {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    return instruction_descriptor_bf16(BM, BN, false);
 }
 
 template <int BN, int MODE>
@@ -200,7 +101,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * OUT_COLS;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, GAVE_UP_EMPTY)) { alive = false; break; }
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, &tvb_gemm_tc_status_word, GAVE_UP_EMPTY)) { alive = false; break; }
                     const uint32_t a_at = base + stage * T::STAGE_BYTES, b_at = a_at + T::A_BYTES;
                     mbar_arrive_expect(full_bar(stage), T::STAGE_BYTES);
                     tma_load_2d(b_at, &map_w, kb * BK, n0, full_bar(stage));
@@ -223,11 +124,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++local) {
                 const int acc = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1u;
-                if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, GAVE_UP_ACC_EMPTY)) break;
+                if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, &tvb_gemm_tc_status_word, GAVE_UP_ACC_EMPTY)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag, GAVE_UP_FULL)) { alive = false; break; }
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, &tvb_gemm_tc_status_word, GAVE_UP_FULL)) { alive = false; break; }
                     tc_fence_after_sync();
                     const uint32_t a_at = base + stage * T::STAGE_BYTES, b_at = a_at + T::A_BYTES;
                     const uint64_t a_desc = tile_descriptor(a_at), b_desc = tile_descriptor(b_at);
@@ -253,7 +154,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const uint32_t acc_phase = (local >> 1) & 1u;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * OUT_COLS;
             // one lane waits with the limit and tells the others, so that the warp stays whole
-            int ready = lane == 0 ? (int)mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, GAVE_UP_ACC_FULL) : 1;
+            int ready = lane == 0 ? (int)mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, &tvb_gemm_tc_status_word, GAVE_UP_ACC_FULL) : 1;
             ready = __shfl_sync(0xffffffffu, ready, 0);
             if (!ready) break;
             for (int tries = 0; tries < 1024 && !mbar_try(acc_full_bar(acc), acc_phase); ++tries) {}
@@ -318,43 +219,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &result) !=
-                cudaSuccess || result != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiled>(p);
-    }();
-    return fn;
-}
-
 // Map of a row-major bfloat16 matrix [rows, cols] with `ld` elements between rows; boxes of
-// 64 columns x box_rows rows, 128-byte swizzle, zeros outside the matrix.
+// 64 columns x box_rows rows.
 bool make_map(CUtensorMap* map, const void* p, long long rows, long long cols, long long ld, int box_rows) {
-    EncodeTiled encode = encode_tiled();
-    if (!encode) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t element_strides[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p), dims, strides, box,
-                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return tvb_make_map(map, p, 2, dims, strides, box);
 }
 
-int sm_count() {
-    static int counts[64] = {0};
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
-    if (counts[device] == 0) cudaDeviceGetAttribute(&counts[device], cudaDevAttrMultiProcessorCount, device);
-    return counts[device];
-}
+int sm_count() { return tvb_sm_count(); }
 
 template <int BN, int MODE>
 int launch_tc(const CUtensorMap& map_x, const CUtensorMap& map_w, void* out, long long ldo, int m, int n, int k,

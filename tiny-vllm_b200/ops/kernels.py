@@ -451,6 +451,75 @@ def attention_prefill(q: torch.Tensor, q_token_stride: int, key_cache: torch.Ten
     return out
 
 
+# ------------------------------------------- tcgen05 prefill attention (head size 128)
+_prefill_tc_tile: int | None = None
+_attention_tc_unchecked = False
+
+
+def attention_prefill_tc_tile_tokens() -> int:
+    global _prefill_tc_tile
+    if _prefill_tc_tile is None:
+        _prefill_tc_tile = _fn("attention_prefill_tc", "tvb_attention_prefill_tc_tile_tokens", [])()
+    return _prefill_tc_tile
+
+
+def attention_prefill_tc_supports(head_dim: int, num_q: int, num_kv: int, page_size: int) -> bool:
+    """Head size 128, pages of 8 to 128 tokens (a power of two), whole groups of q heads."""
+    return (head_dim == 128 and num_q > 0 and num_kv > 0 and num_q % num_kv == 0
+            and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0)
+
+
+def attention_prefill_tc(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor,
+                         value_cache: torch.Tensor, block_tables: torch.Tensor, positions: torch.Tensor,
+                         tile_row: torch.Tensor, tile_first: torch.Tensor, tile_count: torch.Tensor, *,
+                         num_q: int, num_kv: int, head_dim: int, window: int | None, scale: float,
+                         out: torch.Tensor | None = None) -> torch.Tensor:
+    """Paged causal attention on the tcgen05 tensor cores for tiles of up to 128 consecutive
+    query tokens of one request (bfloat16, head size 128).  Tile i holds ``tile_count[i]`` tokens
+    from flat index ``tile_first[i]`` on of request row ``tile_row[i]``; the tiles with the longest
+    context come first.  The kernel reads whole pages: cache slots past a request's last key must
+    hold finite values (they are multiplied by zero)."""
+    _need_cuda(q, key_cache, value_cache, block_tables, positions, tile_row, tile_first, tile_count)
+    if q.dtype != torch.bfloat16 or key_cache.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill_tc is a bfloat16 kernel")
+    if key_cache.dim() != 4 or (key_cache.shape[1], key_cache.shape[3]) != (num_kv, head_dim) or \
+            value_cache.shape != key_cache.shape or not key_cache.is_contiguous() or \
+            not value_cache.is_contiguous():
+        raise KernelError("attention_prefill_tc: caches must be contiguous [pages, num_kv, page_size, head_dim]")
+    if not attention_prefill_tc_supports(head_dim, num_q, num_kv, key_cache.shape[2]):
+        raise KernelError(f"attention_prefill_tc does not take head_dim {head_dim}, {num_q}/{num_kv} heads, "
+                          f"pages of {key_cache.shape[2]}")
+    if q.dim() != 2 or q.stride(1) != 1 or q.stride(0) != q_token_stride or q_token_stride % 8 \
+            or q.shape[1] < num_q * head_dim:
+        raise KernelError("attention_prefill_tc: q must be [tokens, >= num_q * head_dim] with 16-byte aligned rows")
+    for t in (block_tables, positions, tile_row, tile_first, tile_count):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError("attention_prefill_tc: index tensors must be contiguous int32")
+    tokens, tiles = positions.shape[0], tile_row.shape[0]
+    if out is None:
+        out = torch.empty((tokens, num_q * head_dim), dtype=q.dtype, device=q.device)
+    fn = _fn("attention_prefill_tc", "tvb_attention_prefill_tc",
+             [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
+              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+              c_void_p])
+    global _attention_tc_unchecked
+    _check(fn(q.data_ptr(), q_token_stride, tokens, key_cache.data_ptr(), value_cache.data_ptr(),
+              key_cache.shape[0], block_tables.data_ptr(), block_tables.shape[1], positions.data_ptr(),
+              tile_row.data_ptr(), tile_first.data_ptr(), tile_count.data_ptr(), tiles, out.data_ptr(),
+              num_q, num_kv, head_dim, key_cache.shape[2], window or 0, scale, _stream()),
+           "attention_prefill_tc")
+    _attention_tc_unchecked = True
+    return out
+
+
+def attention_prefill_tc_status() -> int:
+    """0, or which bounded wait of an attention_prefill_tc launch gave up since the last call.
+    Synchronises the device; reading clears the record."""
+    global _attention_tc_unchecked
+    _attention_tc_unchecked = False
+    return _fn("attention_prefill_tc", "tvb_attention_prefill_tc_status", [])()
+
+
 # ------------------------------------------------ weight-streaming small-M GEMM
 SMALL_M_MAX_ROWS = 32
 PREFETCH_MAX_BYTES = 32 << 20
@@ -579,4 +648,9 @@ def check_finished_launches() -> None:
         status = gemm_tc_status()
         if status:
             raise KernelError(f"gemm_tc: a wait inside the kernel ran out (code {status}); "
+                              "the results of this step are not valid")
+    if _attention_tc_unchecked:
+        status = attention_prefill_tc_status()
+        if status:
+            raise KernelError(f"attention_prefill_tc: a wait inside the kernel ran out (code {status}); "
                               "the results of this step are not valid")
