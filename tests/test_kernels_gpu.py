@@ -366,6 +366,87 @@ def test_attention_prefill_window_edge_and_far_key():
         close(got, want, dtype, bf16=1.2e-2)
 
 
+def finite_cache(case, dtype):
+    """The case's caches with the unused slots at a large finite value instead of NaN: the tcgen05
+    kernel copies whole pages and multiplies what lies past a request's end by zero."""
+    fill = lambda c: torch.nan_to_num(c.float(), nan=3.0e4).to(dtype).to(DEV)
+    return fill(case["kc"]), fill(case["vc"])
+
+
+def run_prefill_tc(case, *, nq, nkv, d, window, scale):
+    from tinyvllm_b200.ops.attention import prefill_tiles
+    counts, starts, previous = [], [], None
+    for row, position in zip(case["token_row"].tolist(), case["positions"].tolist()):
+        if row != previous:
+            counts.append(0), starts.append(position)
+            previous = row
+        counts[-1] += 1
+    big, rest = prefill_tiles(counts, starts, tensor_memory=True)
+    as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    kc, vc = finite_cache(case, torch.bfloat16)
+    q = case["q"].to(DEV).view(-1, nq * d)
+    args = (q, nq * d, kc, vc, case["tables"].to(DEV), case["positions"].to(DEV))
+    heads = dict(num_q=nq, num_kv=nkv, head_dim=d, window=window, scale=scale)
+    out = torch.full((q.shape[0], nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    if big[0]:
+        k().attention_prefill_tc(*args, *map(as_int, big), **heads, out=out)
+    if rest[0]:
+        k().attention_prefill(*args, *map(as_int, rest), **heads, out=out)
+    assert k().attention_prefill_tc_status() == 0
+    return out.view(-1, nq, d), big, rest
+
+
+@pytest.mark.parametrize("window", [None, 70, 129])
+@pytest.mark.parametrize("shape", [(1, 1, 16), (4, 2, 16), (16, 8, 8), (6, 2, 32), (2, 1, 128)])
+def test_attention_prefill_tc(shape, window):
+    """The tcgen05 tile kernel alone (with the 64-row kernel for the short rests of entries):
+    portions that start anywhere, tiles cut by the end of an entry, shuffled pages."""
+    nq, nkv, page = shape
+    d, dtype = 128, torch.bfloat16
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[300, 1, 70, 515, 64, 1000],
+                      queries=[130, 1, 70, 3, 64, 777], seed=nq + page)
+    want = plain_paged(case, d ** -0.5, window, dtype)
+    got, big, rest = run_prefill_tc(case, nq=nq, nkv=nkv, d=d, window=window, scale=d ** -0.5)
+    assert big[0] and rest[0]                      # both kernels had tiles
+    assert sum(big[2]) + sum(rest[2]) == case["q"].shape[0]
+    close(got, want, dtype, bf16=1.2e-2)
+
+
+def test_attention_prefill_tc_window_edge_far_key_and_growing_maximum():
+    """One key far back scaled up so that its score stands out (it must be found, or be cut off
+    exactly at the window's edge), and keys that grow towards the end so that every row's
+    reference has to move several times."""
+    nq, nkv, d, page, dtype = 2, 1, 128, 16, torch.bfloat16
+    for window in (None, 128, 129, 400):
+        length = 900
+        outside = length - 1 - (window or 500)
+        case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[length], queries=[300],
+                          seed=window or 1, boost=(0, outside, 12.0))
+        want = plain_paged(case, 0.2, window, dtype)
+        got, _, _ = run_prefill_tc(case, nq=nq, nkv=nkv, d=d, window=window, scale=0.2)
+        close(got, want, dtype, bf16=1.2e-2)
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[1024], queries=[1024], seed=3)
+    ramp = torch.linspace(0.2, 3.0, 1024)
+    case["keys"][0] = (case["keys"][0] * ramp[:, None, None]).to(dtype).float()
+    for block in range(1024 // page):
+        span = slice(block * page, (block + 1) * page)
+        case["kc"][case["tables"][0, block]] = case["keys"][0][span].transpose(0, 1).to(dtype)
+    want = plain_paged(case, 0.5, None, dtype)
+    got, _, _ = run_prefill_tc(case, nq=nq, nkv=nkv, d=d, window=None, scale=0.5)
+    close(got, want, dtype, bf16=1.2e-2)
+
+
+def test_attention_prefill_tc_refuses():
+    from tinyvllm_b200.ops.kernels import KernelError
+    assert not k().attention_prefill_tc_supports(64, 4, 2, 16)
+    assert not k().attention_prefill_tc_supports(128, 4, 2, 5)
+    z = lambda *shape: torch.zeros(*shape, dtype=torch.bfloat16, device=DEV)
+    i = lambda *v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="does not take"):
+        k().attention_prefill_tc(z(4, 128), 128, z(3, 2, 16, 64), z(3, 2, 16, 64), i(0).view(1, 1), i(0, 1, 2, 3),
+                                 i(0), i(0), i(4), num_q=2, num_kv=2, head_dim=64, window=None, scale=1.0)
+
+
 @pytest.mark.parametrize("window", [None, 150])
 @pytest.mark.parametrize("shape", [(4, 2, 64, 16, 8), (8, 2, 128, 16, 4), (2, 2, 128, 7, 1),
                                    (8, 1, 256, 32, 5), (16, 8, 128, 16, 8)])

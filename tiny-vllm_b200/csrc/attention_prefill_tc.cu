@@ -10,8 +10,8 @@
 // denominator carries the same reference, so the quotient is the same softmax).
 //
 // Roles: warp 0 issues the copies (lane p the page p of a block), warp 1 one thread issues the
-// products, warps 2..9 are the softmax rows.  S and P are double-buffered, so the products of
-// block j + 1 run while the rows work on block j.  Keys are walked in blocks that start at
+// products, warps 2..9 are the softmax rows.  S is double-buffered, so S of block j + 1 is
+// computed while the rows work on block j.  Keys are walked in blocks that start at
 // absolute multiples of 128, so a row's arithmetic does not depend on how the prompt was cut.
 // Persistent CTAs take (tile, head) items, the tiles sorted by the host with the longest first.
 //
@@ -38,7 +38,7 @@ constexpr int KT = 128;                      // keys of a block
 constexpr int HD = 128;                      // head size
 constexpr int HALF_BYTES = 128 * 64 * 2;     // [128 rows, 64 values] bfloat16: one swizzled sub-tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // a Q, K, V or P tile
-constexpr int SLOTS = 3;                     // ring of K / V tiles
+constexpr int SLOTS = 4;                     // ring of K / V tiles
 constexpr int THREADS = 320;
 constexpr int ROW_WARPS = 8;
 constexpr uint32_t TMEM_COLS = 512;          // S0 S1 O, 128 float32 columns each (a power of two is allocated)
@@ -47,10 +47,9 @@ constexpr float RESCALE_STEP = 8.0f;         // log2 of the growth of a row's ma
 // barrier numbers
 constexpr int B_Q_FULL = 0, B_Q_EMPTY = 1, B_KV_FULL = 2, B_KV_EMPTY = B_KV_FULL + SLOTS,
               B_S_FULL = B_KV_EMPTY + SLOTS, B_S_EMPTY = B_S_FULL + 2, B_P_FULL = B_S_EMPTY + 2,
-              B_P_EMPTY = B_P_FULL + 2, B_O_DONE = B_P_EMPTY + 2, B_O_FREE = B_O_DONE + 1,
-              B_PAIR = B_O_FREE + 1, BARRIERS = B_PAIR + 4;
+              B_O_DONE = B_P_FULL + 1, B_O_FREE = B_O_DONE + 1, B_PAIR = B_O_FREE + 1, BARRIERS = B_PAIR + 4;
 constexpr int EXCHANGE_BYTES = 2 * QT * 2 * 4;      // [buffer][row][half] float
-constexpr int SHARED_BYTES = TILE_BYTES * (1 + SLOTS + 2) + EXCHANGE_BYTES + BARRIERS * 8 + 16 + 1024;
+constexpr int SHARED_BYTES = TILE_BYTES * (1 + SLOTS + 1) + EXCHANGE_BYTES + BARRIERS * 8 + 16 + 1024;
 
 __device__ int tvb_attention_prefill_tc_status_word = 0;
 
@@ -91,11 +90,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t kv_at = base + TILE_BYTES;
     const uint32_t p_at = kv_at + SLOTS * TILE_BYTES;
     uint8_t* p_generic = aligned + TILE_BYTES * (1 + SLOTS);
-    float* exchange = reinterpret_cast<float*>(aligned + TILE_BYTES * (1 + SLOTS + 2));      // [2][QT][2]
-    const uint32_t bars = p_at + 2 * TILE_BYTES + EXCHANGE_BYTES;
+    float* exchange = reinterpret_cast<float*>(aligned + TILE_BYTES * (1 + SLOTS + 1));      // [2][QT][2]
+    const uint32_t bars = p_at + TILE_BYTES + EXCHANGE_BYTES;
     auto bar = [&](int i) { return bars + 8u * i; };
     uint32_t* tmem_base_slot =
-        reinterpret_cast<uint32_t*>(aligned + TILE_BYTES * (1 + SLOTS + 2) + EXCHANGE_BYTES + BARRIERS * 8);
+        reinterpret_cast<uint32_t*>(aligned + TILE_BYTES * (1 + SLOTS + 1) + EXCHANGE_BYTES + BARRIERS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     int* status = &tvb_attention_prefill_tc_status_word;
 
@@ -105,8 +104,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < BARRIERS; ++i) {
-            const bool by_rows = (i >= B_S_EMPTY && i < B_S_EMPTY + 2) || (i >= B_P_FULL && i < B_P_FULL + 2) ||
-                                 i == B_O_FREE;
+            const bool by_rows = (i >= B_S_EMPTY && i < B_S_EMPTY + 2) || i == B_P_FULL || i == B_O_FREE;
             mbar_init(bar(i), by_rows ? ROW_WARPS : (i >= B_PAIR ? 2 : 1));
         }
         *abort_flag = 0;
@@ -221,16 +219,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ++ring;
                 return true;
             };
-            // O (+)= P[g & 1] V for global block g; the first block of an item starts O afresh
+            // O (+)= P V for global block g; the first block of an item starts O afresh
             auto issue_pv = [&](uint32_t gi, bool first_of_item) -> bool {
                 const int slot = ring % SLOTS;
-                const uint32_t phase = (ring / SLOTS) & 1u, b = gi & 1u, use = (gi >> 1) & 1u;
+                const uint32_t phase = (ring / SLOTS) & 1u;
                 if (!mbar_wait(bar(B_KV_FULL + slot), phase, abort_flag, status, 5)) return false;
-                if (!mbar_wait(bar(B_P_FULL + b), use, abort_flag, status, 6)) return false;
+                if (!mbar_wait(bar(B_P_FULL), gi & 1u, abort_flag, status, 6)) return false;
                 if (first_of_item && !mbar_wait(bar(B_O_FREE), (done_items & 1u) ^ 1u, abort_flag, status, 7))
                     return false;
                 tc_fence_after_sync();
-                const uint32_t v_tile = kv_at + slot * TILE_BYTES, p_tile = p_at + b * TILE_BYTES;
+                const uint32_t v_tile = kv_at + slot * TILE_BYTES, p_tile = p_at;
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk) {
                     // 16 keys: 32 bytes inside a row of P, two 1024-byte atoms of V
@@ -240,7 +238,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                            !(first_of_item && kk == 0));
                 }
                 tc_commit(bar(B_KV_EMPTY + slot));
-                tc_commit(bar(B_P_EMPTY + b));
                 tc_commit(bar(B_O_DONE));
                 ++ring;
                 return true;
@@ -271,14 +268,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_address = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        // one lane waits with the limit and tells the others, so that the warp stays whole
+        // every lane waits (with the limit); the warp goes on only if all of them saw the phase
         auto warp_wait = [&](int barrier, uint32_t parity, int code) -> bool {
-            int ready = lane == 0 ? (int)mbar_wait(bar(barrier), parity, abort_flag, status, code) : 1;
-            ready = __shfl_sync(0xffffffffu, ready, 0);
-            if (!ready) return false;
-            for (int tries = 0; tries < 1024 && !mbar_try(bar(barrier), parity); ++tries) {}
-            __syncwarp();
-            return true;
+            const bool seen = mbar_wait(bar(barrier), parity, abort_flag, status, code);
+            return __all_sync(0xffffffffu, seen);
         };
         auto warp_arrive = [&](int barrier) {
             __syncwarp();
@@ -318,14 +311,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const bool full = key0 + 63 <= it.p0 && (window <= 0 || key0 >= it.p0 + QT - 1 - window + 1);
                 float s[64];
                 float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                if (full) {
 #pragma unroll
-                for (int e = 0; e < 64; ++e) {
-                    s[e] = __uint_as_float(v[e]) * scale_log2;
-                    if (!full) {
-                        const int key = key0 + e;
-                        if (key > q_pos || key < lowest) s[e] = -INFINITY;
+                    for (int e = 0; e < 64; ++e) {
+                        s[e] = __uint_as_float(v[e]) * scale_log2;
+                        part[e & 3] = fmaxf(part[e & 3], s[e]);
                     }
-                    part[e & 3] = fmaxf(part[e & 3], s[e]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) {
+                        const int key = key0 + e;
+                        s[e] = key > q_pos || key < lowest ? -INFINITY : __uint_as_float(v[e]) * scale_log2;
+                        part[e & 3] = fmaxf(part[e & 3], s[e]);
+                    }
                 }
                 const float mine = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
                 float* shared_max = exchange + (b * QT + row) * 2;
@@ -340,13 +338,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     reference = block_max;
                     l *= factor;
                 }
-                // Every completion of O_DONE is waited for in turn (a parity wait cannot tell a phase from
-                // the one two before it): here if O has to be scaled, else before P is handed over.
-                bool seen_previous = j == 0;
+                // a row that has seen no key yet subtracts 0 so that no inf - inf appears
+                const float subtract = reference == -INFINITY ? 0.0f : reference;
+                uint4 packed[8];
+                float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int e = 0; e < 64; e += 8) {
+                    float p[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        p[i] = exp2_fast(s[e + i] - subtract);
+                        sums[i & 3] += p[i];
+                    }
+                    packed[e / 8] = pack_bf16x8(p);
+                }
+                l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+                // The product of the block before has finished: P may be overwritten and O scaled.  Every
+                // completion of O_DONE is waited for in turn (a parity wait cannot tell a phase from the one
+                // two before it).
+                if (j > 0 && !warp_wait(B_O_DONE, (gi - 1) & 1u, 12)) { alive = false; break; }
                 if (j > 0 && __any_sync(0xffffffffu, moves)) {
                     // scale this thread's 64 columns of O where the products so far have left them
-                    if (!warp_wait(B_O_DONE, (gi - 1) & 1u, 12)) { alive = false; break; }
-                    seen_previous = true;
                     tc_fence_after_sync();
 #pragma unroll
                     for (int c = 0; c < 64; c += 32) {
@@ -360,26 +372,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tmem_store_wait();
                     tc_fence_before_sync();
                 }
-                // a row that has seen no key yet subtracts 0 so that no inf - inf appears
-                const float subtract = reference == -INFINITY ? 0.0f : reference;
-                if (!warp_wait(B_P_EMPTY + b, use ^ 1u, 11)) { alive = false; break; }
-                uint8_t* p_row = p_generic + b * TILE_BYTES + half * HALF_BYTES + row * 128;
-                float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                // row-major [128 rows, 64 keys], 16-byte chunks swizzled by the row
+                uint8_t* p_row = p_generic + half * HALF_BYTES + row * 128;
 #pragma unroll
-                for (int e = 0; e < 64; e += 8) {
-                    float p[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        p[i] = exp2_fast(s[e + i] - subtract);
-                        sums[i & 3] += p[i];
-                    }
-                    // row-major [128 rows, 64 keys], 16-byte chunks swizzled by the row
-                    *reinterpret_cast<uint4*>(p_row + (((e / 8) ^ (row & 7)) * 16)) = pack_bf16x8(p);
-                }
-                l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-                if (!seen_previous && !warp_wait(B_O_DONE, (gi - 1) & 1u, 15)) { alive = false; break; }
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) * 16)) = packed[c];
                 fence_async_shared();
-                warp_arrive(B_P_FULL + b);
+                warp_arrive(B_P_FULL);
             }
             if (!alive) break;
             // ---- the tile's result: O / (both halves of the denominator)

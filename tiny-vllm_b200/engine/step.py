@@ -25,6 +25,7 @@ import torch
 from ..cache.manager import CacheManager, StepCachePlan
 from ..cache.storage import CacheStorage, bytes_per_page, group_runs
 from ..ops import attention as attention_ops
+from ..ops import kernels
 
 
 class StepError(ValueError):
@@ -68,6 +69,9 @@ class StepContext:
     tile_row: torch.Tensor | None = None     # tiles of consecutive query tokens for the tile kernel:
     tile_first: torch.Tensor | None = None   # request row, first flat token and token count of each
     tile_count: torch.Tensor | None = None
+    tile_tc_row: torch.Tensor | None = None      # the same for the tcgen05 tile kernel (tiles of up to 128
+    tile_tc_first: torch.Tensor | None = None    # tokens, longest context first); a token is in one of the
+    tile_tc_count: torch.Tensor | None = None    # two sets
     # host copies, for parts that plan on the host (and for tests)
     host_rows: tuple = ()                # (request_id, first position, count, state_slot, fresh) per entry
 
@@ -103,6 +107,11 @@ class StepRunner:
         self._pinned_free: torch.cuda.Event | None = None
         self._workspace: torch.Tensor | None = None
         self.decode_splits = attention_ops.decode_splits(self.max_model_len)
+        # prefill tiles are cut for the tcgen05 attention kernel if every mixer says it takes them
+        blocks = getattr(model, "blocks", ())
+        self.tensor_memory_tiles = self.dtype == torch.bfloat16 and len(blocks) > 0 and all(
+            getattr(block.mixer, "takes_tensor_memory_tiles", lambda page: False)(page_size)
+            for block in blocks)
 
     # ------------------------------------------------------------- sizing
     @staticmethod
@@ -169,12 +178,16 @@ class StepRunner:
         decode_only = all(count == 1 for count in counts)
         # only the bfloat16 tile kernel reads tile lists; the 32-bit path walks rows
         tiled = not decode_only and self.storage.dtype == torch.bfloat16
-        tile_lists = attention_ops.prefill_tiles(counts) if tiled else ([], [], [])
+        if tiled:
+            tc_lists, tile_lists = attention_ops.prefill_tiles(
+                counts, [p.start for p in plan.entries], tensor_memory=self.tensor_memory_tiles)
+        else:
+            tc_lists, tile_lists = ([], [], []), ([], [], [])
         sizes = [tokens, tokens, tokens, wanted, rows, rows + 1]
         for g in range(groups):
             sizes += [tokens, rows * blocks[g]]
         tiles_at = len(sizes)
-        sizes += [len(tile_lists[0])] * 3
+        sizes += [len(tile_lists[0])] * 3 + [len(tc_lists[0])] * 3
         offsets = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
         host = np.zeros(int(offsets[-1]), dtype=np.int32)
 
@@ -202,6 +215,7 @@ class StepRunner:
         row_starts[rows] = cursor
         for i in range(3):
             view(tiles_at + i)[:] = tile_lists[i]
+            view(tiles_at + 3 + i)[:] = tc_lists[i]
 
         device = self._upload(host)
 
@@ -224,6 +238,9 @@ class StepRunner:
             tile_row=dview(tiles_at) if tiled else None,
             tile_first=dview(tiles_at + 1) if tiled else None,
             tile_count=dview(tiles_at + 2) if tiled else None,
+            tile_tc_row=dview(tiles_at + 3) if tiled else None,
+            tile_tc_first=dview(tiles_at + 4) if tiled else None,
+            tile_tc_count=dview(tiles_at + 5) if tiled else None,
             host_rows=tuple((p.request_id, p.start, p.count, p.state_slot, p.fresh_state)
                             for p in plan.entries),
         )

@@ -42,18 +42,38 @@ def decode_splits(max_model_len: int) -> int:
     return max(1, min(DECODE_MAX_SPLITS, -(-max_model_len // DECODE_SPLIT_GRAIN)))
 
 
-def prefill_tiles(counts) -> tuple[list[int], list[int], list[int]]:
-    """Cut every entry into tiles of consecutive tokens: (row, first flat token, count) lists."""
-    size = kernels.attention_prefill_tile_tokens()
-    rows, firsts, sizes = [], [], []
+# tiles with fewer tokens than this go to the 64-row kernel: a 128-row tensor-memory tile is mostly
+# empty for them
+TC_MIN_TILE_TOKENS = 32
+
+
+def prefill_tiles(counts, starts=None, *, tensor_memory: bool = False):
+    """Cut every entry of a step into tiles of consecutive tokens.
+
+    Returns two triples of lists (row, first flat token, count): tiles of up to 128 tokens for the
+    tcgen05 kernel, the longest context first, and tiles of up to 64 tokens for the mma.sync
+    kernel.  Without ``tensor_memory`` every token is in the second set; with it only the short
+    rests of entries are.  ``starts``: tokens each entry has in the cache before the step."""
+    small = kernels.attention_prefill_tile_tokens()
+    large = kernels.attention_prefill_tc_tile_tokens() if tensor_memory else 0
+    starts = starts if starts is not None else [0] * len(counts)
+    big, ends = ([], [], []), []
+    rest = ([], [], [])
     cursor = 0
     for row, count in enumerate(counts):
-        for start in range(0, count, size):
-            rows.append(row)
-            firsts.append(cursor + start)
-            sizes.append(min(size, count - start))
+        done = 0
+        if tensor_memory:
+            while count - done >= TC_MIN_TILE_TOKENS:
+                size = min(large, count - done)
+                big[0].append(row), big[1].append(cursor + done), big[2].append(size)
+                ends.append(starts[row] + done + size)
+                done += size
+        for start in range(done, count, small):
+            rest[0].append(row), rest[1].append(cursor + start), rest[2].append(min(small, count - start))
         cursor += count
-    return rows, firsts, sizes
+    order = sorted(range(len(ends)), key=lambda i: -ends[i])
+    big = tuple([column[i] for i in order] for column in big)
+    return big, rest
 
 
 def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
@@ -83,9 +103,17 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
         slots=ctx.slots[group] if writes else None, key_cache=keys, value_cache=values)
     if (tiled and ctx.tile_row is not None
             and kernels.attention_prefill_supports(mixer.head_dim, mixer.num_heads, mixer.num_kv_heads)):
-        return kernels.attention_prefill(
-            qkv, qkv.shape[1], keys, values, ctx.block_tables[group], ctx.positions, ctx.tile_row,
-            ctx.tile_first, ctx.tile_count, **heads, window=mixer.window, scale=mixer.scale)
+        out = torch.empty((qkv.shape[0], mixer.num_heads * mixer.head_dim), dtype=qkv.dtype, device=qkv.device)
+        if ctx.tile_tc_row is not None and ctx.tile_tc_row.shape[0] > 0:
+            # the step's tile lists were cut for the tcgen05 kernel: every mixer of the model takes it
+            kernels.attention_prefill_tc(
+                qkv, qkv.shape[1], keys, values, ctx.block_tables[group], ctx.positions, ctx.tile_tc_row,
+                ctx.tile_tc_first, ctx.tile_tc_count, **heads, window=mixer.window, scale=mixer.scale, out=out)
+        if ctx.tile_row.shape[0] > 0:
+            kernels.attention_prefill(
+                qkv, qkv.shape[1], keys, values, ctx.block_tables[group], ctx.positions, ctx.tile_row,
+                ctx.tile_first, ctx.tile_count, **heads, window=mixer.window, scale=mixer.scale, out=out)
+        return out
     scratch = None
     if ctx.split_chunks > 0:
         scratch = ctx.workspace(kernels.attention_rows_scratch_floats(

@@ -12,7 +12,7 @@ are parameters; the position encoding is a part of its own.
 from __future__ import annotations
 
 from ..ops import attention as attention_ops
-from ..ops import linear, linear_norm
+from ..ops import kernels, linear, linear_norm
 from .base import BuildContext, KVNeed, ParamSpec, Part
 from .registry import register_part
 
@@ -64,6 +64,12 @@ class GQAAttention(Part):
 
     def cache_need(self):
         return KVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def takes_tensor_memory_tiles(self, page_size: int) -> bool:
+        """Whether this mixer's prefill may run on the tcgen05 tile kernel; the step cuts its
+        tile lists for that kernel only if every mixer of the model says so."""
+        return kernels.attention_prefill_tc_supports(self.head_dim, self.num_heads, self.num_kv_heads,
+                                                     page_size)
 
     # ---------------------------------------------------------------- running
     def forward(self, x, ctx, run: int):
