@@ -2,18 +2,26 @@
 // tiles of up to 128 consecutive query tokens of one request and one q head against the paged
 // cache.  S = Q K^T and O += P V are tcgen05.mma with the accumulators in tensor memory; Q, K
 // and V tiles arrive through tensor-map copies (K and V page by page, straight from the cache
-// [pages, kv_heads, page_size, 128]) in the 128-byte swizzle.  256 threads, two per query row
-// (64 keys of a block each), read S from tensor memory, apply the mask and the online softmax in
-// float32 and write P as bfloat16 into shared memory for the second product.  O stays in tensor
-// memory over all blocks of a tile; a row's part of it is scaled there only when the row's
-// maximum has grown by more than 2^8 since the reference that its exponentials use was set (the
-// denominator carries the same reference, so the quotient is the same softmax).
+// [pages, kv_heads, page_size, 128]) in the 128-byte swizzle.
 //
-// Roles: warp 0 issues the copies (lane p the page p of a block), warp 1 one thread issues the
-// products, warps 2..9 are the softmax rows.  S is double-buffered, so S of block j + 1 is
-// computed while the rows work on block j.  Keys are walked in blocks that start at
-// absolute multiples of 128, so a row's arithmetic does not depend on how the prompt was cut.
-// Persistent CTAs take (tile, head) items, the tiles sorted by the host with the longest first.
+// The blocks of 128 keys of a tile go alternately to two groups of 128 softmax threads (one
+// thread per query row).  Each group has its own S and its own O in tensor memory, with its own
+// running reference and denominator, so the two chains (read S, mask, maximum, exponentials in
+// float32, P as bfloat16) do not wait for each other: one group's exponentials run under the
+// other's waits.  P never leaves tensor memory: a thread writes its row of P over the columns of
+// S it has read (two bfloat16 per column), and the second product takes its a operand from there.  A row's part of O
+// is scaled in tensor memory only when the row's maximum has grown by more than 2^8 since the
+// reference that its exponentials use was set (the denominator carries the same reference).  At
+// the end of a tile the first group merges the two accumulators:
+// (O_a 2^(m_a - m) + O_b 2^(m_b - m)) / (l_a 2^(m_a - m) + l_b 2^(m_b - m)).
+//
+// Roles: warp 0 issues the copies (lane p the page p of a block), one thread of warp 1 issues the
+// products Q K^T and one thread of warp 10 the products P V (each has its own waits and commits
+// to do between products, and the tensor pipe takes the other's meanwhile), warps 2..5 and 6..9
+// are the two softmax groups.  Keys are walked in blocks that start
+// at absolute multiples of 128, even blocks to the first group, so a row's arithmetic does not
+// depend on how the prompt was cut.  Persistent CTAs take (tile, head) items, the tiles sorted by
+// the host with the longest first.
 //
 // Stands where the reference calls torch's scaled_dot_product_attention per request after
 // gathering the history into a contiguous copy (tinyvllm/runtime/attention.py:112-147,
@@ -38,18 +46,19 @@ constexpr int KT = 128;                      // keys of a block
 constexpr int HD = 128;                      // head size
 constexpr int HALF_BYTES = 128 * 64 * 2;     // [128 rows, 64 values] bfloat16: one swizzled sub-tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // a Q, K, V or P tile
-constexpr int SLOTS = 4;                     // ring of K / V tiles
-constexpr int THREADS = 320;
-constexpr int ROW_WARPS = 8;
-constexpr uint32_t TMEM_COLS = 512;          // S0 S1 O, 128 float32 columns each (a power of two is allocated)
+constexpr int SLOTS = 5;                     // ring of K / V tiles
+constexpr int THREADS = 352;                 // copy warp, issuer of Q K^T, 8 softmax warps, issuer of P V
+constexpr int GROUP_WARPS = 4;               // warps of one softmax group
+constexpr uint32_t TMEM_COLS = 512;          // S_a S_b O_a O_b, 128 float32 columns each
 constexpr float RESCALE_STEP = 8.0f;         // log2 of the growth of a row's maximum that moves its reference
 
-// barrier numbers
+// barrier numbers; [2] = one per softmax group
 constexpr int B_Q_FULL = 0, B_Q_EMPTY = 1, B_KV_FULL = 2, B_KV_EMPTY = B_KV_FULL + SLOTS,
-              B_S_FULL = B_KV_EMPTY + SLOTS, B_S_EMPTY = B_S_FULL + 2, B_P_FULL = B_S_EMPTY + 2,
-              B_O_DONE = B_P_FULL + 1, B_O_FREE = B_O_DONE + 1, B_PAIR = B_O_FREE + 1, BARRIERS = B_PAIR + 4;
-constexpr int EXCHANGE_BYTES = 2 * QT * 2 * 4;      // [buffer][row][half] float
-constexpr int SHARED_BYTES = TILE_BYTES * (1 + SLOTS + 1) + EXCHANGE_BYTES + BARRIERS * 8 + 16 + 1024;
+              B_S_FULL = B_KV_EMPTY + SLOTS, B_P_FULL = B_S_FULL + 2, B_P_READ = B_P_FULL + 2,
+              B_O_LAST = B_P_READ + 2, B_O_FREE = B_O_LAST + 2, B_SECOND_DONE = B_O_FREE + 2, B_FIRST_TOOK = B_SECOND_DONE + 1,
+              BARRIERS = B_FIRST_TOOK + 1;
+constexpr int EXCHANGE_BYTES = QT * 2 * 4;          // [row][reference, denominator] of the second group
+constexpr int SHARED_BYTES = TILE_BYTES * (1 + SLOTS) + EXCHANGE_BYTES + BARRIERS * 8 + 16 + 1024;
 
 __device__ int tvb_attention_prefill_tc_status_word = 0;
 
@@ -64,19 +73,6 @@ __device__ __forceinline__ float exp2_fast(float x) {
     return y;
 }
 
-// 32 lanes x 32 consecutive float32 columns back into tensor memory.
-__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t* r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* block_tables, int table_stride,
@@ -88,13 +84,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint8_t* aligned = raw_shared + (base - smem_address(raw_shared));
     const uint32_t q_at = base;
     const uint32_t kv_at = base + TILE_BYTES;
-    const uint32_t p_at = kv_at + SLOTS * TILE_BYTES;
-    uint8_t* p_generic = aligned + TILE_BYTES * (1 + SLOTS);
-    float* exchange = reinterpret_cast<float*>(aligned + TILE_BYTES * (1 + SLOTS + 1));      // [2][QT][2]
-    const uint32_t bars = p_at + TILE_BYTES + EXCHANGE_BYTES;
+    float* exchange = reinterpret_cast<float*>(aligned + TILE_BYTES * (1 + SLOTS));      // [QT][2]
+    const uint32_t bars = kv_at + SLOTS * TILE_BYTES + EXCHANGE_BYTES;
     auto bar = [&](int i) { return bars + 8u * i; };
     uint32_t* tmem_base_slot =
-        reinterpret_cast<uint32_t*>(aligned + TILE_BYTES * (1 + SLOTS + 1) + EXCHANGE_BYTES + BARRIERS * 8);
+        reinterpret_cast<uint32_t*>(aligned + TILE_BYTES * (1 + SLOTS) + EXCHANGE_BYTES + BARRIERS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     int* status = &tvb_attention_prefill_tc_status_word;
 
@@ -104,8 +98,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < BARRIERS; ++i) {
-            const bool by_rows = (i >= B_S_EMPTY && i < B_S_EMPTY + 2) || i == B_P_FULL || i == B_O_FREE;
-            mbar_init(bar(i), by_rows ? ROW_WARPS : (i >= B_PAIR ? 2 : 1));
+            const bool by_group = (i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_FREE && i < B_O_FREE + 2) ||
+                                  i == B_SECOND_DONE || i == B_FIRST_TOOK;
+            mbar_init(bar(i), by_group ? GROUP_WARPS : 1);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -192,82 +187,91 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             ++done_items;
         }
         __syncwarp();
-    } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- products
+    } else if (warp == 1 || warp == 10) {
+        // ---- products.  The tiles of an item with n blocks come through the ring in the order K0, K1,
+        // V0, K2, V1, ..., V(n-1): K of block j is the item's tile 2 j - 1 (0 for j = 0), V of block j
+        // its tile 2 j + 2 (2 n - 1 for the last).  Block j belongs to softmax group j & 1.
+        if (lane == 0 && warp == 1) {
             constexpr uint32_t idesc_qk = instruction_descriptor_bf16(QT, KT, false);
-            constexpr uint32_t idesc_pv = instruction_descriptor_bf16(QT, HD, true);
-            uint32_t ring = 0, g = 0;
-            int done_items = 0;
+            uint32_t ring_base = 0, used_a = 0, used_b = 0, done_items = 0;
             bool alive = true;
-            // S[g & 1] = Q K^T for global block g
-            auto issue_qk = [&](uint32_t gi) -> bool {
-                const int slot = ring % SLOTS;
-                const uint32_t phase = (ring / SLOTS) & 1u, b = gi & 1u, use = (gi >> 1) & 1u;
-                if (!mbar_wait(bar(B_KV_FULL + slot), phase, abort_flag, status, 3)) return false;
-                if (!mbar_wait(bar(B_S_EMPTY + b), use ^ 1u, abort_flag, status, 4)) return false;
-                tc_fence_after_sync();
-                const uint32_t k_tile = kv_at + slot * TILE_BYTES;
-#pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t half = (kk / 4) * HALF_BYTES, step = 2u * (kk % 4);
-                    tc_mma(tmem_base + b * KT, tile_descriptor(q_at + half) + step,
-                           tile_descriptor(k_tile + half) + step, idesc_qk, kk != 0);
-                }
-                tc_commit(bar(B_KV_EMPTY + slot));
-                tc_commit(bar(B_S_FULL + b));
-                ++ring;
-                return true;
-            };
-            // O (+)= P V for global block g; the first block of an item starts O afresh
-            auto issue_pv = [&](uint32_t gi, bool first_of_item) -> bool {
-                const int slot = ring % SLOTS;
-                const uint32_t phase = (ring / SLOTS) & 1u;
-                if (!mbar_wait(bar(B_KV_FULL + slot), phase, abort_flag, status, 5)) return false;
-                if (!mbar_wait(bar(B_P_FULL), gi & 1u, abort_flag, status, 6)) return false;
-                if (first_of_item && !mbar_wait(bar(B_O_FREE), (done_items & 1u) ^ 1u, abort_flag, status, 7))
-                    return false;
-                tc_fence_after_sync();
-                const uint32_t v_tile = kv_at + slot * TILE_BYTES, p_tile = p_at;
-#pragma unroll
-                for (int kk = 0; kk < KT / 16; ++kk) {
-                    // 16 keys: 32 bytes inside a row of P, two 1024-byte atoms of V
-                    const uint32_t half = (kk / 4) * HALF_BYTES, step = 2u * (kk % 4);
-                    tc_mma(tmem_base + 2 * KT, tile_descriptor(p_tile + half) + step,
-                           tile_descriptor_mn_major(v_tile + kk * 2048, HALF_BYTES), idesc_pv,
-                           !(first_of_item && kk == 0));
-                }
-                tc_commit(bar(B_KV_EMPTY + slot));
-                tc_commit(bar(B_O_DONE));
-                ++ring;
-                return true;
-            };
             for (int round = 0; alive; ++round) {
                 Item it;
                 if (!item_of(round, it)) break;
                 if (!mbar_wait(bar(B_Q_FULL), done_items & 1u, abort_flag, status, 8)) break;
-                tc_fence_after_sync();
-                alive = issue_qk(g);
-                if (alive && it.blocks == 1) tc_commit(bar(B_Q_EMPTY));
-                for (int j = 0; j < it.blocks && alive; ++j) {
-                    if (j + 1 < it.blocks) {
-                        alive = issue_qk(g + j + 1);
-                        if (alive && j + 2 == it.blocks) tc_commit(bar(B_Q_EMPTY));
+                for (int j = 0; j < it.blocks; ++j) {
+                    const uint32_t b = j & 1u;
+                    const uint32_t n = (b ? used_b : used_a) + j / 2;      // the group's n-th block
+                    const uint32_t tile = ring_base + (j == 0 ? 0 : 2 * j - 1);
+                    const uint32_t slot = tile % SLOTS, phase = (tile / SLOTS) & 1u;
+                    if (!mbar_wait(bar(B_KV_FULL + slot), phase, abort_flag, status, 3)) { alive = false; break; }
+                    // S of the group is also where its P lies: the product that read P of the block before
+                    // must have finished
+                    if (n > 0 && !mbar_wait(bar(B_P_READ + b), (n - 1) & 1u, abort_flag, status, 4)) { alive = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t k_tile = kv_at + slot * TILE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {
+                        const uint32_t half = (kk / 4) * HALF_BYTES, step = 2u * (kk % 4);
+                        tc_mma(tmem_base + b * KT, tile_descriptor(q_at + half) + step,
+                               tile_descriptor(k_tile + half) + step, idesc_qk, kk != 0);
                     }
-                    if (alive) alive = issue_pv(g + j, j == 0);
+                    tc_commit(bar(B_KV_EMPTY + slot));
+                    tc_commit(bar(B_S_FULL + b));
                 }
-                g += it.blocks;
+                if (alive) tc_commit(bar(B_Q_EMPTY));
+                ring_base += 2 * it.blocks;
+                used_a += (it.blocks + 1) / 2;
+                used_b += it.blocks / 2;
+                ++done_items;
+            }
+        } else if (lane == 0) {
+            constexpr uint32_t idesc_pv = instruction_descriptor_bf16(QT, HD, true);
+            uint32_t ring_base = 0, used_a = 0, used_b = 0, done_items = 0;
+            bool alive = true;
+            for (int round = 0; alive; ++round) {
+                Item it;
+                if (!item_of(round, it)) break;
+                for (int j = 0; j < it.blocks; ++j) {
+                    const uint32_t b = j & 1u;
+                    const uint32_t n = (b ? used_b : used_a) + j / 2;
+                    const uint32_t tile = ring_base + (j + 1 < it.blocks ? 2 * j + 2 : 2 * it.blocks - 1);
+                    const uint32_t slot = tile % SLOTS, phase = (tile / SLOTS) & 1u;
+                    const bool first_of_item = j < 2, last_of_item = j + 2 >= it.blocks;
+                    if (!mbar_wait(bar(B_KV_FULL + slot), phase, abort_flag, status, 5)) { alive = false; break; }
+                    if (!mbar_wait(bar(B_P_FULL + b), n & 1u, abort_flag, status, 6)) { alive = false; break; }
+                    if (first_of_item && !mbar_wait(bar(B_O_FREE + b), (done_items & 1u) ^ 1u, abort_flag, status, 7)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t v_tile = kv_at + slot * TILE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < KT / 16; ++kk) {
+                        // 16 keys: 8 columns of P (two bfloat16 a column, over S), two 1024-byte atoms of V
+                        tc_mma_a_in_tmem(tmem_base + 2 * KT + b * HD, tmem_base + b * KT + kk * 8,
+                                         tile_descriptor_mn_major(v_tile + kk * 2048, HALF_BYTES), idesc_pv,
+                                         !(first_of_item && kk == 0));
+                    }
+                    tc_commit(bar(B_KV_EMPTY + slot));
+                    tc_commit(bar(B_P_READ + b));
+                    if (last_of_item) tc_commit(bar(B_O_LAST + b));
+                }
+                ring_base += 2 * it.blocks;
+                used_a += (it.blocks + 1) / 2;
+                used_b += it.blocks / 2;
                 ++done_items;
             }
         }
         __syncwarp();
     } else {
-        // ---- softmax rows: two threads per query row, 64 keys of a block each.  Warps 2..9: the
-        // warp's number modulo 4 names the 32 lanes of tensor memory it may read, warps w and w + 4
-        // share them and take the first and the second 64 columns.
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        // ---- softmax rows: group 0 = warps 2..5 takes the even blocks of a tile, group 1 = warps 6..9
+        // the odd ones; a warp's number modulo 4 names the 32 lanes of tensor memory it may read.
+        const int quarter = warp & 3, group = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_address = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t s_address = lane_address + group * KT;
+        const uint32_t o_address = lane_address + 2 * KT + group * HD;
         // every lane waits (with the limit); the warp goes on only if all of them saw the phase
         auto warp_wait = [&](int barrier, uint32_t parity, int code) -> bool {
             const bool seen = mbar_wait(bar(barrier), parity, abort_flag, status, code);
@@ -277,16 +281,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(barrier));
         };
-        // the two warps that share 32 query rows meet (a bounded wait, as everywhere)
-        uint32_t pair_phase = 0;
-        auto pair_sync = [&]() -> bool {
-            warp_arrive(B_PAIR + quarter);
-            const bool met = warp_wait(B_PAIR + quarter, pair_phase, 14);
-            pair_phase ^= 1u;
-            return met;
-        };
-        uint32_t g = 0;
-        int done_items = 0;
+        uint32_t used = 0;                    // blocks this group has taken so far
+        uint32_t finals = 0;                  // tiles in which this group had blocks
+        uint32_t done_items = 0;
         bool alive = true;
         for (int round = 0; alive; ++round) {
             Item it;
@@ -294,42 +291,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int q_pos = it.p0 + row;
             const int lowest = window > 0 ? q_pos - window + 1 : 0;      // first key this row sees
             float reference = -INFINITY;      // what the exponentials of this row subtract (in log2 units)
-            float l = 0.0f;                   // this thread's part of the denominator
-            for (int j = 0; j < it.blocks && alive; ++j) {
-                const uint32_t gi = g + j, b = gi & 1u, use = (gi >> 1) & 1u;
-                const int key0 = (it.block0 + j) * KT + half * 64;
-                if (!warp_wait(B_S_FULL + b, use, 10)) { alive = false; break; }
+            float l = 0.0f;                   // the denominator of this group's blocks
+            for (int j = group; j < it.blocks && alive; j += 2, ++used) {
+                const uint32_t parity = used & 1u;
+                const int key0 = (it.block0 + j) * KT;
+                const bool has_previous = j >= 2;
+                if (!warp_wait(B_S_FULL + group, parity, 10)) { alive = false; break; }
                 tc_fence_after_sync();
-                uint32_t v[64];
-                tmem_load_32(lane_address + b * KT + half * 64, v);
-                tmem_load_32(lane_address + b * KT + half * 64 + 32, v + 32);
-                tmem_load_wait();
-                // S is not read again: the products of the block after next may overwrite it
-                tc_fence_before_sync();
-                warp_arrive(B_S_EMPTY + b);
                 // below every row's diagonal and inside every row's window: no mask
-                const bool full = key0 + 63 <= it.p0 && (window <= 0 || key0 >= it.p0 + QT - 1 - window + 1);
-                float s[64];
+                const bool full = key0 + KT - 1 <= it.p0 && (window <= 0 || key0 >= it.p0 + QT - 1 - window + 1);
+                // ---- first pass over S: the block's maximum of this row
                 float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                if (full) {
 #pragma unroll
-                    for (int e = 0; e < 64; ++e) {
-                        s[e] = __uint_as_float(v[e]) * scale_log2;
-                        part[e & 3] = fmaxf(part[e & 3], s[e]);
-                    }
-                } else {
+                for (int c = 0; c < KT; c += 64) {
+                    uint32_t v[64];
+                    tmem_load_32(s_address + c, v);
+                    tmem_load_32(s_address + c + 32, v + 32);
+                    tmem_load_wait();
+                    if (full) {
 #pragma unroll
-                    for (int e = 0; e < 64; ++e) {
-                        const int key = key0 + e;
-                        s[e] = key > q_pos || key < lowest ? -INFINITY : __uint_as_float(v[e]) * scale_log2;
-                        part[e & 3] = fmaxf(part[e & 3], s[e]);
+                        for (int e = 0; e < 64; ++e) part[e & 3] = fmaxf(part[e & 3], __uint_as_float(v[e]));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 64; ++e) {
+                            const int key = key0 + c + e;
+                            part[e & 3] = fmaxf(part[e & 3], key > q_pos || key < lowest ? -INFINITY : __uint_as_float(v[e]));
+                        }
                     }
                 }
-                const float mine = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
-                float* shared_max = exchange + (b * QT + row) * 2;
-                shared_max[half] = mine;
-                if (!pair_sync()) { alive = false; break; }
-                const float block_max = fmaxf(mine, shared_max[half ^ 1]);
+                // scale > 0: the maximum of the scaled scores is the scaled maximum
+                const float block_max = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) * scale_log2;
                 // the reference moves when the maximum has outgrown it by more than 2^RESCALE_STEP
                 const bool moves = block_max > reference + RESCALE_STEP || (reference == -INFINITY && block_max > -INFINITY);
                 float factor = 1.0f;
@@ -338,76 +329,112 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     reference = block_max;
                     l *= factor;
                 }
-                // a row that has seen no key yet subtracts 0 so that no inf - inf appears
-                const float subtract = reference == -INFINITY ? 0.0f : reference;
-                uint4 packed[8];
-                float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                // S of this block is there, so every product issued before it has finished, the one into this
+                // group's O among them: O may be scaled.
+                if (has_previous && __any_sync(0xffffffffu, moves)) {
 #pragma unroll
-                for (int e = 0; e < 64; e += 8) {
-                    float p[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        p[i] = exp2_fast(s[e + i] - subtract);
-                        sums[i & 3] += p[i];
-                    }
-                    packed[e / 8] = pack_bf16x8(p);
-                }
-                l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-                // The product of the block before has finished: P may be overwritten and O scaled.  Every
-                // completion of O_DONE is waited for in turn (a parity wait cannot tell a phase from the one
-                // two before it).
-                if (j > 0 && !warp_wait(B_O_DONE, (gi - 1) & 1u, 12)) { alive = false; break; }
-                if (j > 0 && __any_sync(0xffffffffu, moves)) {
-                    // scale this thread's 64 columns of O where the products so far have left them
-                    tc_fence_after_sync();
-#pragma unroll
-                    for (int c = 0; c < 64; c += 32) {
+                    for (int c = 0; c < HD; c += 32) {
                         uint32_t o[32];
-                        tmem_load_32(lane_address + 2 * KT + half * 64 + c, o);
+                        tmem_load_32(o_address + c, o);
                         tmem_load_wait();
 #pragma unroll
                         for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
-                        tmem_store_32(lane_address + 2 * KT + half * 64 + c, o);
+                        tmem_store_32(o_address + c, o);
                     }
-                    tmem_store_wait();
-                    tc_fence_before_sync();
                 }
-                // row-major [128 rows, 64 keys], 16-byte chunks swizzled by the row
-                uint8_t* p_row = p_generic + half * HALF_BYTES + row * 128;
+                // ---- second pass: exponentials; P (two bfloat16 a column) over the columns of S just read
+                // a row that has seen no key yet subtracts 0 so that no inf - inf appears
+                const float subtract = reference == -INFINITY ? 0.0f : reference;
+                float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) * 16)) = packed[c];
-                fence_async_shared();
-                warp_arrive(B_P_FULL);
+                for (int c = 0; c < KT; c += 64) {
+                    uint32_t v[64];
+                    tmem_load_32(s_address + c, v);
+                    tmem_load_32(s_address + c + 32, v + 32);
+                    tmem_load_wait();
+                    uint32_t packed[32];
+                    if (full) {
+#pragma unroll
+                        for (int e = 0; e < 64; e += 2) {
+                            const float p0 = exp2_fast(fmaf(__uint_as_float(v[e]), scale_log2, -subtract));
+                            const float p1 = exp2_fast(fmaf(__uint_as_float(v[e + 1]), scale_log2, -subtract));
+                            sums[e & 3] += p0;
+                            sums[(e & 3) + 1] += p1;
+                            packed[e / 2] = pack_bf16x2(p0, p1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 64; e += 2) {
+                            const int key = key0 + c + e;
+                            const float p0 = key > q_pos || key < lowest
+                                                 ? 0.0f : exp2_fast(fmaf(__uint_as_float(v[e]), scale_log2, -subtract));
+                            const float p1 = key + 1 > q_pos || key + 1 < lowest
+                                                 ? 0.0f : exp2_fast(fmaf(__uint_as_float(v[e + 1]), scale_log2, -subtract));
+                            sums[e & 3] += p0;
+                            sums[(e & 3) + 1] += p1;
+                            packed[e / 2] = pack_bf16x2(p0, p1);
+                        }
+                    }
+                    tmem_store_32(s_address + c / 2, packed);
+                }
+                l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+                tmem_store_wait();
+                tc_fence_before_sync();
+                warp_arrive(B_P_FULL + group);
             }
             if (!alive) break;
-            // ---- the tile's result: O / (both halves of the denominator)
-            const uint32_t last = g + it.blocks - 1;
-            float* shared_sum = exchange + ((last & 1u) * QT + row) * 2;
-            if (!pair_sync()) break;                  // the maxima of the last block have been read
-            shared_sum[half] = l;
-            if (!pair_sync()) break;
-            const float total = l + shared_sum[half ^ 1];
-            if (!warp_wait(B_O_DONE, last & 1u, 13)) break;
-            tc_fence_after_sync();
-            uint32_t o[64];
-            tmem_load_32(lane_address + 2 * KT + half * 64, o);
-            tmem_load_32(lane_address + 2 * KT + half * 64 + 32, o + 32);
-            tmem_load_wait();
-            tc_fence_before_sync();
-            warp_arrive(B_O_FREE);
-            g += it.blocks;
-            ++done_items;
-            if (row < it.count) {
+            const int own_blocks = (it.blocks - group + 1) / 2;
+            // the last product into this group's O has finished
+            if (own_blocks > 0) {
+                if (!warp_wait(B_O_LAST + group, finals & 1u, 13)) break;
+                ++finals;
+            }
+            if (group == 1) {
+                // hand reference and denominator to the first group (which has taken those of the tile before)
+                if (done_items > 0 && !warp_wait(B_FIRST_TOOK, (done_items - 1) & 1u, 16)) break;
+                exchange[row * 2] = reference;
+                exchange[row * 2 + 1] = l;
+                warp_arrive(B_SECOND_DONE);
+            } else {
+                // ---- the tile's result: both accumulators on the larger reference, over both denominators
+                if (!warp_wait(B_SECOND_DONE, done_items & 1u, 17)) break;
+                const float other_reference = exchange[row * 2], other_l = exchange[row * 2 + 1];
+                warp_arrive(B_FIRST_TOOK);
+                const float top = fmaxf(reference, other_reference);
+                const float mine = reference == -INFINITY ? 0.0f : exp2_fast(reference - top);
+                const float theirs = other_reference == -INFINITY ? 0.0f : exp2_fast(other_reference - top);
+                const float total = l * mine + other_l * theirs;
                 const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
-                bf16* out_row = out + (int64_t)(it.first + row) * out_stride + it.head * HD + half * 64;
+                const float weight_a = mine * inverse, weight_b = theirs * inverse;
+                const bool second_used = it.blocks > 1;            // else O of the second group holds nothing of this tile
+                tc_fence_after_sync();
+                bf16* out_row = out + (int64_t)(it.first + row) * out_stride + it.head * HD;
 #pragma unroll
-                for (int e = 0; e < 64; e += 8) {
-                    float f[8];
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t a[32], b[32];
+                    tmem_load_32(lane_address + 2 * KT + c, a);
+                    if (second_used) tmem_load_32(lane_address + 2 * KT + HD + c, b);
+                    tmem_load_wait();
+                    if (c + 32 == HD) {
+                        tc_fence_before_sync();
+                        warp_arrive(B_O_FREE);
+                        warp_arrive(B_O_FREE + 1);
+                    }
+                    if (row < it.count) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[e + i]) * inverse;
-                    *reinterpret_cast<uint4*>(out_row + e) = pack_bf16x8(f);
+                        for (int e = 0; e < 32; e += 8) {
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                f[i] = __uint_as_float(a[e + i]) * weight_a;
+                                if (second_used) f[i] = fmaf(__uint_as_float(b[e + i]), weight_b, f[i]);
+                            }
+                            *reinterpret_cast<uint4*>(out_row + c + e) = pack_bf16x8(f);
+                        }
+                    }
                 }
             }
+            ++done_items;
         }
     }
 
