@@ -153,3 +153,33 @@ def test_trace_run_program(dtype_name, model_folders, tmp_path):
     assert result.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
     got = rh.read_trace_output(steps, out_dir, TINY_CONFIGS[name].vocab_size)
     rh.compare(got, rh.oracle(model_folders[name], requests, dtype), dtype, what="trace_run")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_steps_replayed_as_graphs_give_the_eager_logits(dtype, model_folders):
+    """A step whose signature comes back is captured at its second occurrence and replayed from
+    the third: the logits of every occurrence are those of a runner that never captures, bit
+    for bit, also with other steps in between and with pages that are used again."""
+    from tinyvllm_b200.engine.step import StepEntry
+
+    name = "e"
+    vocab = TINY_CONFIGS[name].vocab_size
+    eager = make_runner(model_folders[name], dtype, PAGE_SIZES[name], 24, max_requests=4)
+    graphed = make_runner(model_folders[name], dtype, PAGE_SIZES[name], 24, max_requests=4)
+    graphed.enable_step_graphs(limit=2)
+    shapes = [(150, 3), (150, 3), (40, 2), (150, 3), (150, 3), (40, 2), (40, 2), (7, 1), (150, 3), (7, 1), (7, 1)]
+    for step, (count, wanted) in enumerate(shapes):
+        tokens = tuple(random_tokens(vocab, count, 1000 + step))
+        want = tuple(range(count - wanted, count))
+        results = []
+        for r in (eager, graphed):
+            r.open(step)
+            results.append(r.run([StepEntry(step, tokens, want)]).clone())
+            # two decoded tokens behind the prompt: the cache the step left is the eager one's
+            for extra in range(2):
+                results.append(r.run([StepEntry(step, (tokens[extra],), (0,))]).clone())
+            r.close(step)
+        half = len(results) // 2
+        for a, b in zip(results[:half], results[half:]):
+            assert torch.equal(a, b), f"step {step}"
+    assert len(graphed._step_graphs) == 2          # the limit holds; later shapes stay eager

@@ -137,6 +137,7 @@ class Engine:
                     sizes.append(config.max_num_seqs)
                 graphs = DecodeGraphs(runner, sizes, max_model_len=config.max_model_len)
                 graphs.capture()
+                runner.enable_step_graphs()       # prefill and mixed steps whose shape comes back
         log.info("engine ready: %s, %s, %d pages of %d tokens per group, %.1f MiB of weights",
                  spec.architecture, config.dtype, pages, config.kv_block_size,
                  model.weight_bytes() / 2**20)
@@ -211,8 +212,7 @@ class Engine:
                 tokens_device = replayed[0]
                 self.graph_steps += 1
         if tokens_device is None:
-            ctx = self.runner.build_context(entries, scheduled.cache_plan)
-            logits = self.runner.execute(ctx)
+            logits = self.runner.forward(entries, scheduled.cache_plan)
             if logits is not None:
                 tokens_device = self.sampler.sample(logits, params, draws)
         if tokens_device is None:

@@ -74,6 +74,9 @@ class StepContext:
     tile_tc_count: torch.Tensor | None = None    # two sets
     # host copies, for parts that plan on the host (and for tests)
     host_rows: tuple = ()                # (request_id, first position, count, state_slot, fresh) per entry
+    signature: tuple = ()                # sizes and flags that fix the step's launches (two steps with the
+                                         # same signature differ in the contents of their tensors only)
+    arena: torch.Tensor | None = None    # the int32 tensor all the fields above are views of
 
     def writes_cache(self, run: int) -> bool:
         return self.cache_sources[run] is None
@@ -81,6 +84,16 @@ class StepContext:
     def workspace(self, floats: int) -> torch.Tensor:
         return self.workspace_of(floats)
 
+
+
+@dataclass
+class _StepGraph:
+    """A captured step: the graph, the tensor its fields are copied into, its logits."""
+
+    graph: object
+    arena: torch.Tensor
+    logits: torch.Tensor | None
+    ctx: StepContext                      # keeps the views the graph reads alive
 
 
 class StepRunner:
@@ -106,6 +119,11 @@ class StepRunner:
         self._pinned: torch.Tensor | None = None
         self._pinned_free: torch.cuda.Event | None = None
         self._workspace: torch.Tensor | None = None
+        self._retired_workspaces: list[torch.Tensor] = []
+        self._step_graph_limit = 0
+        self._step_graphs: dict[tuple, _StepGraph] = {}
+        self._step_seen: dict[tuple, int] = {}
+        self._step_graph_pool = None
         self.decode_splits = attention_ops.decode_splits(self.max_model_len)
         # prefill tiles are cut for the tcgen05 attention kernel if every mixer says it takes them
         blocks = getattr(model, "blocks", ())
@@ -133,6 +151,8 @@ class StepRunner:
         if self._workspace is None or self._workspace.numel() < floats:
             if torch.cuda.is_current_stream_capturing():
                 raise StepError("scratch memory must be sized before a graph is captured")
+            if self._workspace is not None:
+                self._retired_workspaces.append(self._workspace)      # captured graphs may still name it
             self._workspace = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
         return self._workspace
 
@@ -167,8 +187,11 @@ class StepRunner:
         return self.manager.plan([(e.request_id, len(e.tokens)) for e in entries])
 
     def build_context(self, entries: Sequence[StepEntry], plan: StepCachePlan,
-                      *, split_chunks: int | None = None) -> StepContext:
-        """Lower entries + cache plan to device tensors (one pinned buffer, one copy)."""
+                      *, split_chunks: int | None = None, arena_of=None) -> StepContext:
+        """Lower entries + cache plan to device tensors (one pinned buffer, one copy).
+
+        ``arena_of(signature, count)`` may name the int32 device tensor the step's fields are
+        copied into (a captured graph reads its own); else a new one is allocated."""
         rows = len(entries)
         counts = [len(e.tokens) for e in entries]
         tokens = sum(counts)
@@ -217,13 +240,15 @@ class StepRunner:
             view(tiles_at + i)[:] = tile_lists[i]
             view(tiles_at + 3 + i)[:] = tc_lists[i]
 
-        device = self._upload(host)
+        if split_chunks is None:
+            split_chunks = attention_ops.choose_split(tokens, max_position)
+        # all that decides which kernels a step launches and with which sizes
+        signature = (tuple(sizes), decode_only, split_chunks)
+        device = self._upload(host, None if arena_of is None else arena_of(signature, host.shape[0]))
 
         def dview(i):
             return device[int(offsets[i]):int(offsets[i]) + sizes[i]]
 
-        if split_chunks is None:
-            split_chunks = attention_ops.choose_split(tokens, max_position)
         fresh = [p.state_slot for p in plan.entries if p.fresh_state]
         self.storage.clear_state(fresh)
         return StepContext(
@@ -243,9 +268,10 @@ class StepRunner:
             tile_tc_count=dview(tiles_at + 5) if tiled else None,
             host_rows=tuple((p.request_id, p.start, p.count, p.state_slot, p.fresh_state)
                             for p in plan.entries),
+            signature=signature, arena=device,
         )
 
-    def _upload(self, host: np.ndarray) -> torch.Tensor:
+    def _upload(self, host: np.ndarray, device: torch.Tensor | None = None) -> torch.Tensor:
         count = host.shape[0]
         if self._pinned is None or self._pinned.numel() < count:
             if self._pinned_free is not None:
@@ -255,7 +281,8 @@ class StepRunner:
         if self._pinned_free is not None:
             self._pinned_free.synchronize()          # the previous step's copy has left the buffer
         self._pinned[:count].numpy()[:] = host
-        device = torch.empty(count, dtype=torch.int32, device=self.device)
+        if device is None:
+            device = torch.empty(count, dtype=torch.int32, device=self.device)
         device.copy_(self._pinned[:count], non_blocking=True)
         self._pinned_free = torch.cuda.Event()
         self._pinned_free.record()
@@ -263,6 +290,59 @@ class StepRunner:
 
     def execute(self, ctx: StepContext) -> torch.Tensor | None:
         return self.model.forward(ctx)
+
+    # ------------------------------------------------- steps as CUDA graphs
+    def enable_step_graphs(self, limit: int = 16) -> None:
+        """Steps whose signature (token, row, block and tile counts) comes back are captured as CUDA
+        graphs at their second occurrence and replayed from the third: the host then issues one
+        launch instead of some ten a layer.  At most ``limit`` graphs are kept; they share one
+        memory pool.  Only for models whose parts do all per-step work in kernels (no host-side
+        planning from ``host_rows``)."""
+        self._step_graph_limit = limit
+
+    @torch.inference_mode()
+    def forward(self, entries: Sequence[StepEntry], plan: StepCachePlan) -> torch.Tensor | None:
+        """The step's logits, through a captured graph if this kind of step has one."""
+        if self._step_graph_limit <= 0:
+            return self.execute(self.build_context(entries, plan))
+        chosen = {}
+
+        def arena_of(signature, count):
+            chosen["signature"] = signature
+            graph = self._step_graphs.get(signature)
+            if graph is not None:
+                chosen["graph"] = graph
+                return graph.arena
+            seen = self._step_seen.get(signature, 0) + 1
+            self._step_seen[signature] = seen
+            if seen >= 2 and len(self._step_graphs) < self._step_graph_limit:
+                chosen["capture"] = True
+                return torch.empty(count, dtype=torch.int32, device=self.device)
+            return None
+
+        ctx = self.build_context(entries, plan, arena_of=arena_of)
+        graph = chosen.get("graph")
+        if graph is not None:
+            graph.graph.replay()
+            return graph.logits
+        logits = self.execute(ctx)
+        if chosen.get("capture"):
+            self._capture_step(ctx)
+        return logits
+
+    def _capture_step(self, ctx: StepContext) -> None:
+        """Record the launches of a step that has just run eagerly on ``ctx`` (nothing runs again)."""
+        graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(graph, pool=self._step_graph_pool):
+                logits = self.model.forward(ctx)
+        except Exception:
+            self._step_graph_limit = 0        # a part that cannot be captured: stay eager from now on
+            torch.cuda.synchronize()
+            raise
+        if self._step_graph_pool is None:
+            self._step_graph_pool = graph.pool()
+        self._step_graphs[ctx.signature] = _StepGraph(graph, ctx.arena, logits, ctx)
 
     @torch.inference_mode()
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
@@ -275,8 +355,7 @@ class StepRunner:
                 + ", ".join(f"group {g} has {self.manager.free_pages(g)} free pages"
                             for g in range(len(self.manager.groups))))
         try:
-            ctx = self.build_context(entries, plan)
-            logits = self.execute(ctx)
+            logits = self.forward(entries, plan)
         except BaseException:
             self.manager.rollback(plan)
             raise
