@@ -12,21 +12,27 @@
 // memory of the cluster's first CTA (distributed shared memory), which merges them
 // in rank order: no scratch in global memory and no second kernel.
 //
-// LPK = head_dim / 8 lanes share a key, each lane holding 8 dimensions (one 16-byte
-// copy).  Every warp walks its keys through a ring of cp.async stages of its own in
-// shared memory; the cache slots of its keys are looked up once, up front, and the
-// first stage is in flight before the kernel waits for the projection (keys and
-// values already in the cache do not depend on it).  Scores, softmax and output sums
-// are float32.  The size of a split follows from the request's own position (and
-// window) alone, so its result does not depend on the batch it is in.
+// Every warp walks its keys in tiles of 8 through a ring of cp.async stages of its own in shared
+// memory (16-byte chunks swizzled by the key, so that ldmatrix reads them without bank conflicts);
+// the cache slots of its keys are looked up once, up front, and the first stages are in flight
+// before the kernel waits for the projection (keys and values already in the cache do not depend
+// on it).  The q heads of the CTA are the rows of an m16n8k16 tensor-core tile (rows past HPB are
+// zero): S = Q K^T and O += P V are mma.sync with float32 accumulators (the second product's k of
+// 16 is the tile's 8 keys and 8 zeros), a quarter of the instructions of a dot product spread
+// over lanes.  Small tiles and four warps keep a CTA's shared memory at 47 KB, so that four CTAs
+// share an SM: measured, residency counts for more here than instructions (tiles of 16 keys were
+// slower than the dot products they replaced, tiles of 8 are faster).  Softmax is float32; P is
+// rounded to bfloat16 for the second product while the denominator sums the unrounded values (as
+// tinyvllm/kernels/paged_decode.cu:322-356 does).  The size of a split follows from the request's
+// own position (and window) alone, so its result does not depend on the batch it is in.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
 
-#define DEC_WARPS 8
-#define DEC_UNROLL 2        // key rows a warp loads per stage and matrix
+#define DEC_WARPS 4
+#define DEC_TILE 8          // keys of a stage (the second product's k = 16 is half zeros)
 #define DEC_STAGES 2        // stages of each warp's ring of keys and values in shared memory
 #define DEC_MAX_SPLITS 8
 
@@ -44,9 +50,26 @@ struct DecodeShared {
     float part_o[DEC_MAX_SPLITS][HPB][HEAD_DIM];
     float part_m[DEC_MAX_SPLITS][HPB];
     float part_l[DEC_MAX_SPLITS][HPB];
-    uint4 ring[DEC_WARPS][DEC_STAGES][2][DEC_UNROLL][32];   // per warp: stages of (keys, values), 16 B a lane
+    // per warp: stages of (keys, values) [16 keys][HEAD_DIM] bfloat16, chunk c of key k at c ^ (k & 7)
+    uint4 ring[DEC_WARPS][DEC_STAGES][2][DEC_TILE * HEAD_DIM / 8];
     // int slot[DEC_WARPS][warp_slot_capacity] follows
 };
+
+__device__ __forceinline__ void dec_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_address(p)));
+}
+__device__ __forceinline__ void dec_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_address(p)));
+}
+// d += a . b for a 16 x 16 tile whose rows 8..15 are zero (a1 = a3 = 0)
+__device__ __forceinline__ void dec_mma(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    const uint32_t zero = 0u;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
+}
 
 // RMSNorm + half-split rotation of one head by one warp; result rounded to bfloat16, as float.
 // `src` was written by the kernel before this one: read through volatile loads.
@@ -106,9 +129,10 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         bf16* __restrict__ value_cache, const int* __restrict__ block_tables,
                         int table_stride, int page_size, bf16* __restrict__ out, int num_q, int num_kv,
                         int window, float scale, int write_cache, int warp_slot_capacity) {
-    constexpr int LPK = HEAD_DIM / 8;          // lanes that share one key
-    constexpr int KPI = 32 / LPK;              // keys per warp instruction
-    constexpr int WARP_KEYS = KPI * DEC_UNROLL;
+    constexpr int CPR = HEAD_DIM / 8;          // 16-byte chunks of a key's row
+    constexpr int KPI = 32 / CPR;              // keys a warp copies per instruction
+    constexpr int WARP_KEYS = DEC_TILE;
+    static_assert(HPB <= 8 && 32 % CPR == 0 && DEC_TILE % KPI == 0 && HEAD_DIM % 32 == 0, "shape of the tile");
     extern __shared__ __align__(16) unsigned char shared_raw[];
     DecodeShared<HEAD_DIM, HPB>& sh = *reinterpret_cast<DecodeShared<HEAD_DIM, HPB>*>(shared_raw);
     int* slot_s = reinterpret_cast<int*>(shared_raw + sizeof(DecodeShared<HEAD_DIM, HPB>));
@@ -142,8 +166,8 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     const int base = range_first + split * split_keys;
     const int first = max(lo, base);
     const int last = min(position - 1, base + split_keys - 1);
-    const int sub = lane % LPK;                 // which 8 dimensions of a key this lane holds
-    const int key_in_instr = lane / LPK;
+    const int sub = lane % CPR;                 // which 16-byte chunk of a key's row this lane copies
+    const int key_in_instr = lane / CPR;
     const int* table = block_tables + (int64_t)row * table_stride;
     // the cache is [pages, num_kv, page, head_dim]: a key's row for this kv head
     const int64_t row_stride = HEAD_DIM;
@@ -171,13 +195,16 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     __syncwarp();
 
     auto issue = [&](int i) {                   // the i-th sub-tile of this warp into stage i % DEC_STAGES
-        uint4(*stage)[DEC_UNROLL][32] = sh.ring[warp][i % DEC_STAGES];
+        uint4* keys_to = sh.ring[warp][i % DEC_STAGES][0];
+        uint4* values_to = sh.ring[warp][i % DEC_STAGES][1];
 #pragma unroll
-        for (int u = 0; u < DEC_UNROLL; ++u) {
-            const int slot = my_slots[i * WARP_KEYS + u * KPI + key_in_instr];
+        for (int u = 0; u < DEC_TILE / KPI; ++u) {
+            const int key = u * KPI + key_in_instr;
+            const int slot = my_slots[i * WARP_KEYS + key];
             const int64_t offset = (int64_t)max(slot, 0) * row_stride;
-            cp_async_16(&stage[0][u][lane], k_base + offset, slot >= 0);
-            cp_async_16(&stage[1][u][lane], v_base + offset, slot >= 0);
+            const int at = key * CPR + (sub ^ (key & 7));
+            cp_async_16(keys_to + at, k_base + offset, slot >= 0);
+            cp_async_16(values_to + at, v_base + offset, slot >= 0);
         }
     };
 #pragma unroll
@@ -230,92 +257,98 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         }
     }
 
-    float q_reg[HPB][8];
+    // ---- q as the a operand: row g of the tile is q head g (zero past HPB), two registers a k step
+    const int g = lane >> 2, t4 = lane & 3;
+    uint32_t q_frag[HEAD_DIM / 16][2];
 #pragma unroll
-    for (int h = 0; h < HPB; ++h)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q_reg[h][i] = sh.q[h][sub * 8 + i];
-    float m_run[HPB], l_run[HPB], o_run[HPB][8];
-#pragma unroll
-    for (int h = 0; h < HPB; ++h) {
-        m_run[h] = -INFINITY;
-        l_run[h] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o_run[h][i] = 0.0f;
+    for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+        q_frag[ks][0] = q_frag[ks][1] = 0u;
+        if (g < HPB) {
+            const float* qh = sh.q[g] + ks * 16 + 2 * t4;
+            q_frag[ks][0] = pack_bf16x2(qh[0], qh[1]);
+            q_frag[ks][1] = pack_bf16x2(qh[8], qh[9]);
+        }
     }
+    float m_run = -INFINITY, l_run = 0.0f;      // of row g; the four lanes of a row hold the same
+    float o_run[HEAD_DIM / 8][4];               // [n tile][row g: columns 2 t4, 2 t4 + 1 | row g + 8: unused]
+#pragma unroll
+    for (int n = 0; n < HEAD_DIM / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o_run[n][i] = 0.0f;
 
     for (int i = 0; i < mine; ++i) {
         if (i + DEC_STAGES - 1 < mine) issue(i + DEC_STAGES - 1);
         cp_async_commit();
-        cp_async_wait<DEC_STAGES - 1>();        // sub-tile i has landed (a lane reads only what it copied)
-        const uint4(*stage)[DEC_UNROLL][32] = sh.ring[warp][i % DEC_STAGES];
+        cp_async_wait<DEC_STAGES - 1>();        // sub-tile i has landed ...
+        __syncwarp();                           // ... for every lane of the warp
+        const uint4* k_tile = sh.ring[warp][i % DEC_STAGES][0];
+        const uint4* v_tile = sh.ring[warp][i % DEC_STAGES][1];
         const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
-        bool valid[DEC_UNROLL];
-        float score[HPB][DEC_UNROLL];
+
+        // S[row][key] for the 8 keys of the tile
+        float s_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        {
+            const int key = lane & 7;
 #pragma unroll
-        for (int u = 0; u < DEC_UNROLL; ++u) {
-            const int key = key0 + u * KPI + key_in_instr;
-            valid[u] = key >= first && key <= last;
-            float kf[8];
-            unpack_bf16x8(stage[0][u][lane], kf);
-#pragma unroll
-            for (int h = 0; h < HPB; ++h) {
-                float dot = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) dot = __fmaf_rn(q_reg[h][j], kf[j], dot);
-#pragma unroll
-                for (int delta = LPK / 2; delta > 0; delta >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, delta);
-                score[h][u] = valid[u] ? __fmul_rn(dot, scale) : -INFINITY;
+            for (int ks2 = 0; ks2 < HEAD_DIM / 32; ++ks2) {
+                uint32_t b[4];
+                const int chunk = ks2 * 4 + (lane >> 3);
+                dec_ldmatrix_x4(b, k_tile + key * CPR + (chunk ^ key));
+                dec_mma(s_acc, q_frag[2 * ks2][0], q_frag[2 * ks2][1], b[0], b[1]);
+                dec_mma(s_acc, q_frag[2 * ks2 + 1][0], q_frag[2 * ks2 + 1][1], b[2], b[3]);
             }
         }
-        float prob[HPB][DEC_UNROLL];
+        // online softmax of row g over the 8 keys (this lane holds keys 2 t4, 2 t4 + 1)
+        float score[2];
+        bool valid[2];
+        float tile_max = -INFINITY;
 #pragma unroll
-        for (int h = 0; h < HPB; ++h) {
-            float tile_max = score[h][0];
-#pragma unroll
-            for (int u = 1; u < DEC_UNROLL; ++u) tile_max = fmaxf(tile_max, score[h][u]);
-#pragma unroll
-            for (int delta = LPK; delta < 32; delta <<= 1)
-                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, delta));
-            const float new_max = fmaxf(m_run[h], tile_max);      // finite: the sub-tile has a valid key
-            const float rescale = m_run[h] == -INFINITY ? 0.0f : __expf(m_run[h] - new_max);
-            m_run[h] = new_max;
-            float sum = 0.0f;
-#pragma unroll
-            for (int u = 0; u < DEC_UNROLL; ++u) {
-                prob[h][u] = valid[u] ? __expf(score[h][u] - new_max) : 0.0f;
-                sum += prob[h][u];
-            }
-            l_run[h] = l_run[h] * rescale + sum;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o_run[h][j] *= rescale;
+        for (int e = 0; e < 2; ++e) {
+            const int key = key0 + 2 * t4 + e;
+            valid[e] = key >= first && key <= last;
+            score[e] = valid[e] ? __fmul_rn(s_acc[e], scale) : -INFINITY;
+            tile_max = fmaxf(tile_max, score[e]);
         }
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+        const float new_max = fmaxf(m_run, tile_max);          // finite: the sub-tile has a valid key
+        const float rescale = m_run == -INFINITY ? 0.0f : __expf(m_run - new_max);
+        const bool moved = __any_sync(0xffffffffu, new_max != m_run);
+        m_run = new_max;
+        float prob[2];
 #pragma unroll
-        for (int u = 0; u < DEC_UNROLL; ++u) {
-            float vf[8];
-            unpack_bf16x8(stage[1][u][lane], vf);   // zero where there is no key
+        for (int e = 0; e < 2; ++e) prob[e] = valid[e] ? __expf(score[e] - new_max) : 0.0f;
+        float sum = prob[0] + prob[1];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_run = l_run * rescale + sum;
+        const uint32_t p_lo = pack_bf16x2(prob[0], prob[1]);            // keys 0..7; k 8..15 of the product are zero
+        if (moved) {
 #pragma unroll
-            for (int h = 0; h < HPB; ++h)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) o_run[h][j] = __fmaf_rn(prob[h][u], vf[j], o_run[h][j]);
+            for (int n = 0; n < HEAD_DIM / 8; ++n) { o_run[n][0] *= rescale; o_run[n][1] *= rescale; }
         }
+        // O += P V, 32 head dimensions (four n tiles) per ldmatrix
+#pragma unroll
+        for (int n4 = 0; n4 < HEAD_DIM / 32; ++n4) {
+            uint32_t b[4];
+            const int key = lane & 7;
+            const int chunk = n4 * 4 + (lane >> 3);
+            dec_ldmatrix_x4_trans(b, v_tile + key * CPR + (chunk ^ key));
+#pragma unroll
+            for (int m = 0; m < 4; ++m) dec_mma(o_run[4 * n4 + m], p_lo, 0u, b[m], 0u);
+        }
+        __syncwarp();                           // the stage may be filled again
     }
     pdl_launch_dependents();
 
-    // ---- lanes that hold the same dimensions for different keys, then the warps, in a fixed order
+    // ---- the warps' partial results, merged below in a fixed order
+    if (g < HPB) {
 #pragma unroll
-    for (int h = 0; h < HPB; ++h) {
-#pragma unroll
-        for (int delta = LPK; delta < 32; delta <<= 1) {
-            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], delta);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o_run[h][i] += __shfl_xor_sync(0xffffffffu, o_run[h][i], delta);
+        for (int n = 0; n < HEAD_DIM / 8; ++n) {
+            sh.warp_o[warp][g][n * 8 + 2 * t4] = o_run[n][0];
+            sh.warp_o[warp][g][n * 8 + 2 * t4 + 1] = o_run[n][1];
         }
-        if (lane < LPK) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sh.warp_o[warp][h][sub * 8 + i] = o_run[h][i];
-        }
-        if (lane == 0) { sh.warp_m[warp][h] = m_run[h]; sh.warp_l[warp][h] = l_run[h]; }
+        if (t4 == 0) { sh.warp_m[warp][g] = m_run; sh.warp_l[warp][g] = l_run; }
     }
     __syncthreads();
     DecodeShared<HEAD_DIM, HPB>* first_cta = cluster.map_shared_rank(&sh, 0);
@@ -365,7 +398,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
 
 template <int HEAD_DIM>
 static int decode_warp_slot_capacity(int max_context, int splits) {
-    constexpr int WARP_KEYS = (32 / (HEAD_DIM / 8)) * DEC_UNROLL;
+    constexpr int WARP_KEYS = DEC_TILE;
     const int split_keys = ((max_context + splits - 1) / splits + 63) / 64 * 64 + 64;
     return (split_keys / (WARP_KEYS * DEC_WARPS) + 2) * WARP_KEYS;
 }
