@@ -158,3 +158,62 @@ def test_attention_part_refuses_head_sizes_the_kernels_do_not_take():
               head_dim=24, scale=1.0, qk_norm_eps=None, window=None)
     with pytest.raises(KeyError, match="no mixer part named 'nope'"):
         build("mixer", "nope", torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_block_part_alone(dtype):
+    """The arrangement of a layer (norm, mixer, norm, feed-forward, deferred residual sums) alone,
+    as the first layer (no stream yet) and as a later one, in portions, against the plain parts."""
+    from tinyvllm_b200.config.spec import PartSpec
+    from tinyvllm_b200.engine.step import StepEntry, StepRunner
+    from tinyvllm_b200.parts import BuildContext, build_part
+    hidden, inter, nq, nkv, d, eps = 72, 104, 4, 2, 32, 3e-6
+    spec = PartSpec("prenorm_residual", {
+        "mixer_norm_name": "input_layernorm", "feed_forward_norm_name": "post_attention_layernorm",
+        "mixer_name": "self_attn", "feed_forward_name": "mlp"})
+    block = build_part(
+        "block", spec, BuildContext(DEV, dtype, "L", build_part),
+        mixer=PartSpec("gqa_attention", {
+            "hidden_size": hidden, "num_heads": nq, "num_kv_heads": nkv, "head_dim": d, "scale": d ** -0.5,
+            "qk_norm_eps": eps, "window": None,
+            "position": PartSpec("rope_half_split", {"head_dim": d, "theta": 1e4, "max_positions": 1024})}),
+        feed_forward=PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": inter}),
+        norm=PartSpec("rms_norm", {"width": hidden, "eps": eps}))
+    w = bind_random(block, dtype, seed=3)
+    runner = StepRunner(OnePartModel(block.mixer, dtype, max_positions=1024), page_size=8, num_pages=64,
+                        max_requests=2)
+    torch.manual_seed(5)
+    tokens = 140
+    x = torch.randn(tokens, hidden).to(dtype)
+    stream = torch.randn(tokens, hidden).to(dtype)
+    cfg = {"nq": nq, "nkv": nkv, "d": d, "eps": eps}
+    cos, sin = plain.rope_tables(d, tokens, 1e4)
+    for first_layer in (True, False):
+        if first_layer:
+            want_stream = x.float()
+            normed = plain.rms_norm(x.float(), w["L.input_layernorm.weight"], eps, dtype)
+        else:
+            normed, want_stream = plain.add_rms_norm(x.float(), stream.float(), w["L.input_layernorm.weight"],
+                                                     eps, dtype)
+        attended, _ = plain.attention_block(cfg, w, "L", normed, cos, sin, None, dtype)
+        normed, want_stream = plain.add_rms_norm(attended, want_stream, w["L.post_attention_layernorm.weight"],
+                                                 eps, dtype)
+        want = plain.mlp_block(w, "L", normed, dtype)
+        rid = f"r{first_layer}"
+        runner.open(rid)
+        outs, streams, start = [], [], 0
+        with torch.inference_mode():
+            for count in (100, 2, 37, 1):
+                entries = [StepEntry(rid, tuple([1] * count), ())]
+                plan = runner.plan(entries)
+                ctx = runner.build_context(entries, plan)
+                part = slice(start, start + count)
+                out, new_stream = block.forward(
+                    x[part].to(DEV).contiguous(), None if first_layer else stream[part].to(DEV).contiguous(),
+                    ctx, 0)
+                outs.append(out), streams.append(new_stream)
+                runner.manager.commit(plan)
+                start += count
+        runner.close(rid)
+        check(torch.cat(outs), want, dtype)
+        check(torch.cat(streams), want_stream, dtype)
