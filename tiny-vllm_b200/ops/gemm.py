@@ -1,6 +1,10 @@
 """bfloat16 matrix products: which kernel takes which shape.
 
-Up to 32 rows (decode): the package's weight-streaming kernel.  The packed gate/up product
+Up to 16 rows (decode) with a bfloat16 result: the package's weight-streaming kernel (measured
+against cuBLAS per shape: it wins up to 8 rows by 20 to 50 %, is level around 16 and loses
+beyond).  Results in float32 (the logits: vocabulary x width, the one product of a decode step
+that is long enough to be bound by bandwidth alone) go to cuBLAS with float32 output at every
+row count: 53 us against 84 us at 8 rows.  The packed gate/up product
 with its activation at 128 rows and more (prefill): the package's tcgen05 kernel, which keeps
 the accumulator in tensor memory and applies SiLU(gate) * up on the way out.  The other
 products with more than 32 rows: cuBLAS through ``torch.nn.functional.linear``, the library
@@ -32,11 +36,13 @@ def next_weight(weight: torch.Tensor) -> torch.Tensor | None:
 
 # rows from which the tcgen05 kernel's tiles of 128 rows are mostly full
 TC_MIN_ROWS = 128
+# rows up to which the weight-streaming kernel is chosen over cuBLAS
+SMALL_M_DISPATCH_ROWS = 16
 
 
 def small(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether the weight-streaming kernel takes this product."""
-    return (x.shape[0] <= kernels.SMALL_M_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+    return (x.shape[0] <= SMALL_M_DISPATCH_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
             and x.stride(0) % 8 == 0 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0)
 
 
@@ -46,21 +52,23 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype
         raise kernels.KernelError("linear_bf16 wants bfloat16 operands")
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise kernels.KernelError(f"linear_bf16 cannot produce {out_dtype}")
-    if small(x, weight):
-        mode = kernels.GEMM_BF16 if out_dtype == torch.bfloat16 else kernels.GEMM_F32
-        return kernels.gemm_small_m(x, weight, mode, out=out, prefetch=next_weight(weight))
-    if out_dtype == torch.bfloat16:
-        if out is not None:
-            return torch.mm(x, weight.t(), out=out)
-        return torch.nn.functional.linear(x, weight)
-    if x.shape[0] <= 256:
+    if out_dtype == torch.float32:
         # float32 results (logits) keep the float32 accumulator unrounded
-        return kernels.gemm_nt_simt(x, weight, out=out, out_dtype=torch.float32)
-    result = torch.nn.functional.linear(x, weight).float()
+        if x.stride(1) == 1 and weight.stride(1) == 1 and x.shape[1] % 8 == 0:
+            result = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        elif x.shape[0] <= 256:
+            return kernels.gemm_nt_simt(x, weight, out=out, out_dtype=torch.float32)
+        else:
+            result = torch.nn.functional.linear(x, weight).float()
+        if out is not None:
+            out.copy_(result)
+            return out
+        return result
+    if small(x, weight):
+        return kernels.gemm_small_m(x, weight, kernels.GEMM_BF16, out=out, prefetch=next_weight(weight))
     if out is not None:
-        out.copy_(result)
-        return out
-    return result
+        return torch.mm(x, weight.t(), out=out)
+    return torch.nn.functional.linear(x, weight)
 
 
 def linear_silu_bf16(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
