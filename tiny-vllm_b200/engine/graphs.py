@@ -17,6 +17,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from ..ops import attention as attention_ops
 from ..ops import kernels
 from ..sampling.sampler import ROW_WORDS, pack_rows, sample_packed
 from .step import StepContext
@@ -82,7 +83,7 @@ class DecodeGraphs:
                           for g in range(groups)],
             cache_sources=self.runner.cache_sources, max_position=self.max_model_len - 1,
             split_chunks=self.split_chunks, workspace_of=self.runner._workspace_of,
-            decode_only=True, decode_splits=self.runner.decode_splits,
+            decode_only=True, decode_splits=attention_ops.decode_splits(self.max_model_len, size),
             max_context=self.max_model_len)
 
     def _fill_padding(self, bucket: _Bucket) -> None:

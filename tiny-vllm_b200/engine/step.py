@@ -259,7 +259,7 @@ class StepRunner:
             block_tables=[dview(7 + 2 * g).view(rows, blocks[g]) for g in range(groups)],
             cache_sources=self.cache_sources, max_position=max_position, split_chunks=split_chunks,
             workspace_of=self._workspace_of, decode_only=decode_only,
-            decode_splits=self.decode_splits, max_context=self.max_model_len,
+            decode_splits=attention_ops.decode_splits(self.max_model_len, rows), max_context=self.max_model_len,
             tile_row=dview(tiles_at) if tiled else None,
             tile_first=dview(tiles_at + 1) if tiled else None,
             tile_count=dview(tiles_at + 2) if tiled else None,
