@@ -312,7 +312,7 @@ def eager_profile(args, warmup: int) -> int:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"])

@@ -86,6 +86,10 @@ class StepContext:
 
 
 
+# block-table widths are multiples of this many pages
+TABLE_WIDTH_GRAIN = 8
+
+
 @dataclass
 class _StepGraph:
     """A captured step: the graph, the tensor its fields are copied into, its logits."""
@@ -94,6 +98,7 @@ class _StepGraph:
     arena: torch.Tensor
     logits: torch.Tensor | None
     ctx: StepContext                      # keeps the views the graph reads alive
+    last_used: int = 0                    # step count at its last replay
 
 
 class StepRunner:
@@ -124,6 +129,7 @@ class StepRunner:
         self._step_graphs: dict[tuple, _StepGraph] = {}
         self._step_seen: dict[tuple, int] = {}
         self._step_graph_pool = None
+        self._step_count = 0
         self.decode_splits = attention_ops.decode_splits(self.max_model_len)
         # prefill tiles are cut for the tcgen05 attention kernel if every mixer says it takes them
         blocks = getattr(model, "blocks", ())
@@ -197,7 +203,9 @@ class StepRunner:
         tokens = sum(counts)
         wanted = sum(len(e.want) for e in entries)
         groups = len(self.manager.groups)
-        blocks = [max(1, max(len(p.tables[g]) for p in plan.entries)) for g in range(groups)]
+        # block tables as wide as the longest, rounded up so that steps of growing requests share a shape
+        blocks = [-(-max(1, max(len(p.tables[g]) for p in plan.entries)) // TABLE_WIDTH_GRAIN) * TABLE_WIDTH_GRAIN
+                  for g in range(groups)]
         decode_only = all(count == 1 for count in counts)
         # only the bfloat16 tile kernel reads tile lists; the 32-bit path walks rows
         tiled = not decode_only and self.storage.dtype == torch.bfloat16
@@ -295,8 +303,8 @@ class StepRunner:
     def enable_step_graphs(self, limit: int = 16) -> None:
         """Steps whose signature (token, row, block and tile counts) comes back are captured as CUDA
         graphs at their second occurrence and replayed from the third: the host then issues one
-        launch instead of some ten a layer.  At most ``limit`` graphs are kept; they share one
-        memory pool.  Only for models whose parts do all per-step work in kernels (no host-side
+        launch instead of some ten a layer.  At most ``limit`` graphs are kept (the one unused for
+        longest makes room); they share one memory pool.  Only for models whose parts do all per-step work in kernels (no host-side
         planning from ``host_rows``)."""
         self._step_graph_limit = limit
 
@@ -309,13 +317,21 @@ class StepRunner:
 
         def arena_of(signature, count):
             chosen["signature"] = signature
+            self._step_count += 1
             graph = self._step_graphs.get(signature)
             if graph is not None:
+                graph.last_used = self._step_count
                 chosen["graph"] = graph
                 return graph.arena
             seen = self._step_seen.get(signature, 0) + 1
+            if len(self._step_seen) > 4096:
+                self._step_seen.clear()
             self._step_seen[signature] = seen
-            if seen >= 2 and len(self._step_graphs) < self._step_graph_limit:
+            if seen >= 2:
+                if len(self._step_graphs) >= self._step_graph_limit:
+                    # the graph that has waited longest for its shape to come back makes room
+                    oldest = min(self._step_graphs, key=lambda key: self._step_graphs[key].last_used)
+                    del self._step_graphs[oldest]
                 chosen["capture"] = True
                 return torch.empty(count, dtype=torch.int32, device=self.device)
             return None
@@ -342,7 +358,7 @@ class StepRunner:
             raise
         if self._step_graph_pool is None:
             self._step_graph_pool = graph.pool()
-        self._step_graphs[ctx.signature] = _StepGraph(graph, ctx.arena, logits, ctx)
+        self._step_graphs[ctx.signature] = _StepGraph(graph, ctx.arena, logits, ctx, self._step_count)
 
     @torch.inference_mode()
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
