@@ -6,7 +6,7 @@
 #include "common.cuh"
 
 // -------------------------------------------------------------------- RMSNorm
-// TPR threads share a row (32: one warp, 8 rows a CTA; 256: the whole CTA).  A thread holds up to
+// TPR threads share a row (32: one warp, 8 rows a CTA; 64, 128; 256: the whole CTA).  A thread holds up to
 // 4 words of 8 values.  `x` and `residual` come from the kernel before: coherent loads.
 #define NORM_WORDS 4
 
@@ -16,6 +16,7 @@ rms_norm_bf16_kernel(const bf16* x, const bf16* residual, const W* __restrict__ 
                      bf16* __restrict__ y, bf16* __restrict__ residual_out,
                      const int* __restrict__ gather, int rows, int width, float eps) {
     __shared__ float scratch[32];
+    __shared__ float row_parts[8];
     pdl_wait();
     pdl_launch_dependents();
     const int rows_per_cta = 256 / TPR;
@@ -43,7 +44,20 @@ rms_norm_bf16_kernel(const bf16* x, const bf16* residual, const W* __restrict__ 
             if (residual_out) *reinterpret_cast<uint4*>(residual_out + (int64_t)out_row * width + at) = pack_bf16x8(values[i]);
         }
     }
-    squares = TPR == 32 ? warp_sum(squares) : block_sum(squares, scratch);
+    if (TPR == 32) {
+        squares = warp_sum(squares);
+    } else if (TPR == 256) {
+        squares = block_sum(squares, scratch);
+    } else {
+        // TPR / 32 warps share a row: their sums meet in shared memory and are added in warp order
+        squares = warp_sum(squares);
+        if ((threadIdx.x & 31) == 0) row_parts[threadIdx.x >> 5] = squares;
+        __syncthreads();
+        const int first_warp = (threadIdx.x / TPR) * (TPR / 32);
+        squares = 0.0f;
+#pragma unroll
+        for (int w = 0; w < TPR / 32; ++w) squares = __fadd_rn(squares, row_parts[first_warp + w]);
+    }
     const float inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(squares, 1.0f / (float)width), eps)));
 #pragma unroll
     for (int i = 0; i < NORM_WORDS; ++i) {
@@ -65,18 +79,29 @@ extern "C" int tvb_rms_norm_bf16(const void* x, const void* residual, const void
                                  int weight_dtype, int pdl, void* stream) {
     if (rows <= 0) return 0;
     if (!tvb_rms_norm_bf16_supports(width)) return TVB_BAD_ARGUMENT;
-    // a warp per row when there are rows enough to fill the GPU that way, else a CTA per row
-    const bool warp_rows = width <= 8 * NORM_WORDS * 32 && rows >= 512;
-    const int rows_per_cta = warp_rows ? 8 : 1;
+    // threads that share a row: the fewer rows, the more, so that the GPU is filled either way
+    // (measured at width 1024: 8192 rows 32 or 64, 2048 rows 64, 512 rows 128, few rows 256); a
+    // thread holds at most NORM_WORDS words, which bounds the width a narrow team takes
+    int tpr = rows >= 4096 ? 32 : rows >= 1024 ? 64 : rows >= 256 ? 128 : 256;
+    while (width > 8 * NORM_WORDS * tpr) tpr *= 2;
+    const int rows_per_cta = 256 / tpr;
     TvbLaunch launch(dim3((rows + rows_per_cta - 1) / rows_per_cta), dim3(256), 0, (cudaStream_t)stream, pdl);
     cudaError_t e;
 #define NORM_LAUNCH(TPR, WT)                                                                          \
     e = cudaLaunchKernelEx(&launch.config, rms_norm_bf16_kernel<TPR, WT>, (const bf16*)x,             \
                            (const bf16*)residual, (const WT*)weight, (bf16*)y, (bf16*)residual_out,   \
                            gather, rows, width, eps)
-    if (weight_dtype == TVB_F32) { if (warp_rows) NORM_LAUNCH(32, float); else NORM_LAUNCH(256, float); }
-    else if (weight_dtype == TVB_BF16) { if (warp_rows) NORM_LAUNCH(32, bf16); else NORM_LAUNCH(256, bf16); }
+#define NORM_BY_TPR(WT)                                        \
+    do {                                                       \
+        if (tpr == 32) NORM_LAUNCH(32, WT);                    \
+        else if (tpr == 64) NORM_LAUNCH(64, WT);               \
+        else if (tpr == 128) NORM_LAUNCH(128, WT);             \
+        else NORM_LAUNCH(256, WT);                             \
+    } while (0)
+    if (weight_dtype == TVB_F32) NORM_BY_TPR(float);
+    else if (weight_dtype == TVB_BF16) NORM_BY_TPR(bf16);
     else return TVB_BAD_ARGUMENT;
+#undef NORM_BY_TPR
 #undef NORM_LAUNCH
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
