@@ -381,7 +381,7 @@ def run_prefill_tc(case, *, nq, nkv, d, window, scale):
             counts.append(0), starts.append(position)
             previous = row
         counts[-1] += 1
-    big, rest = prefill_tiles(counts, starts, tensor_memory=True)
+    big, rest, _ = prefill_tiles(counts, starts, tensor_memory=True)
     as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     kc, vc = finite_cache(case, torch.bfloat16)
     q = case["q"].to(DEV).view(-1, nq * d)
@@ -489,6 +489,17 @@ def test_attention_decode_fused(shape, window):
     stored_k = by_slot(kc)[slots.long().to(DEV)]
     close(stored_k, want_k, dtype, bf16=1.6e-2)
     assert torch.equal(by_slot(vc)[slots.long().to(DEV)].float().cpu(), vn)
+    # the same tokens once more, now that their keys and values are in the cache and with q
+    # prepared (the decoded tokens of a step that also holds prompt portions): the same result
+    prepared = qkv.clone()
+    prepared[:, :nq * d] = want_q.reshape(requests, nq * d).to(dtype)
+    prepared[:, nq * d:] = 0                                   # k and v of the projection are not read
+    again = k().attention_decode(
+        prepared.to(DEV), num_q=nq, num_kv=nkv, head_dim=d, positions=positions.to(DEV),
+        token_row=case["token_row"].to(DEV), slots=None, q_weight=None, k_weight=None, eps=0.0, cos=None,
+        sin=None, key_cache=kc, value_cache=vc, block_tables=case["tables"].to(DEV), window=window,
+        scale=d ** -0.5, splits=splits, max_context=1024, new_in_cache=True).view(requests, nq, d)
+    close(again, torch.stack(rows), dtype, bf16=1.2e-2)
 
 
 def test_attention_decode_padding_and_unsupported():

@@ -165,7 +165,10 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     const int own_split = (position - range_first) / split_keys;     // holds the new token
     const int base = range_first + split * split_keys;
     const int first = max(lo, base);
-    const int last = min(position - 1, base + split_keys - 1);
+    // write_cache 2: the new token's key and value are in the cache already (and q is ready): it is
+    // a key like the others, nothing of it is taken from the projection
+    const bool cached_new = write_cache == 2;
+    const int last = min(cached_new ? position : position - 1, base + split_keys - 1);
     const int sub = lane % CPR;                 // which 16-byte chunk of a key's row this lane copies
     const int key_in_instr = lane / CPR;
     const int* table = block_tables + (int64_t)row * table_stride;
@@ -221,7 +224,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         const int table_row = min(position, table_positions - 1);
         const float* cos_row = cos_table ? cos_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
         const float* sin_row = sin_table ? sin_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
-        for (int job = warp; job < HPB + 2; job += DEC_WARPS) {
+        for (int job = warp; job < (cached_new ? HPB : HPB + 2); job += DEC_WARPS) {
             if (job < HPB) {
                 norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(first_q_head + job) * HEAD_DIM, q_weight, eps,
                                               cos_row, sin_row, sh.q[job], lane);
@@ -236,8 +239,8 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     }
     __syncthreads();
 
-    if (split == own_split) {
-        if (write_cache && (blockIdx.y % blocks_per_kv) == 0) {
+    if (split == own_split && !cached_new) {
+        if (write_cache == 1 && (blockIdx.y % blocks_per_kv) == 0) {
             const int slot = slots[request];
             if (slot >= 0) {
                 const int64_t at = (((int64_t)(slot / page_size) * num_kv + kv_head) * page_size + slot % page_size) * HEAD_DIM;
@@ -364,7 +367,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
             l += sh.warp_l[w][h] * f;
             o += sh.warp_o[w][h][dim] * f;
         }
-        if (split == own_split) {               // the new token itself, from shared memory
+        if (split == own_split && !cached_new) {   // the new token itself, from shared memory
             const float s = sh.s_new[h];
             const float new_max = fmaxf(m, s);
             const float f_old = m == -INFINITY ? 0.0f : __expf(m - new_max);
@@ -438,6 +441,9 @@ extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv
 // request.  Caches: [pages, num_kv, page_size, head_dim].  weight_dtype: TVB_BF16 or TVB_F32 (norm weights; null pointers skip the norm).
 // splits (1..8) is the cluster size: the number of pieces every request's keys are cut into.
 // max_context bounds position + 1 of every request (it sizes the list of cache slots a warp keeps).
+// write_cache: 0 the new key and value are used but not stored, 1 they are stored in slot slots[i],
+// 2 they are in the cache already, as the other keys are, and q comes normalised and rotated (the
+// decoded tokens of a step that also holds prompt portions, after the pass that prepares all its tokens).
 extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                                     const float* cos_table, const float* sin_table, int table_positions,
                                     const int* positions, const int* token_row, const int* slots,

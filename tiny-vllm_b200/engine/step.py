@@ -74,6 +74,8 @@ class StepContext:
     tile_tc_count: torch.Tensor | None = None    # two sets
     # host copies, for parts that plan on the host (and for tests)
     host_rows: tuple = ()                # (request_id, first position, count, state_slot, fresh) per entry
+    single_runs: tuple = ()              # (first flat token, count) of runs of single-token entries beside
+                                         # prompt portions: not in the tile lists, the row kernel takes them
     signature: tuple = ()                # sizes and flags that fix the step's launches (two steps with the
                                          # same signature differ in the contents of their tensors only)
     arena: torch.Tensor | None = None    # the int32 tensor all the fields above are views of
@@ -210,10 +212,11 @@ class StepRunner:
         # only the bfloat16 tile kernel reads tile lists; the 32-bit path walks rows
         tiled = not decode_only and self.storage.dtype == torch.bfloat16
         if tiled:
-            tc_lists, tile_lists = attention_ops.prefill_tiles(
-                counts, [p.start for p in plan.entries], tensor_memory=self.tensor_memory_tiles)
+            tc_lists, tile_lists, single_runs = attention_ops.prefill_tiles(
+                counts, [p.start for p in plan.entries], tensor_memory=self.tensor_memory_tiles,
+                singles_apart=True)
         else:
-            tc_lists, tile_lists = ([], [], []), ([], [], [])
+            tc_lists, tile_lists, single_runs = ([], [], []), ([], [], []), ()
         sizes = [tokens, tokens, tokens, wanted, rows, rows + 1]
         for g in range(groups):
             sizes += [tokens, rows * blocks[g]]
@@ -251,7 +254,7 @@ class StepRunner:
         if split_chunks is None:
             split_chunks = attention_ops.choose_split(tokens, max_position)
         # all that decides which kernels a step launches and with which sizes
-        signature = (tuple(sizes), decode_only, split_chunks)
+        signature = (tuple(sizes), decode_only, split_chunks, single_runs)
         device = self._upload(host, None if arena_of is None else arena_of(signature, host.shape[0]))
 
         def dview(i):
@@ -276,7 +279,7 @@ class StepRunner:
             tile_tc_count=dview(tiles_at + 5) if tiled else None,
             host_rows=tuple((p.request_id, p.start, p.count, p.state_slot, p.fresh_state)
                             for p in plan.entries),
-            signature=signature, arena=device,
+            signature=signature, arena=device, single_runs=single_runs,
         )
 
     def _upload(self, host: np.ndarray, device: torch.Tensor | None = None) -> torch.Tensor:

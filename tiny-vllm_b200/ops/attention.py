@@ -54,20 +54,31 @@ def decode_splits(max_model_len: int, rows: int = 1) -> int:
 TC_MIN_TILE_TOKENS = 32
 
 
-def prefill_tiles(counts, starts=None, *, tensor_memory: bool = False):
+def prefill_tiles(counts, starts=None, *, tensor_memory: bool = False, singles_apart: bool = False):
     """Cut every entry of a step into tiles of consecutive tokens.
 
-    Returns two triples of lists (row, first flat token, count): tiles of up to 128 tokens for the
-    tcgen05 kernel, the longest context first, and tiles of up to 64 tokens for the mma.sync
-    kernel.  Without ``tensor_memory`` every token is in the second set; with it only the short
-    rests of entries are.  ``starts``: tokens each entry has in the cache before the step."""
+    Returns two triples of lists (row, first flat token, count) and a list of runs: tiles of up to
+    128 tokens for the tcgen05 kernel, the longest context first; tiles of up to 64 tokens for the
+    mma.sync kernel; and, with ``singles_apart``, (first flat token, count) of every run of
+    consecutive single-token entries (decoded tokens beside prompt portions), which go to the row
+    kernel with their keys spread over the grid instead of a 64-row tile each.  Without
+    ``tensor_memory`` nothing is in the first set; with it only the short rests of entries are in
+    the second.  ``starts``: tokens each entry has in the cache before the step."""
     small = kernels.attention_prefill_tile_tokens()
     large = kernels.attention_prefill_tc_tile_tokens() if tensor_memory else 0
     starts = starts if starts is not None else [0] * len(counts)
     big, ends = ([], [], []), []
     rest = ([], [], [])
+    runs: list[list[int]] = []
     cursor = 0
     for row, count in enumerate(counts):
+        if singles_apart and count == 1:
+            if runs and runs[-1][0] + runs[-1][1] == cursor:
+                runs[-1][1] += 1
+            else:
+                runs.append([cursor, 1])
+            cursor += 1
+            continue
         done = 0
         if tensor_memory:
             while count - done >= TC_MIN_TILE_TOKENS:
@@ -80,7 +91,7 @@ def prefill_tiles(counts, starts=None, *, tensor_memory: bool = False):
         cursor += count
     order = sorted(range(len(ends)), key=lambda i: -ends[i])
     big = tuple([column[i] for i in order] for column in big)
-    return big, rest
+    return big, rest, tuple((first, count) for first, count in runs)
 
 
 def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
@@ -120,6 +131,29 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
             kernels.attention_prefill(
                 qkv, qkv.shape[1], keys, values, ctx.block_tables[group], ctx.positions, ctx.tile_row,
                 ctx.tile_first, ctx.tile_count, **heads, window=mixer.window, scale=mixer.scale, out=out)
+        for first, count in ctx.single_runs:
+            # Decoded tokens beside the portions.  Their q is normalised and rotated and their k, v are
+            # in the cache already, so the fused decode kernel runs without its norm, rotation and
+            # cache write: context split over a cluster, keys streamed once per group of q heads.
+            part = slice(first, first + count)
+            splits = decode_splits(ctx.max_context, count)
+            if kernels.attention_decode_supports(mixer.head_dim, mixer.num_heads, mixer.num_kv_heads, splits):
+                kernels.attention_decode(
+                    qkv[part], **heads, positions=ctx.positions[part], token_row=ctx.token_row[part],
+                    slots=None, q_weight=None, k_weight=None, eps=0.0, cos=None, sin=None, key_cache=keys,
+                    value_cache=values, block_tables=ctx.block_tables[group], window=mixer.window,
+                    scale=mixer.scale, splits=splits, max_context=ctx.max_context, out=out[part],
+                    new_in_cache=True)
+                continue
+            chunks = choose_split(count, ctx.max_position)
+            scratch = None
+            if chunks > 0:
+                scratch = ctx.workspace(kernels.attention_rows_scratch_floats(
+                    count, mixer.num_heads, mixer.head_dim, chunks))
+            kernels.attention_rows(
+                qkv[part], qkv.shape[1], keys, values, ctx.block_tables[group], ctx.token_row[part],
+                ctx.positions[part], **heads, window=mixer.window, scale=mixer.scale, out=out[part],
+                scratch=scratch, max_chunks=chunks)
         return out
     scratch = None
     if ctx.split_chunks > 0:

@@ -356,9 +356,11 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
                      cos: torch.Tensor | None, sin: torch.Tensor | None, key_cache: torch.Tensor,
                      value_cache: torch.Tensor, block_tables: torch.Tensor, window: int | None,
                      scale: float, splits: int, max_context: int,
-                     out: torch.Tensor | None = None) -> torch.Tensor:
+                     out: torch.Tensor | None = None, new_in_cache: bool = False) -> torch.Tensor:
     """One new token per request, from the raw packed projection to the attention output:
     q/k norm and rotation, cache write (unless ``slots`` is None) and attention in one launch.
+    ``new_in_cache``: the new tokens' keys and values are in the cache already and q comes
+    prepared (no norm weights, no tables, no slots): only the attention is left to do.
     Request i is row ``token_row[i]`` of ``block_tables`` (-1: padding) and stands at
     ``positions[i]``.  Every request's keys are cut into ``splits`` pieces, one per CTA of a cluster;
     ``max_context`` bounds ``positions + 1``."""
@@ -379,6 +381,8 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     for t in (positions, token_row, block_tables) + ((slots,) if slots is not None else ()):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError("attention_decode: index tensors must be contiguous int32")
+    if new_in_cache and not (slots is None and q_weight is None and k_weight is None and cos is None and sin is None):
+        raise KernelError("attention_decode: with new_in_cache nothing is normalised, rotated or stored")
     weight_tag = BF16
     if q_weight is not None:
         if k_weight is None or q_weight.dtype != k_weight.dtype or q_weight.shape != (head_dim,):
@@ -397,7 +401,8 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
               positions.data_ptr(), token_row.data_ptr(), _ptr(slots), key_cache.data_ptr(),
               value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
               key_cache.shape[2], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
-              splits, 1 if slots is not None else 0, max_context, weight_tag, _pdl("attention"),
+              splits, 2 if new_in_cache else (1 if slots is not None else 0), max_context, weight_tag,
+              _pdl("attention"),
               _stream()),
            "attention_decode")
     return out
