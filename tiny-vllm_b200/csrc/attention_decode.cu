@@ -31,12 +31,11 @@
 
 namespace cg = cooperative_groups;
 
-#define DEC_WARPS 4
 #define DEC_TILE 8          // keys of a stage (the second product's k = 16 is half zeros)
 #define DEC_STAGES 2        // stages of each warp's ring of keys and values in shared memory
 #define DEC_MAX_SPLITS 8
 
-template <int HEAD_DIM, int HPB>
+template <int HEAD_DIM, int HPB, int DEC_WARPS>
 struct DecodeShared {
     float q[HPB][HEAD_DIM];            // normalised, rotated, rounded q heads
     float k_new[HEAD_DIM];             // the new key and value as stored (rounded)
@@ -119,7 +118,7 @@ __device__ __forceinline__ void norm_rotate_head(const volatile unsigned short* 
     }
 }
 
-template <int HEAD_DIM, int HPB, typename W>
+template <int HEAD_DIM, int HPB, int DEC_WARPS, typename W>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_table,
@@ -134,8 +133,8 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     constexpr int WARP_KEYS = DEC_TILE;
     static_assert(HPB <= 8 && 32 % CPR == 0 && DEC_TILE % KPI == 0 && HEAD_DIM % 32 == 0, "shape of the tile");
     extern __shared__ __align__(16) unsigned char shared_raw[];
-    DecodeShared<HEAD_DIM, HPB>& sh = *reinterpret_cast<DecodeShared<HEAD_DIM, HPB>*>(shared_raw);
-    int* slot_s = reinterpret_cast<int*>(shared_raw + sizeof(DecodeShared<HEAD_DIM, HPB>));
+    DecodeShared<HEAD_DIM, HPB, DEC_WARPS>& sh = *reinterpret_cast<DecodeShared<HEAD_DIM, HPB, DEC_WARPS>*>(shared_raw);
+    int* slot_s = reinterpret_cast<int*>(shared_raw + sizeof(DecodeShared<HEAD_DIM, HPB, DEC_WARPS>));
 
     cg::cluster_group cluster = cg::this_cluster();
     const int split = blockIdx.x;              // = rank in the cluster
@@ -354,7 +353,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         if (t4 == 0) { sh.warp_m[warp][g] = m_run; sh.warp_l[warp][g] = l_run; }
     }
     __syncthreads();
-    DecodeShared<HEAD_DIM, HPB>* first_cta = cluster.map_shared_rank(&sh, 0);
+    DecodeShared<HEAD_DIM, HPB, DEC_WARPS>* first_cta = cluster.map_shared_rank(&sh, 0);
     for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
         const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
         float m = -INFINITY;
@@ -399,23 +398,23 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     }
 }
 
-template <int HEAD_DIM>
+template <int HEAD_DIM, int DEC_WARPS>
 static int decode_warp_slot_capacity(int max_context, int splits) {
     constexpr int WARP_KEYS = DEC_TILE;
     const int split_keys = ((max_context + splits - 1) / splits + 63) / 64 * 64 + 64;
     return (split_keys / (WARP_KEYS * DEC_WARPS) + 2) * WARP_KEYS;
 }
 
-template <int HEAD_DIM, int HPB, typename W>
+template <int HEAD_DIM, int HPB, int DEC_WARPS, typename W>
 static int launch_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                          const float* cos_table, const float* sin_table, int table_positions,
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
                          void* value_cache, const int* block_tables, int table_stride, int page_size,
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
                          int splits, int write_cache, int max_context, int pdl, cudaStream_t stream) {
-    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, W>;
-    const int warp_slots = decode_warp_slot_capacity<HEAD_DIM>(max_context, splits);
-    const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB>) + (size_t)DEC_WARPS * warp_slots * sizeof(int);
+    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, W>;
+    const int warp_slots = decode_warp_slot_capacity<HEAD_DIM, DEC_WARPS>(max_context, splits);
+    const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB, DEC_WARPS>) + (size_t)DEC_WARPS * warp_slots * sizeof(int);
     if (shared > 200 * 1024) return TVB_BAD_ARGUMENT;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (e != cudaSuccess) return (int)e;
@@ -459,14 +458,30 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
     const int group = num_q / num_kv;
     const int hpb = group % 4 == 0 ? 4 : group;
     cudaStream_t s = (cudaStream_t)stream;
+    // Four warps a CTA keep four CTAs on an SM, which is what counts when the grid fills the GPU;
+    // a grid of fewer CTAs than SMs (one or two requests) is faster with eight warps a CTA, each
+    // with half as many keys to walk (batch 1, context 2,100: 10.3 us against 12.8 us).
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+            sm_count = 0;
+    }
+    const bool wide = head_dim <= 128 && (long long)requests * num_kv * (group / hpb) * splits <= sm_count;
 #define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
                     token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
                     requests, num_q, num_kv, window, scale, splits, write_cache, max_context, pdl, s
+#define DECODE_BY_WARPS(D, H, WT)                                       \
+    do {                                                                \
+        if (wide) return launch_decode<D, H, 8, WT>(DECODE_ARGS);       \
+        return launch_decode<D, H, 4, WT>(DECODE_ARGS);                 \
+    } while (0)
 #define DECODE_BY_HPB(D, WT)                                            \
     do {                                                                \
-        if (hpb == 1) return launch_decode<D, 1, WT>(DECODE_ARGS);      \
-        if (hpb == 2) return launch_decode<D, 2, WT>(DECODE_ARGS);      \
-        return launch_decode<D, 4, WT>(DECODE_ARGS);                    \
+        if (hpb == 1) DECODE_BY_WARPS(D, 1, WT);                        \
+        if (hpb == 2) DECODE_BY_WARPS(D, 2, WT);                        \
+        DECODE_BY_WARPS(D, 4, WT);                                      \
     } while (0)
 #define DECODE_BY_DIM(WT)                                               \
     do {                                                                \
