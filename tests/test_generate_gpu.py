@@ -53,3 +53,47 @@ def test_long_decoding(model_folders):
     sequence = prompt + list(output.output_token_ids)
     logits = plain.forward(cfg, weights, sequence[:-1])
     assert logits[len(prompt) - 1:].argmax(-1).tolist() == list(output.output_token_ids)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_runs_give_the_tokens_of_single_steps(dtype, model_folders):
+    """Several decode steps back to back, fed on the device, against one step at a time: the same
+    tokens for greedy and for seeded sampling, requests that stop on a token inside a run, requests
+    that end by length at different times, and a newcomer while others decode."""
+    from tinyvllm_b200 import GenerateRequest, SamplingParams
+    from tinyvllm_b200.engine.engine import Engine
+
+    name = "e" if dtype == "bfloat16" else "b"
+    config = TINY_CONFIGS[name]
+    folder = model_folders[name]
+    prompts = [random_tokens(config.vocab_size, n, 500 + n) for n in (3, 17, 40, 9)]
+    samplings = [SamplingParams(max_new_tokens=23, ignore_eos=True),
+                 SamplingParams(max_new_tokens=9, temperature=0.8, top_k=20, seed=5, ignore_eos=True),
+                 SamplingParams(max_new_tokens=30, temperature=1.1, top_p=0.9, seed=11, ignore_eos=True),
+                 SamplingParams(max_new_tokens=14, ignore_eos=True)]
+    results = {}
+    for run_steps in (1, 4):
+        engine = Engine.from_config(engine_config(folder, name, dtype=dtype, decode_run_steps=run_steps))
+        try:
+            # stop tokens: whatever the first request produces as its 6th token ends it there
+            if run_steps == 1:
+                probe = engine.generate([GenerateRequest(tuple(prompts[0]), samplings[0])])[0]
+                stop = probe.output_token_ids[5]
+            engine.scheduler.eos_token_ids = frozenset({stop})
+            stopping = SamplingParams(max_new_tokens=23)
+            ids = [engine.submit(p, s) for p, s in zip(prompts[:3], [stopping] + samplings[1:3])]
+            outputs = {}
+            steps = 0
+            while engine.has_unfinished():
+                if steps == 3:
+                    ids.append(engine.submit(prompts[3], samplings[3]))       # arrives while others decode
+                for done in engine.step().finished:
+                    outputs[done.request_id] = (tuple(done.output_token_ids), done.finish_reason)
+                steps += 1
+            results[run_steps] = [outputs[i] for i in ids]
+            if run_steps > 1:
+                assert engine.steps_run > steps          # some calls ran several decode steps
+        finally:
+            engine.close()
+    assert results[1] == results[4]
+    assert results[1][0][1] == "stop" and len(results[1][0][0]) <= 6

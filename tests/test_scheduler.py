@@ -222,3 +222,96 @@ def test_random_workloads_finish_with_every_token_accounted_for(seed):
     # requests finished earlier were already taken by nobody: collect them from the loop above
     assert all(pool.free_count == pool.num_pages for pool in cache.pools)
     assert cache.slots.free_count == cache.slots.num_slots
+
+
+# ------------------------------------------------------------------ decode runs
+def test_decode_run_only_when_nothing_waits_and_as_long_as_every_request_may_go():
+    scheduler, cache = make(pages=64, page_size=4, seqs=3, budget=32, chunk=16, max_len=40)
+    scheduler.add(request(0, 5, new=10))
+    scheduler.add(request(1, 7, new=3))
+    assert scheduler.schedule_decode_run(4) is None            # nothing decodes yet
+    run_step(scheduler)                                         # both prompts in one step, first tokens
+    assert scheduler.decoding == [0, 1] and not scheduler.prefilling
+    run = scheduler.schedule_decode_run(4)
+    # request 1 has 2 of its 3 tokens left: the run is 2 steps long, one plan of 2 tokens each
+    assert run is not None and run.steps == 2
+    assert [(i.request_id, i.start, i.count) for i in run.items] == [(0, 5, 2), (1, 7, 2)]
+    events = scheduler.commit_run(run, [{0: 50, 1: 60}, {0: 51, 1: 61}])
+    cache.check()
+    assert events == [(0, 50), (1, 60), (0, 51), (1, 61)]
+    done = scheduler.take_finished()
+    assert [r.request_id for r in done] == [1] and done[0].output_token_ids == [101, 60, 61]
+    assert scheduler.requests[0].computed_tokens == 7 and scheduler.requests[0].output_token_ids == [100, 50, 51]
+    # a newcomer waits: no run while it does, a plain step takes it in
+    scheduler.add(request(2, 4, new=2))
+    assert scheduler.schedule_decode_run(4) is None
+    step, _ = run_step(scheduler)
+    assert {i.request_id for i in step.items} == {0, 2}
+    # the context limit bounds a run like the token limit does
+    scheduler2, _ = make(max_len=12)
+    scheduler2.add(request(0, 8, new=50))
+    run_step(scheduler2)
+    run = scheduler2.schedule_decode_run(8)
+    assert run.steps == 3                                       # 9 tokens now, 12 at most
+    scheduler2.commit_run(run, [{0: 1}, {0: 2}, {0: 3}])
+    assert scheduler2.take_finished()[0].finish_reason == "length"
+    assert scheduler2.schedule_decode_run(8) is None
+
+
+def test_stop_token_inside_a_run_ends_the_request_there_and_frees_its_pages():
+    scheduler, cache = make(pages=16, page_size=4, seqs=2, eos=(9,))
+    scheduler.add(request(0, 6, new=20))
+    scheduler.add(request(1, 3, new=20, ignore_eos=True))
+    run_step(scheduler)
+    free_before = cache.free_pages(0)
+    run = scheduler.schedule_decode_run(4)
+    assert run.steps == 4
+    events = scheduler.commit_run(run, [{0: 5, 1: 9}, {0: 9, 1: 9}, {0: 7, 1: 9}, {0: 8, 1: 9}])
+    cache.check()
+    # request 0 stops at its second token; what the run made for it afterwards is dropped
+    assert [e for e in events if e[0] == 0] == [(0, 5), (0, 9)]
+    assert [e for e in events if e[1] == 9 and e[0] == 1] == [(1, 9)] * 4      # ignore_eos goes on
+    done = scheduler.take_finished()
+    assert [r.request_id for r in done] == [0] and done[0].finish_reason == "stop"
+    assert done[0].output_token_ids == [100, 5, 9]
+    assert not cache.is_open(0) and cache.is_open(1)
+    assert cache.free_pages(0) >= free_before - 1               # request 0's pages are back
+    with pytest.raises(ValueError, match="a run of"):
+        run2 = scheduler.schedule_decode_run(3)
+        scheduler.commit_run(run2, [{1: 1}])
+
+
+def test_runs_and_single_steps_produce_the_same_requests():
+    """Random workloads drained with and without runs: same outputs, no page lost."""
+    for seed in range(6):
+        outputs = []
+        for run_steps in (1, 4):
+            rng = random.Random(seed)
+            scheduler, cache = make(pages=40, page_size=4, seqs=3, budget=24, chunk=8, max_len=64, eos=(7,))
+            for rid in range(6):
+                scheduler.add(request(rid, rng.randrange(1, 20), new=rng.randrange(1, 12)))
+            counters = {}
+
+            def token_of(rid):
+                counters[rid] = counters.get(rid, 0) + 1
+                return (rid * 31 + counters[rid] * 5) % 11          # sometimes the stop token 7
+
+            guard = 0
+            while scheduler.has_unfinished():
+                run = scheduler.schedule_decode_run(run_steps) if run_steps > 1 else None
+                if run is not None:
+                    rows = [{i.request_id: token_of(i.request_id) for i in run.items} for _ in range(run.steps)]
+                    scheduler.commit_run(run, rows)
+                else:
+                    run_step(scheduler, token_of)
+                cache.check()
+                guard += 1
+                assert guard < 1000
+            outputs.append({r.request_id: (tuple(r.output_token_ids), r.finish_reason)
+                            for r in scheduler.take_finished()})
+            assert all(pool.free_count == pool.num_pages for pool in cache.pools)
+        # the made-up tokens depend on how often a request was asked, which a run does beyond a
+        # request's end too: compare what does not (lengths up to the first stop token)
+        for rid in outputs[0]:
+            a, b = outputs[0][rid], outputs[1][rid]
+            assert a[1] == b[1] and len(a[0]) == len(b[0]), (seed, rid, a, b)

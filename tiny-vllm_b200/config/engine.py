@@ -2,7 +2,8 @@
 
 Field names, defaults and checks follow tinyvllm/config.py:15-92 where the
 reference has them.  Added: ``dtype="float32"`` (a true 32-bit path),
-``weights``/``seed`` (random weights instead of a checkpoint), ``graph_batch_sizes``.
+``weights``/``seed`` (random weights instead of a checkpoint), ``graph_batch_sizes``,
+``decode_run_steps`` (decode steps the engine runs back to back before it looks at their tokens).
 Dropped: ``attention_backend`` (there is one backend), ``enable_prefix_caching``
 (not built), float16.
 """
@@ -45,6 +46,9 @@ class EngineConfig:
     weights: Literal["checkpoint", "random"] = "checkpoint"
     seed: int = 0
     graph_batch_sizes: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
+    # While nothing waits, up to this many decode steps run back to back, each fed the step before's
+    # tokens on the device; the host reads their tokens together afterwards.  1: one step a time.
+    decode_run_steps: int = 4
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:
@@ -59,7 +63,7 @@ class EngineConfig:
         if type(self.enforce_eager) is not bool:
             raise TypeError("enforce_eager must be bool")
         for name in ("max_model_len", "max_num_seqs", "max_num_batched_tokens",
-                     "prefill_chunk_size", "kv_block_size", "kv_cache_memory_bytes"):
+                     "prefill_chunk_size", "kv_block_size", "kv_cache_memory_bytes", "decode_run_steps"):
             _positive_int(name, getattr(self, name))
         for name in ("prefill_reserve_tokens", "prefill_reserve_requests", "seed"):
             _non_negative_int(name, getattr(self, name))

@@ -86,10 +86,11 @@ def plan_pages(kv_cache_memory_bytes: int, bytes_per_page: int, free_bytes: int,
 
 class Engine:
     def __init__(self, runner: StepRunner, scheduler: Scheduler, *, graphs: DecodeGraphs | None = None,
-                 clock=time.monotonic_ns) -> None:
+                 clock=time.monotonic_ns, decode_run_steps: int = 1) -> None:
         self.runner = runner
         self.scheduler = scheduler
         self.graphs = graphs
+        self.decode_run_steps = decode_run_steps if graphs is not None else 1
         self.sampler = Sampler()
         self._clock = clock
         self._next_id = 0
@@ -141,7 +142,7 @@ class Engine:
         log.info("engine ready: %s, %s, %d pages of %d tokens per group, %.1f MiB of weights",
                  spec.architecture, config.dtype, pages, config.kv_block_size,
                  model.weight_bytes() / 2**20)
-        return cls(runner, scheduler, graphs=graphs)
+        return cls(runner, scheduler, graphs=graphs, decode_run_steps=config.decode_run_steps)
 
     # ------------------------------------------------------------- requests
     def _check_usable(self) -> None:
@@ -177,6 +178,10 @@ class Engine:
         """Run one step of whatever the scheduler picks; tokens and finished requests."""
         self._check_usable()
         now = self._clock()
+        if self.decode_run_steps > 1 and self.graphs.bucket_for(len(self.scheduler.decoding)) is not None:
+            run = self.scheduler.schedule_decode_run(self.decode_run_steps, now)
+            if run is not None:
+                return self._step_run(run)
         scheduled = self.scheduler.schedule(now)
         if scheduled is None:
             return StepEvents((), tuple(RequestOutput.of(r) for r in self.scheduler.take_finished()))
@@ -189,6 +194,27 @@ class Engine:
                 self.scheduler.abort_step(scheduled)
             raise
         self.steps_run += 1
+        finished = tuple(RequestOutput.of(r) for r in self.scheduler.take_finished())
+        return StepEvents(tuple(events), finished)
+
+    def _step_run(self, run) -> StepEvents:
+        """Several decode steps back to back (see DecodeGraphs.run_many); their tokens in step order."""
+        requests = self.scheduler.requests
+        ids = [item.request_id for item in run.items]
+        try:
+            first = [requests[i].tokens(item.start, item.start + 1)[0] for i, item in zip(ids, run.items)]
+            params = [requests[i].sampling for i in ids]
+            draws = [len(requests[i].output_token_ids) for i in ids]
+            rows = self.graphs.run_many(run.cache_plan, first, params, draws, run.steps)
+            kernels.check_finished_launches()
+            events = self.scheduler.commit_run(run, [dict(zip(ids, row)) for row in rows], self._clock())
+        except BaseException as exc:
+            self._failed = repr(exc)
+            if run.cache_plan.state == "planned":
+                self.scheduler.cache.rollback(run.cache_plan)
+            raise
+        self.steps_run += run.steps
+        self.graph_steps += run.steps
         finished = tuple(RequestOutput.of(r) for r in self.scheduler.take_finished())
         return StepEvents(tuple(events), finished)
 

@@ -47,6 +47,7 @@ class _Bucket:
         # per group and row: (request, entries written, leading entries given back) of the last step
         self.row_tables = [[None] * size for _ in range(groups)]
         self.copied: torch.cuda.Event | None = None      # the last upload has left the pinned buffer
+        self.history: torch.Tensor | None = None         # pinned [steps, size]: the tokens of a run's steps
 
     def host_view(self, i: int) -> np.ndarray:
         return self.host_np[self.offsets[i]:self.offsets[i] + self.sizes[i]]
@@ -138,30 +139,25 @@ class DecodeGraphs:
                 return bucket
         return None
 
-    @torch.inference_mode()
-    def run(self, plan, entries, params, draws) -> tuple[torch.Tensor, torch.Tensor] | None:
-        """Replay the graph for a step of single tokens; (tokens, logits) views of the first
-        ``len(entries)`` rows, valid until the next replay.  None if no graph holds the step."""
-        rows = len(entries)
-        bucket = self.bucket_for(rows)
-        if bucket is None:
-            return None
+    def _fill(self, bucket: _Bucket, planned, rows: int, tokens, offset: int, params, draws) -> None:
+        """Write the fields of one decode step into the bucket's pinned buffer.  ``offset``: how
+        many tokens of the plan lie before this step (0 for a plain step); ``tokens`` None leaves
+        the token ids as they are (they come from the step before, on the device)."""
         if bucket.copied is not None:
             bucket.copied.synchronize()
-        planned = plan.entries
-        self.runner.storage.clear_state([p.state_slot for p in planned if p.fresh_state])
         groups = len(self.runner.manager.groups)
         # per-row fields, one array assignment each; rows past the step are padding
         size = bucket.size
-        bucket.host_view(0)[:rows] = [entry.tokens[0] for entry in entries]
-        bucket.host_view(0)[rows:] = 0
-        bucket.host_view(1)[:rows] = [p.start for p in planned]
+        if tokens is not None:
+            bucket.host_view(0)[:rows] = tokens
+            bucket.host_view(0)[rows:] = 0
+        bucket.host_view(1)[:rows] = [p.start + offset for p in planned]
         bucket.host_view(1)[rows:] = -1
         bucket.host_view(2)[:rows] = np.arange(rows)
         bucket.host_view(2)[rows:] = -1
         bucket.host_view(4)[:rows] = [p.state_slot for p in planned]
         for g in range(groups):
-            bucket.host_view(6 + 2 * g)[:rows] = [p.slots[g][0] for p in planned]
+            bucket.host_view(6 + 2 * g)[:rows] = [p.slots[g][offset] for p in planned]
             bucket.host_view(6 + 2 * g)[rows:] = -1
             # block tables stay in the buffer from step to step: a row whose request is the one of
             # the step before only gets the entries that were added or given back since
@@ -185,8 +181,54 @@ class DecodeGraphs:
                 known[r] = None
         packed = bucket.host_view(len(bucket.sizes) - 1).reshape(ROW_WORDS, size)
         packed[:] = pack_rows(params, draws, capacity=size)
+
+    @torch.inference_mode()
+    def run(self, plan, entries, params, draws) -> tuple[torch.Tensor, torch.Tensor] | None:
+        """Replay the graph for a step of single tokens; (tokens, logits) views of the first
+        ``len(entries)`` rows, valid until the next replay.  None if no graph holds the step."""
+        rows = len(entries)
+        bucket = self.bucket_for(rows)
+        if bucket is None:
+            return None
+        planned = plan.entries
+        self.runner.storage.clear_state([p.state_slot for p in planned if p.fresh_state])
+        self._fill(bucket, planned, rows, [entry.tokens[0] for entry in entries], 0, params, draws)
         bucket.device.copy_(bucket.host, non_blocking=True)
         bucket.copied = torch.cuda.Event()
         bucket.copied.record()
         bucket.graph.replay()
         return bucket.tokens[:rows], bucket.logits[:rows]
+
+    @torch.inference_mode()
+    def run_many(self, plan, first_tokens, params, draws, steps: int) -> list[list[int]] | None:
+        """``steps`` decode steps of the same requests back to back: the plan holds ``steps`` tokens
+        per request, step i runs its i-th.  The tokens a step samples are the next step's input on
+        the device (the host only uploads positions, slots and sampling arguments, which it knows
+        in advance) and are copied to pinned memory after every step; the host waits once, at the
+        end, so its work for step i + 1 runs while the GPU is at step i.  Returns the tokens
+        [steps][rows], or None if no graph holds the rows."""
+        rows = len(first_tokens)
+        bucket = self.bucket_for(rows)
+        if bucket is None:
+            return None
+        planned = plan.entries
+        self.runner.storage.clear_state([p.state_slot for p in planned if p.fresh_state])
+        if bucket.history is None or bucket.history.shape[0] < steps:
+            bucket.history = torch.zeros((steps, bucket.size), dtype=torch.int32, pin_memory=True)
+        ids_end = int(bucket.offsets[1])
+        for index in range(steps):
+            self._fill(bucket, planned, rows, first_tokens if index == 0 else None, index, params,
+                       [d + index for d in draws])
+            if index == 0:
+                bucket.device.copy_(bucket.host, non_blocking=True)
+            else:
+                bucket.device_view(0).copy_(bucket.tokens, non_blocking=True)
+                bucket.device[ids_end:].copy_(bucket.host[ids_end:], non_blocking=True)
+            bucket.copied = torch.cuda.Event()
+            bucket.copied.record()
+            bucket.graph.replay()
+            bucket.history[index].copy_(bucket.tokens, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        done.synchronize()
+        return bucket.history[:steps, :rows].tolist()

@@ -25,6 +25,7 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 from enum import Enum
+from typing import Sequence
 
 from ..cache.manager import CacheManager, StepCachePlan
 from ..sampling.params import SamplingParams
@@ -94,6 +95,15 @@ class ScheduledStep:
     @property
     def num_tokens(self) -> int:
         return sum(item.count for item in self.items)
+
+
+@dataclass
+class ScheduledRun:
+    """Several decode steps of the same requests, planned at once: item.count tokens each."""
+
+    items: tuple[WorkItem, ...]
+    cache_plan: StepCachePlan
+    steps: int
 
 
 class Scheduler:
@@ -265,6 +275,57 @@ class Scheduler:
         if had_both:
             self._prefer_waiting = not self._prefer_waiting
         return ScheduledStep(tuple(items), plan)
+
+    def schedule_decode_run(self, max_steps: int, now_ns: int = 0) -> ScheduledRun | None:
+        """Up to ``max_steps`` decode steps of all decoding requests as one plan, or None.
+
+        Only when nothing waits and nothing is being prefilled (a newcomer would wait for the whole
+        run), and only as many steps as every request may still take: none reaches its token limit
+        or the context limit before the run's last step.  A request that meets a stop token inside
+        the run ends there; what the run computed for it beyond is dropped with its pages."""
+        if max_steps < 2 or not self.decoding or self.waiting or self.prefilling:
+            return None
+        if len(self.decoding) > min(self.max_num_seqs, self.max_num_batched_tokens):
+            return None
+        steps = max_steps
+        for request_id in self.decoding:
+            request = self.requests[request_id]
+            steps = min(steps, request.remaining_new_tokens, self.max_model_len - request.total_tokens)
+        if steps < 2:
+            return None
+        items = tuple(WorkItem(request_id, self.requests[request_id].computed_tokens, steps, True)
+                      for request_id in self.decoding)
+        plan = self.cache.plan([(item.request_id, item.count) for item in items])
+        if plan is None:
+            return None
+        return ScheduledRun(items, plan, steps)
+
+    def commit_run(self, run: ScheduledRun, sampled: Sequence[dict[int, int]], now_ns: int = 0) -> list[tuple[int, int]]:
+        """The run ran.  ``sampled[i]`` maps request id to the token of the run's i-th step.
+        Returns (request id, token) in step order; a request that ended inside the run has no
+        tokens after its end."""
+        if len(sampled) != run.steps:
+            raise ValueError(f"a run of {run.steps} steps came back with {len(sampled)}")
+        for tokens in sampled:
+            for item in run.items:
+                if item.request_id not in tokens:
+                    raise ValueError(f"no token was sampled for request {item.request_id}")
+        self.cache.commit(run.cache_plan)
+        events = []
+        for index, tokens in enumerate(sampled):
+            for item in run.items:
+                request = self.requests[item.request_id]
+                if request.status.terminal:          # ended earlier in this run, or cancelled
+                    continue
+                request.computed_tokens = item.start + index + 1
+                token = int(tokens[item.request_id])
+                request.output_token_ids.append(token)
+                events.append((item.request_id, token))
+                if token in self.eos_token_ids and not request.sampling.ignore_eos:
+                    self._finish(request, "stop", now_ns)
+                elif request.remaining_new_tokens <= 0 or request.total_tokens >= self.max_model_len:
+                    self._finish(request, "length", now_ns)
+        return events
 
     # ------------------------------------------------------------- results
     def abort_step(self, step: ScheduledStep) -> None:
