@@ -60,8 +60,8 @@ def prefill_tiles(counts, starts=None, *, tensor_memory: bool = False, singles_a
     Returns two triples of lists (row, first flat token, count) and a list of runs: tiles of up to
     128 tokens for the tcgen05 kernel, the longest context first; tiles of up to 64 tokens for the
     mma.sync kernel; and, with ``singles_apart``, (first flat token, count) of every run of
-    consecutive single-token entries (decoded tokens beside prompt portions), which go to the row
-    kernel with their keys spread over the grid instead of a 64-row tile each.  Without
+    consecutive tokens that are attended one by one: single-token entries (decoded tokens beside
+    prompt portions) and, with ``tensor_memory``, the rests of entries too short for a tile.  Without
     ``tensor_memory`` nothing is in the first set; with it only the short rests of entries are in
     the second.  ``starts``: tokens each entry has in the cache before the step."""
     small = kernels.attention_prefill_tile_tokens()
@@ -86,6 +86,14 @@ def prefill_tiles(counts, starts=None, *, tensor_memory: bool = False, singles_a
                 big[0].append(row), big[1].append(cursor + done), big[2].append(size)
                 ends.append(starts[row] + done + size)
                 done += size
+            if singles_apart and done < count:
+                # the short rest of an entry: token by token like decoded tokens (a 64-row tile for a
+                # few tokens walks a long context alone: 75 us at 2,048 keys, whatever their number)
+                if runs and runs[-1][0] + runs[-1][1] == cursor + done:
+                    runs[-1][1] += count - done
+                else:
+                    runs.append([cursor + done, count - done])
+                done = count
         for start in range(done, count, small):
             rest[0].append(row), rest[1].append(cursor + start), rest[2].append(min(small, count - start))
         cursor += count
