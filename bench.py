@@ -150,7 +150,13 @@ def random_prompt(rng: random.Random, count: int) -> list[int]:
     return [rng.randrange(MODEL["vocab_size"]) for _ in range(count)]
 
 
-def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloat16", eager: bool = False):
+def new_tokens_of(steps: int, warmup: int) -> int:
+    """Tokens a request of the decode measurement may generate (a call of step() runs up to four)."""
+    return steps + 5 * warmup + 32
+
+
+def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloat16", eager: bool = False,
+                new_tokens: int = 512):
     from tinyvllm_b200 import EngineConfig
     from tinyvllm_b200.engine.engine import Engine
     from tinyvllm_b200.models import Qwen3Config
@@ -158,9 +164,10 @@ def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloa
     config = Qwen3Config(**{**MODEL, "num_hidden_layers": layers})
     Path(folder, "config.json").write_text(json.dumps(config.to_json()))
     kv_bytes_per_token = 2 * layers * MODEL["num_key_value_heads"] * MODEL["head_dim"] * 2
-    kv_budget = kv_bytes_per_token * (max_num_seqs * 2816 + 4096)
+    context = max(CONTEXT_LIMIT, PROMPT_TOKENS + new_tokens + 16)     # more steps than the workload's 256 fit too
+    kv_budget = kv_bytes_per_token * (max_num_seqs * (PROMPT_TOKENS + new_tokens + 64) + 4096)
     engine_config = EngineConfig(
-        model=folder, dtype=dtype, weights="random", seed=0, max_model_len=CONTEXT_LIMIT,
+        model=folder, dtype=dtype, weights="random", seed=0, max_model_len=context,
         max_num_seqs=max_num_seqs, max_num_batched_tokens=max(4096, max_num_seqs),
         prefill_chunk_size=2048, prefill_reserve_tokens=0, prefill_reserve_requests=0,
         kv_block_size=16, kv_cache_memory_bytes=kv_budget,
@@ -192,7 +199,7 @@ def run_decode(engine, batch: int, steps: int, warmup: int, sampler: ClockSample
     from tinyvllm_b200.ops import kernels
 
     rng = random.Random(batch)
-    sampling = SamplingParams(max_new_tokens=steps + 5 * warmup + 32, ignore_eos=True)
+    sampling = SamplingParams(max_new_tokens=new_tokens_of(steps, warmup), ignore_eos=True)
 
     def fresh_batch():
         """``batch`` requests with their prompts in the cache, about to decode their second token."""
@@ -308,7 +315,7 @@ def eager_profile(args, warmup: int) -> int:
 
     rng = random.Random(0)
     with tempfile.TemporaryDirectory() as folder:
-        engine = make_engine(folder, args.layers, args.batch, eager=True)
+        engine = make_engine(folder, args.layers, args.batch, eager=True, new_tokens=new_tokens_of(args.steps, warmup))
         sampling = SamplingParams(max_new_tokens=warmup + args.steps + 4, ignore_eos=True)
         for _ in range(args.batch):
             engine.submit(random_prompt(rng, PROMPT_TOKENS), sampling)
@@ -352,7 +359,7 @@ def main() -> int:
     sampler = ClockSampler()
     sampler.start()
     with tempfile.TemporaryDirectory() as folder:
-        engine = make_engine(folder, args.layers, max(args.batch, 1))
+        engine = make_engine(folder, args.layers, max(args.batch, 1), new_tokens=new_tokens_of(args.steps, warmup))
         main_run = run_decode(engine, args.batch, args.steps, warmup, sampler)
         prefill_ms = run_prefill(engine)
         weight_bytes = engine.runner.model.weight_bytes()
@@ -363,7 +370,7 @@ def main() -> int:
         if not args.no_points:
             for batch in (1, 64):
                 with tempfile.TemporaryDirectory() as other:
-                    point_engine = make_engine(other, args.layers, batch)
+                    point_engine = make_engine(other, args.layers, batch, new_tokens=new_tokens_of(args.steps, warmup))
                     result = run_decode(point_engine, batch, args.steps, warmup, None)
                     points[f"decode_b{batch}"] = round(result["tokens_per_s"], 1)
                     points[f"decode_b{batch}_e2e"] = round(result["e2e_tokens_per_s"], 1)
