@@ -6,8 +6,12 @@ max(0, p - window + 1) to p through the block table.
 
 * bfloat16, every entry one token, head size 64/128/256: one fused launch
   (``attention_decode``): norm, rotation, cache write and attention split over a cluster.
-* bfloat16, head size 64/128: ``qk_norm_rope_store`` then the tensor-core tile kernel
-  (``attention_prefill``).
+* bfloat16 prompt portions, head size 128: ``qk_norm_rope_store``, then tiles of up to 128
+  tokens on the tcgen05 kernel (``attention_prefill_tc``: S, P and O in tensor memory); the
+  decoded tokens of the same step and the rests of portions shorter than 32 tokens are
+  attended token by token by ``attention_decode`` (their keys are in the cache by then).
+* bfloat16 prompt portions, head size 64 (or pages the tcgen05 kernel does not take): tiles of
+  64 tokens on the mma.sync kernel (``attention_prefill``).
 * everything else (float32, other head sizes): ``qk_norm_rope_store`` then the row kernel,
   one warp per token and head.
 """

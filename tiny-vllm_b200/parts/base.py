@@ -12,8 +12,13 @@ norm            ``forward(x) -> y`` and ``add(x, residual) -> (y, new_residual)`
 position        ``prepare(ctx)``; handed to the mixer that asked for it
 mixer           ``cache_need() -> KVNeed | StateNeed | None`` and
                 ``forward(x, ctx, run) -> y`` where ``ctx`` is the step's
-                :class:`StepContext` and ``run`` the index in the run list
-feed_forward    ``forward(x, ctx) -> y``
+                :class:`StepContext` and ``run`` the index in the run list;
+                optionally ``forward_normed(hidden, residual, norm, ctx, run)
+                -> (y, new_residual)`` (takes its pre-norm into its first
+                projection), ``streamed_weights()`` (the large weights in the
+                order a step reads them) and ``takes_tensor_memory_tiles(page_size)``
+feed_forward    ``forward(x, ctx) -> y``, optionally ``forward_normed`` and
+                ``streamed_weights`` as above
 block           ``forward(hidden, residual, ctx, run) -> (hidden, residual)``
 embedding       ``forward(token_ids) -> hidden``
 head            ``forward(hidden_rows) -> logits`` (float32)
