@@ -617,3 +617,15 @@ def test_gemm_small_m_with_norm_prologue(shape, weight_dtype):
         act, _ = k().gemm_small_m(h.to(DEV), w.to(DEV), 2, norm_weight=nw.to(DEV),
                                   residual=res.to(DEV), eps=1e-5)
         close(act, plain.swiglu(x @ w.float().T, torch.bfloat16), torch.bfloat16, bf16=1.2e-2)
+
+
+def test_a_wait_that_is_never_satisfied_ends_by_itself_and_is_reported():
+    """The bounded mbarrier wait of the tcgen05 kernels, on a barrier nothing arrives on: it gives
+    up after about a second, records its code, raises the CTA's abort flag, the kernel returns and
+    the context goes on working."""
+    status, waited = k().wait_probe(77)
+    assert status == 77
+    assert 500 <= waited <= 20_000          # millions of SM cycles: the limit is 2e9
+    x = torch.arange(8, device=DEV)
+    assert int((x * 2).sum()) == 56          # the device still answers
+    assert k().gemm_tc_status() == 0 and k().attention_prefill_tc_status() == 0

@@ -646,6 +646,18 @@ def gemm_tc_status() -> int:
     return _fn("gemm_tc", "tvb_gemm_tc_status", [])()
 
 
+def wait_probe(code: int = 77) -> tuple[int, int]:
+    """Run the one-CTA kernel that waits on a barrier nothing arrives on: (status code the bounded
+    wait recorded, millions of SM cycles it waited).  Takes about a second; the context stays
+    usable.  Shows that a wait of the tcgen05 kernels that is never satisfied ends by itself."""
+    waited = ctypes.c_int(0)
+    fn = _fn("wait_probe", "tvb_wait_probe", [c_int, ctypes.POINTER(ctypes.c_int), c_void_p])
+    status = fn(code, ctypes.byref(waited), _stream())
+    if status < 0:
+        raise KernelError(f"wait_probe failed ({status})")
+    return status, waited.value
+
+
 def check_finished_launches() -> None:
     """Call after a step's results have reached the host: raises if a kernel with bounded waits
     gave up in a launch since the last call.  Costs nothing when no such kernel was launched."""
