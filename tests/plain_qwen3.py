@@ -23,7 +23,6 @@ and values that an earlier run produced.
 from __future__ import annotations
 
 import json
-import math
 from pathlib import Path
 
 import torch

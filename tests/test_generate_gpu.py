@@ -1,7 +1,6 @@
 """Generation through the Python entry point against the plain implementation."""
 
 import pytest
-import torch
 
 import plain_qwen3 as plain
 from tiny_configs import PAGE_SIZES, TINY_CONFIGS, random_tokens

@@ -274,7 +274,6 @@ def test_gemm_bfloat16_inputs_float32_result():
 
 
 def pack(rows):
-    import numpy as np
     from tinyvllm_b200.sampling.params import SamplingParams
     from tinyvllm_b200.sampling.sampler import pack_rows
     params = [SamplingParams(temperature=t, top_k=tk, top_p=tp, seed=s) for t, tk, tp, s, _ in rows]

@@ -6,7 +6,6 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from tiny_configs import random_tokens
 
 pytestmark = pytest.mark.gpu
 

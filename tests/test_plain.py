@@ -5,7 +5,7 @@ import math
 import torch
 
 import plain_qwen3 as plain
-from tiny_configs import TINY_CONFIGS, random_tokens
+from tiny_configs import random_tokens
 
 
 def test_logits_at_a_position_do_not_depend_on_later_tokens(model_folders):

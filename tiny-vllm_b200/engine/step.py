@@ -16,7 +16,7 @@ entry, not only its last token; there is no per-request loop on the host.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Sequence
 
 import numpy as np
@@ -25,7 +25,6 @@ import torch
 from ..cache.manager import CacheManager, StepCachePlan
 from ..cache.storage import CacheStorage, bytes_per_page, group_runs
 from ..ops import attention as attention_ops
-from ..ops import kernels
 
 
 class StepError(ValueError):

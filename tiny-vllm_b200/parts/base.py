@@ -26,7 +26,7 @@ head            ``forward(hidden_rows) -> logits`` (float32)
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable
 
 import torch

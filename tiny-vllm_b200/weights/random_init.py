@@ -18,7 +18,6 @@ from typing import Iterator
 
 import torch
 
-from ..parts.base import ParamSpec, Part
 
 NORMAL_STD = 0.02
 AROUND_ONE_SPREAD = 0.1
