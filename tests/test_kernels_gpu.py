@@ -618,6 +618,42 @@ def test_gemm_small_m_with_norm_prologue(shape, weight_dtype):
         close(act, plain.swiglu(x @ w.float().T, torch.bfloat16), torch.bfloat16, bf16=1.2e-2)
 
 
+@pytest.mark.parametrize("weight_dtype", [torch.float32, torch.bfloat16], ids=["w32", "w16"])
+@pytest.mark.parametrize("shape", [(8, 1024, 512, 3072), (1, 256, 48, 96), (13, 1000, 264, 40), (16, 2048, 1000, 64),
+                                   (27, 320, 72, 130)])
+def test_gemm_small_m_adds_to_the_stream_and_the_next_product_norms_it(shape, weight_dtype):
+    """Two products with a pre-norm between them and no norm kernel: the first adds its result to
+    the residual stream and stores the rows' sums of squares tile by tile, the second normalises
+    the stream with them while loading it."""
+    m, k_first, width, n_second = shape
+    torch.manual_seed(m + width)
+    x = torch.randn(m, k_first).bfloat16()
+    w_first = (torch.randn(width, k_first) * 0.05).bfloat16()
+    stream = (torch.randn(m, width) * 3).bfloat16()
+    if m > 2:
+        stream[2] *= 40                        # rows of very different size: a row's own sum must be used
+    nw = (1 + 0.1 * torch.randn(width)).to(weight_dtype)
+    w_second = (torch.randn(n_second, width) * 0.05).bfloat16()
+    product = (x.float() @ w_first.float().T).bfloat16().float()
+    want_stream = (product + stream.float()).bfloat16().float()
+    summed, squares = k().gemm_small_m(x.to(DEV), w_first.to(DEV), 0, add_stream=stream.to(DEV))
+    # the accumulation order of the product differs from torch's: a result may round to the neighbour
+    for row in range(m):                       # row by row: the large row must not hide the others
+        close(summed[row], want_stream[row], torch.bfloat16, bf16=8e-3)
+    tiles, padded = -(-width // 16), -(-m // 8) * 8
+    assert squares.shape == (tiles, padded)
+    got_squares = squares.sum(0).cpu()
+    assert torch.allclose(got_squares[:m], (summed.float().cpu() ** 2).sum(1), rtol=1e-5)
+    assert torch.all(got_squares[m:] == 0)
+    # the second product takes the stream the first one made, so that the comparison is of the norm alone
+    normed = plain.rms_norm(summed.float().cpu(), nw.float(), 1e-5, torch.bfloat16)
+    got = k().gemm_small_m(summed, w_second.to(DEV), 0, norm_weight=nw.to(DEV), eps=1e-5, row_squares=squares)
+    close(got, normed @ w_second.float().T, torch.bfloat16, bf16=8e-3)
+    if n_second % 2 == 0:
+        act = k().gemm_small_m(summed, w_second.to(DEV), 2, norm_weight=nw.to(DEV), eps=1e-5, row_squares=squares)
+        close(act, plain.swiglu(normed @ w_second.float().T, torch.bfloat16), torch.bfloat16, bf16=1.2e-2)
+
+
 def test_a_wait_that_is_never_satisfied_ends_by_itself_and_is_reported():
     """The bounded mbarrier wait of the tcgen05 kernels, on a barrier nothing arrives on: it gives
     up after about a second, records its code, raises the CTA's abort flag, the kernel returns and

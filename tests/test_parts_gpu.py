@@ -200,7 +200,7 @@ def test_block_part_alone(dtype):
         want = plain.mlp_block(w, "L", normed, dtype)
         rid = f"r{first_layer}"
         runner.open(rid)
-        outs, streams, start = [], [], 0
+        outs, streams, sums, start = [], [], [], 0
         with torch.inference_mode():
             for count in (100, 2, 37, 1):
                 entries = [StepEntry(rid, tuple([1] * count), ())]
@@ -210,9 +210,19 @@ def test_block_part_alone(dtype):
                 out, new_stream = block.forward(
                     x[part].to(DEV).contiguous(), None if first_layer else stream[part].to(DEV).contiguous(),
                     ctx, 0)
-                outs.append(out), streams.append(new_stream)
+                if out is None:
+                    # few bfloat16 rows: the down projection added its output to the stream itself
+                    assert dtype == torch.bfloat16 and count <= 16
+                    sums.append((part, new_stream))
+                else:
+                    outs.append((part, out)), streams.append((part, new_stream))
                 runner.manager.commit(plan)
                 start += count
         runner.close(rid)
-        check(torch.cat(outs), want, dtype)
-        check(torch.cat(streams), want_stream, dtype)
+        for part, out in outs:
+            check(out, want[part], dtype)
+        for part, new_stream in streams:
+            check(new_stream, want_stream[part], dtype)
+        for part, summed in sums:
+            check(summed, (want.float() + want_stream.float()).to(dtype).float()[part], dtype)
+        assert sums or dtype != torch.bfloat16

@@ -98,6 +98,16 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ float bf16_bits_to_float(unsigned short bits) {
     return __uint_as_float((uint32_t)bits << 16);
 }
+__device__ __forceinline__ float ld_global_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];\n" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned short ld_global_u16(const void* p) {
+    unsigned short v;
+    asm volatile("ld.global.cg.u16 %0, [%1];\n" : "=h"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint4 ld_global_16(const void* p) {
     uint4 v;
     asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"

@@ -21,6 +21,17 @@
 // the first CTA also stores the new residual stream.  Epilogues: bfloat16 or float32
 // result, or SiLU(gate) * up for a packed [gate | up] weight (:274-285), so that neither
 // the normalised input nor the activation goes through memory.
+//
+// A pre-norm between two products without a kernel of its own: the first product (a part's
+// output projection) adds its result to the residual stream on the way out and stores, for
+// every row, the sum of squares of the 16 columns of each of its tiles.  The second (the next
+// part's input projection) multiplies its x fragments by the norm weight as it loads them and
+// applies the row's inverse RMS, a factor of the whole row, to the finished sums: only the CTA
+// that writes a tile reads the partial sums (in a fixed order), it asks for them at its start
+// and needs them at its end.  (Every CTA reading them before its first product cost as much as
+// the norm kernel: hundreds of CTAs ask for the same 2 KB.)  The rounding differs from the norm
+// kernel's in one place: round(stream * weight) enters the product, where the kernel rounds
+// stream * inverse RMS first and the product with the weight second.
 // Stands where the reference calls F.linear (tinyvllm/layers.py:84-85).
 #include <cooperative_groups.h>
 
@@ -52,18 +63,31 @@ struct NormArgs {
     const void* weight;         // [k], bfloat16 or float32
     bf16* residual_out;         // null: not stored
     float eps;
+    const float* squares;       // NORM 3, 4: [square_tiles][8 NT] partial sums of squares of the rows of x
+    int square_tiles;
 };
 
-// NT: number of 8-row groups of x (M <= 8 NT).  NORM: 0 none, 1 bfloat16 weight, 2 float32 weight.
+// The epilogue that adds the product to the residual stream (MODE_BF16 only).
+struct StreamArgs {
+    const bf16* stream;         // [m, n] contiguous; null: the plain epilogue
+    float* squares_out;         // [tiles of 16 columns][8 NT]: sums of squares of the new stream
+};
+
+// NT: number of 8-row groups of x (M <= 8 NT).  NORM: 0 none; 1 bfloat16 weight, 2 float32 weight:
+// the prologue normalises x + residual; 3, 4 (bfloat16, float32 weight): x is the stream, its
+// fragments are multiplied by the norm weight and the results by the rows' inverse RMS, from the
+// sums of squares the product before stored.
 template <int NT, int MODE, int NORM>
 __global__ void __launch_bounds__(SM_WARPS * 32)
 gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int64_t ldw,
                     void* __restrict__ out, int64_t ldo, int m, int n, int k, int up_offset, NormArgs norm,
-                    const void* __restrict__ next_weight, long long next_bytes) {
+                    StreamArgs into, const void* __restrict__ next_weight, long long next_bytes) {
     constexpr int SETS = MODE == MODE_SILU ? 2 : 1;
     constexpr int MP = 8 * NT;
     __shared__ float warp_part[SM_WARPS][SETS][16][MP];
     __shared__ float cta_part[SETS][16][MP];
+    constexpr bool PROLOGUE_NORM = NORM == 1 || NORM == 2;
+    constexpr bool SCALED = NORM >= 3;
     extern __shared__ __align__(16) unsigned char dynamic_shared[];
     bf16* x_s = reinterpret_cast<bf16*>(dynamic_shared);       // [MP][k + SM_PAD] when NORM
 
@@ -95,6 +119,8 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.0f;
 
+    constexpr int SQUARE_LOADS = 4;      // tiles of the stream's sums of squares a lane asks for up front
+    float row_squares[SCALED ? NT : 1][SQUARE_LOADS];
     bool ready = false;          // the previous kernel's output may be read (and the norm is done)
     for (int kb0 = rank * SM_WARPS + warp; kb0 < k_blocks || !ready; kb0 += stride * SM_BATCH) {
         uint4 a_lo[SM_BATCH][SETS], a_hi[SM_BATCH][SETS];
@@ -109,9 +135,28 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
             }
         }
         if (!ready) {                // the weights are on their way; now the previous kernel's output
+            // The kernel behind this one may start now: what it does before its own wait (the
+            // decode attention looks up cache slots and starts streaming keys, a product its
+            // weights) runs beside this product, which leaves most of the memory system idle.
+            pdl_launch_dependents();
             prefetch_l2_range(next_weight, next_bytes);   // and those of the product after this one
             pdl_wait();
-            if (NORM) {
+            if (SCALED && rank == 0) {
+                // The rows' sums of squares are needed at the very end only (the inverse RMS is a factor
+                // of the whole row of x, so it is applied to the finished sums): asked for now, by the
+                // CTA that writes the tile; lane `col` of a row's 16 takes tiles col, col + 16, ...
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    const int index = threadIdx.x + i * SM_WARPS * 32;
+                    const int col = index % 16, row = index / 16;
+#pragma unroll
+                    for (int q = 0; q < SQUARE_LOADS; ++q) {
+                        const int t = col + 16 * q;
+                        row_squares[i][q] = t < norm.square_tiles ? ld_global_f32(norm.squares + (int64_t)t * MP + row) : 0.0f;
+                    }
+                }
+            }
+            if (PROLOGUE_NORM) {
                 // every CTA normalises all rows for itself: warp w takes rows w, w + 4, ...
                 for (int row = warp; row < MP; row += SM_WARPS) {
                     bf16* dst = x_s + row * x_row;
@@ -154,8 +199,10 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
                 }
                 __syncthreads();
             }
-            ready = true;
         }
+        // ---- the x fragments of this batch: all loads first, so that their latencies overlap
+        uint4 b_all[SM_BATCH][NT];
+        float norm_weight[SCALED ? SM_BATCH : 1][8];
 #pragma unroll
         for (int u = 0; u < SM_BATCH; ++u) {
             const int kb = kb0 + u * stride;
@@ -163,11 +210,38 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int row = 8 * j + g;
-                uint4 b;
-                if (NORM) b = k_ok ? *reinterpret_cast<const uint4*>(x_s + row * x_row + kb * 32 + 8 * t4)
-                                   : make_uint4(0u, 0u, 0u, 0u);
-                else b = k_ok && row < m ? ld_global_16(x + (int64_t)row * ldx + kb * 32 + 8 * t4)
-                                         : make_uint4(0u, 0u, 0u, 0u);
+                if (PROLOGUE_NORM) b_all[u][j] = k_ok ? *reinterpret_cast<const uint4*>(x_s + row * x_row + kb * 32 + 8 * t4)
+                                                      : make_uint4(0u, 0u, 0u, 0u);
+                else b_all[u][j] = k_ok && row < m ? ld_global_16(x + (int64_t)row * ldx + kb * 32 + 8 * t4)
+                                                   : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (SCALED) {
+                const int at = k_ok ? kb * 32 + 8 * t4 : 0;
+                if (NORM == 4) {
+                    const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(norm.weight) + at);
+                    const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(norm.weight) + at + 4);
+                    norm_weight[u][0] = lo.x, norm_weight[u][1] = lo.y, norm_weight[u][2] = lo.z, norm_weight[u][3] = lo.w;
+                    norm_weight[u][4] = hi.x, norm_weight[u][5] = hi.y, norm_weight[u][6] = hi.z, norm_weight[u][7] = hi.w;
+                } else {
+                    unpack_bf16x8(*reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(norm.weight) + at), norm_weight[u]);
+                }
+            }
+        }
+        if (!ready) {
+            ready = true;
+        }
+#pragma unroll
+        for (int u = 0; u < SM_BATCH; ++u) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                uint4 b = b_all[u][j];
+                if (SCALED) {
+                    float v[8];
+                    unpack_bf16x8(b, v);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], norm_weight[u][e]);
+                    b = pack_bf16x8(v);
+                }
 #pragma unroll
                 for (int s = 0; s < SETS; ++s) {
                     mma_16816(acc[s][j], a_lo[u][s].x, a_hi[u][s].x, a_lo[u][s].y, a_hi[u][s].y, b.x, b.y);
@@ -176,7 +250,6 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
             }
         }
     }
-    pdl_launch_dependents();
 
     // ---- warps of the CTA, then CTAs of the cluster, in a fixed order
 #pragma unroll
@@ -195,10 +268,22 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
         for (int wi = 0; wi < SM_WARPS; ++wi) total += (&warp_part[wi][0][0][0])[index];
         (&cta_part[0][0][0])[index] = total;
     }
+    // thread -> (row of x, column of the tile), columns fastest: 16 consecutive outputs per row; what the
+    // epilogue adds from the stream is asked for before the barrier, so that it arrives meanwhile
+    float from_stream[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        const int index = threadIdx.x + i * SM_WARPS * 32;
+        const int col = index % 16, row = index / 16;
+        from_stream[i] = 0.0f;
+        if (MODE == MODE_BF16 && rank == 0 && into.stream && row < m && n0 + col < n)
+            from_stream[i] = bf16_bits_to_float(ld_global_u16(into.stream + (int64_t)row * n + n0 + col));
+    }
     cluster.sync();
     if (rank == 0) {
-        // thread -> (row of x, column of the tile), columns fastest: 16 consecutive outputs per row
-        for (int index = threadIdx.x; index < 16 * MP; index += SM_WARPS * 32) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            const int index = threadIdx.x + i * SM_WARPS * 32;
             const int col = index % 16, row = index / 16;
             float value[SETS];
 #pragma unroll
@@ -210,17 +295,43 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
                 }
                 value[s] = total;
             }
+            if (SCALED) {
+                // sum of squares of the row: this lane's tiles in ascending order, then the 16 lanes of the row
+                float squares = 0.0f;
+#pragma unroll
+                for (int q = 0; q < SQUARE_LOADS; ++q) squares = __fadd_rn(squares, row_squares[i][q]);
+                for (int t = col + 16 * SQUARE_LOADS; t < norm.square_tiles; t += 16)
+                    squares = __fadd_rn(squares, ld_global_f32(norm.squares + (int64_t)t * MP + row));
+#pragma unroll
+                for (int delta = 8; delta > 0; delta >>= 1) squares = __fadd_rn(squares, __shfl_xor_sync(0xffffffffu, squares, delta));
+                const float inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(squares, 1.0f / (float)k), norm.eps)));
+#pragma unroll
+                for (int s = 0; s < SETS; ++s) value[s] = __fmul_rn(value[s], inverse_rms);
+            }
             if (row < m && n0 + col < n) {
                 const int64_t at = (int64_t)row * ldo + n0 + col;
                 if (MODE == MODE_F32) {
                     reinterpret_cast<float*>(out)[at] = value[0];
                 } else if (MODE == MODE_BF16) {
-                    reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(value[0]);
+                    if (!into.stream) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(value[0]);
                 } else {
                     const float gate = value[0], up = value[SETS - 1];
                     const float activated = round_to<bf16>(__fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate))));
                     reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(__fmul_rn(activated, up));
                 }
+            }
+            if (MODE == MODE_BF16 && into.stream) {
+                // the new residual stream and, over the 16 columns of this tile (16 consecutive lanes),
+                // its sum of squares for the norm that the next product applies
+                float added = 0.0f;
+                if (row < m && n0 + col < n) {
+                    added = round_to<bf16>(__fadd_rn(round_to<bf16>(value[0]), from_stream[i]));
+                    reinterpret_cast<bf16*>(out)[(int64_t)row * ldo + n0 + col] = __float2bfloat16_rn(added);
+                }
+                float squares = __fmul_rn(added, added);
+#pragma unroll
+                for (int delta = 8; delta > 0; delta >>= 1) squares = __fadd_rn(squares, __shfl_xor_sync(0xffffffffu, squares, delta));
+                if (col == 0) into.squares_out[(int64_t)blockIdx.y * MP + row] = squares;
             }
         }
     }
@@ -230,10 +341,11 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
 template <int NT, int MODE, int NORM>
 static int launch_small_m(const void* x, long long ldx, const void* w, long long ldw, void* out,
                           long long ldo, int m, int n, int k, int up_offset, int ranks, int pdl,
-                          NormArgs norm, const void* next_weight, long long next_bytes, cudaStream_t stream) {
+                          NormArgs norm, StreamArgs into, const void* next_weight, long long next_bytes,
+                          cudaStream_t stream) {
     auto kernel = gemm_small_m_kernel<NT, MODE, NORM>;
     size_t dynamic = 0;
-    if (NORM) {
+    if (NORM == 1 || NORM == 2) {
         dynamic = (size_t)8 * NT * (k + SM_PAD) * sizeof(bf16);
         if (dynamic > 160 * 1024) return TVB_BAD_ARGUMENT;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dynamic);
@@ -241,8 +353,8 @@ static int launch_small_m(const void* x, long long ldx, const void* w, long long
     }
     TvbLaunch launch(dim3(ranks, (n + 15) / 16), dim3(SM_WARPS * 32), dynamic, stream, pdl, ranks);
     cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)x, (int64_t)ldx, (const bf16*)w,
-                                       (int64_t)ldw, out, (int64_t)ldo, m, n, k, up_offset, norm, next_weight,
-                                       next_bytes);
+                                       (int64_t)ldw, out, (int64_t)ldo, m, n, k, up_offset, norm, into,
+                                       next_weight, next_bytes);
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
@@ -255,6 +367,14 @@ extern "C" int tvb_gemm_small_m_max_rows() { return 32; }
 // both are contiguous [m, k]); residual_out (may be null) receives the rounded sum.
 // norm_weight_dtype: TVB_BF16 or TVB_F32.
 //
+// row_squares != null (with norm_weight, without residual): x is the residual stream itself and
+// row_squares [square_tiles][m rounded up to 8] holds partial sums of squares of its rows, as a
+// launch with add_stream stored them; the result is that of RMSNorm(x) * norm_weight, computed as
+// (round(x * norm_weight) . w^T) * inverse RMS of the row.  norm_weight is 16-byte aligned.
+// add_stream != null (mode 0): out = round(round(product) + add_stream) (both contiguous [m, n] is
+// assumed for add_stream), and squares_out [ceil(n / 16)][m rounded up to 8] receives the sums of
+// squares of out over each tile of 16 columns.
+//
 // next_weight / next_bytes (may be null / 0): memory the grid asks to be brought into L2 while it
 // works, typically the weight of the product that follows.
 //
@@ -263,12 +383,15 @@ extern "C" int tvb_gemm_small_m_max_rows() { return 32; }
 extern "C" int tvb_gemm_small_m(const void* x, long long ldx, const void* w, long long ldw, void* out,
                                 long long ldo, int m, int n, int k, int mode, const void* residual,
                                 const void* norm_weight, void* residual_out, float eps,
-                                int norm_weight_dtype, const void* next_weight, long long next_bytes,
-                                int pdl, void* stream) {
+                                int norm_weight_dtype, const float* row_squares, int square_tiles,
+                                const void* add_stream, float* squares_out, const void* next_weight,
+                                long long next_bytes, int pdl, void* stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 32 || k <= 0 || k % 8 || ldx % 8 || ldw % 8 || mode < 0 || mode > 2 || n > 65535 * 16)
         return TVB_BAD_ARGUMENT;
     if (norm_weight && ldx != k) return TVB_BAD_ARGUMENT;
+    if (row_squares && (!norm_weight || residual || residual_out || square_tiles <= 0)) return TVB_BAD_ARGUMENT;
+    if (add_stream && (mode != MODE_BF16 || !squares_out)) return TVB_BAD_ARGUMENT;
     const int k_blocks = (k + 31) / 32;
     // enough CTAs per row tile that every warp has about one batch of k blocks, at most 8 per
     // cluster (a power of two)
@@ -278,17 +401,20 @@ extern "C" int tvb_gemm_small_m(const void* x, long long ldx, const void* w, lon
     const int up_offset = mode == MODE_SILU ? n : 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = (m + 7) / 8;
-    NormArgs norm = {(const bf16*)residual, norm_weight, (bf16*)residual_out, eps};
-    const int norm_kind = !norm_weight ? 0 : (norm_weight_dtype == TVB_F32 ? 2 : 1);
+    NormArgs norm = {(const bf16*)residual, norm_weight, (bf16*)residual_out, eps, row_squares, square_tiles};
+    StreamArgs into = {(const bf16*)add_stream, squares_out};
     if (norm_weight && norm_weight_dtype != TVB_F32 && norm_weight_dtype != TVB_BF16) return TVB_BAD_ARGUMENT;
+    const int norm_kind = !norm_weight ? 0 : (norm_weight_dtype == TVB_F32 ? 2 : 1) + (row_squares ? 2 : 0);
 #define SMALL_M(NT, MODE, NORM) \
-    launch_small_m<NT, MODE, NORM>(x, ldx, w, ldw, out, ldo, m, n, k, up_offset, ranks, pdl, norm, \
+    launch_small_m<NT, MODE, NORM>(x, ldx, w, ldw, out, ldo, m, n, k, up_offset, ranks, pdl, norm, into, \
                                    next_weight, next_bytes, s)
 #define BY_NORM(NT, MODE)                                   \
     do {                                                    \
         if (norm_kind == 0) return SMALL_M(NT, MODE, 0);    \
         if (norm_kind == 1) return SMALL_M(NT, MODE, 1);    \
-        return SMALL_M(NT, MODE, 2);                        \
+        if (norm_kind == 2) return SMALL_M(NT, MODE, 2);    \
+        if (norm_kind == 3) return SMALL_M(NT, MODE, 3);    \
+        return SMALL_M(NT, MODE, 4);                        \
     } while (0)
 #define BY_NT(MODE)                                  \
     do {                                             \

@@ -118,5 +118,7 @@ class Model:
             hidden, residual = self.blocks[step.layer].forward(hidden, residual, ctx, run)
         if ctx.num_wanted == 0:
             return None
+        if hidden is None:          # the last block added its output to the stream itself
+            hidden, residual = residual, None
         rows = self.final_norm.add_rows(hidden, residual, ctx.want_rows)
         return self.head.forward(rows)

@@ -534,6 +534,7 @@ GEMM_BF16, GEMM_F32, GEMM_SILU = 0, 1, 2
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
                  out: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
                  residual: torch.Tensor | None = None, eps: float = 0.0, want_residual: bool = True,
+                 row_squares: torch.Tensor | None = None, add_stream: torch.Tensor | None = None,
                  prefetch: torch.Tensor | None = None):
     """x [m <= 32, k] . w [n, k]^T, bfloat16 operands.  mode GEMM_BF16 / GEMM_F32: result
     [m, n] in that dtype; GEMM_SILU: w is [gate | up] with 2 n rows and the result is
@@ -542,6 +543,13 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
     With ``norm_weight`` the product is taken of RMSNorm(x + residual) * norm_weight instead
     of x (``residual`` may be None), and (result, rounded sum x + residual) is returned; the
     sum is None without a residual or with ``want_residual=False``.
+
+    ``add_stream`` (GEMM_BF16; contiguous [m, n]): the result is round(round(product) + add_stream),
+    the new residual stream, and (result, squares) is returned: squares [ceil(n / 16), m rounded up
+    to 8] float32 holds the sum of squares of the result's rows over each tile of 16 columns.
+    ``row_squares`` (with ``norm_weight``, without ``residual``): such sums for the rows of x, which
+    is the stream itself; the result is (round(x * norm_weight) . w^T) * inverse RMS of the row, and
+    only the result is returned.
 
     ``prefetch``: a tensor (the weight of the product after this one) whose first
     ``PREFETCH_MAX_BYTES`` the grid asks into L2 while it works."""
@@ -560,7 +568,22 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
     n = rows // 2 if mode == GEMM_SILU else rows
     residual_out = None
     weight_tag = BF16
-    if norm_weight is not None:
+    padded_rows = -(-m // 8) * 8
+    squares_out = None
+    if add_stream is not None:
+        if (mode != GEMM_BF16 or add_stream.shape != (m, n) or add_stream.dtype != torch.bfloat16
+                or not add_stream.is_contiguous() or out is not None):
+            raise KernelError("gemm_small_m: add_stream is a contiguous bfloat16 [m, n] and the result is new")
+        squares_out = torch.empty((-(-n // 16), padded_rows), dtype=torch.float32, device=x.device)
+    if row_squares is not None:
+        if (norm_weight is None or residual is not None or norm_weight.shape != (k,) or not x.is_contiguous()
+                or row_squares.dtype != torch.float32 or row_squares.dim() != 2
+                or row_squares.shape[1] != padded_rows or not row_squares.is_contiguous()
+                or norm_weight.data_ptr() % 16):
+            raise KernelError("gemm_small_m: row_squares [tiles, m rounded up to 8] float32 goes with a norm "
+                              "weight [k], contiguous x and no residual")
+        weight_tag = dtype_tag(norm_weight.dtype)
+    elif norm_weight is not None:
         if norm_weight.shape != (k,) or not x.is_contiguous() or not gemm_small_m_takes_norm(m, k):
             raise KernelError("gemm_small_m: the fused norm wants contiguous x, a weight [k] and "
                               "rows that fit into shared memory")
@@ -577,13 +600,17 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
                           device=x.device)
     fn = _fn("gemm_small_m", "tvb_gemm_small_m",
              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
-              c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_longlong, c_int, c_void_p])
+              c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_longlong, c_int, c_void_p])
     next_bytes = 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(),
                                                 PREFETCH_MAX_BYTES)
     _check(fn(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
               m, n, k, mode, _ptr(residual), _ptr(norm_weight), _ptr(residual_out), eps, weight_tag,
-              _ptr(prefetch), next_bytes, _pdl("gemm"), _stream()), "gemm_small_m")
-    if norm_weight is not None:
+              _ptr(row_squares), 0 if row_squares is None else row_squares.shape[0], _ptr(add_stream),
+              _ptr(squares_out), _ptr(prefetch), next_bytes, _pdl("gemm"), _stream()), "gemm_small_m")
+    if add_stream is not None:
+        return out, squares_out
+    if norm_weight is not None and row_squares is None:
         return out, residual_out
     return out
 

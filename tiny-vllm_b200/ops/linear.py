@@ -47,15 +47,54 @@ def linear_silu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
 FUSED_NORM_MAX_ROWS = int(os.environ.get("TINYVLLM_B200_FUSED_NORM_ROWS", "2"))
 
 
-def linear_norm(hidden: torch.Tensor, residual: torch.Tensor | None, norm, weight: torch.Tensor, *,
+# TINYVLLM_B200_STREAM_ADD=0: output projections never add to the stream themselves (the norm kernel
+# runs between every two products), for comparison
+STREAM_ADD = os.environ.get("TINYVLLM_B200_STREAM_ADD", "1") != "0"
+
+
+def linear_into_stream(x: torch.Tensor, weight: torch.Tensor, stream: torch.Tensor):
+    """A part's output projection, added to the residual stream where that saves a kernel.
+
+    Returns (None, stream + linear(x, weight)) when the product's kernel does the addition on its
+    way out (small bfloat16 batches): the new stream then carries ``row_squares``, the sums of
+    squares of its rows tile by tile, with which :func:`linear_norm` applies the next pre-norm
+    inside the next product, so that no norm kernel runs between the two (there the norm weight
+    multiplies the stream before the product and the inverse RMS the sums after it: one rounding
+    where the norm kernel has two).  Otherwise
+    (linear(x, weight), stream), and the next norm adds the two as usual."""
+    from . import gemm
+
+    if (STREAM_ADD and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and stream is not None
+            and stream.dtype == torch.bfloat16 and stream.is_contiguous() and gemm.small(x, weight)
+            and stream.shape == (x.shape[0], weight.shape[0])):
+        summed, squares = kernels.gemm_small_m(x, weight, kernels.GEMM_BF16, add_stream=stream,
+                                               prefetch=gemm.next_weight(weight))
+        summed.row_squares = squares
+        return None, summed
+    return linear(x, weight), stream
+
+
+def linear_norm(hidden: torch.Tensor | None, residual: torch.Tensor | None, norm, weight: torch.Tensor, *,
                 silu: bool = False):
     """(linear(norm(hidden + residual), weight), hidden + residual): a pre-norm and the
     projection behind it as one operation.  ``norm`` is a norm part (``weight``, ``eps``,
-    ``forward``, ``add``).  Without a residual the stream is ``hidden`` itself.  ``silu``
+    ``forward``, ``add``).  Without a residual the stream is ``hidden`` itself; without
+    ``hidden`` (None) the residual holds the sum already (:func:`linear_into_stream`).  ``silu``
     applies SiLU(gate) * up to a packed [gate | up] weight.  Small bfloat16 batches run as
     one kernel; everything else as the norm kernel and the product."""
     from . import gemm
 
+    if hidden is None:
+        squares = getattr(residual, "row_squares", None)
+        if (squares is not None and weight.dtype == torch.bfloat16 and type(norm).__name__ == "RMSNorm"
+                and gemm.small(residual, weight) and residual.is_contiguous()
+                and norm.weight.data_ptr() % 16 == 0):
+            mode = kernels.GEMM_SILU if silu else kernels.GEMM_BF16
+            out = kernels.gemm_small_m(residual, weight, mode, norm_weight=norm.weight, eps=norm.eps,
+                                       row_squares=squares, prefetch=gemm.next_weight(weight))
+            return out, residual
+        x = norm.forward(residual)
+        return (linear_silu(x, weight) if silu else linear(x, weight)), residual
     if (hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and hidden.is_contiguous()
             and type(norm).__name__ == "RMSNorm" and gemm.small(hidden, weight)
             and hidden.shape[0] <= FUSED_NORM_MAX_ROWS

@@ -12,7 +12,7 @@ are parameters; the position encoding is a part of its own.
 from __future__ import annotations
 
 from ..ops import attention as attention_ops
-from ..ops import kernels, linear, linear_norm
+from ..ops import kernels, linear, linear_into_stream, linear_norm
 from .base import BuildContext, KVNeed, ParamSpec, Part
 from .registry import register_part
 
@@ -78,10 +78,11 @@ class GQAAttention(Part):
         return linear(attended, self.o_weight)
 
     def forward_normed(self, hidden, residual, norm, ctx, run: int):
-        """forward(norm(hidden + residual)) and the new residual stream."""
+        """forward(norm(hidden + residual)) and the new residual stream; the output is None when
+        the output projection has added it to the stream itself."""
         qkv, residual = linear_norm(hidden, residual, norm, self.qkv_weight)
         attended = attention_ops.mixer_attention(ctx, self, qkv, run)
-        return linear(attended, self.o_weight), residual
+        return linear_into_stream(attended, self.o_weight, residual)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

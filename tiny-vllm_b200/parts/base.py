@@ -15,11 +15,15 @@ mixer           ``cache_need() -> KVNeed | StateNeed | None`` and
                 :class:`StepContext` and ``run`` the index in the run list;
                 optionally ``forward_normed(hidden, residual, norm, ctx, run)
                 -> (y, new_residual)`` (takes its pre-norm into its first
-                projection), ``streamed_weights()`` (the large weights in the
+                projection; ``hidden`` is None when the part before added its
+                output to the residual itself, and ``y`` may be None for the
+                same reason), ``streamed_weights()`` (the large weights in the
                 order a step reads them) and ``takes_tensor_memory_tiles(page_size)``
 feed_forward    ``forward(x, ctx) -> y``, optionally ``forward_normed`` and
                 ``streamed_weights`` as above
-block           ``forward(hidden, residual, ctx, run) -> (hidden, residual)``
+block           ``forward(hidden, residual, ctx, run) -> (hidden, residual)``;
+                ``residual`` is None for the first block, ``hidden`` is None
+                (on the way in or out) when it is in the residual already
 embedding       ``forward(token_ids) -> hidden``
 head            ``forward(hidden_rows) -> logits`` (float32)
 """

@@ -26,18 +26,26 @@ class PreNormResidualBlock(Part):
     def forward(self, hidden, residual, ctx, run: int):
         # a part that can take its norm into its first projection does so (forward_normed
         # returns its output and the new residual stream); the others get a normalised input
+        # A forward_normed may return None as its output: it has added it to the stream already.
         if hasattr(self.mixer, "forward_normed"):
             mixed, residual = self.mixer.forward_normed(hidden, residual, self.mixer_norm, ctx, run)
         else:
-            if residual is None:
-                residual, x = hidden, self.mixer_norm.forward(hidden)
-            else:
-                x, residual = self.mixer_norm.add(hidden, residual)
+            x, residual = _normed(self.mixer_norm, hidden, residual)
             mixed = self.mixer.forward(x, ctx, run)
         if hasattr(self.feed_forward, "forward_normed"):
             return self.feed_forward.forward_normed(mixed, residual, self.feed_forward_norm, ctx)
-        x, residual = self.feed_forward_norm.add(mixed, residual)
+        x, residual = _normed(self.feed_forward_norm, mixed, residual)
         return self.feed_forward.forward(x, ctx), residual
+
+
+def _normed(norm, hidden, residual):
+    """(norm(hidden + residual), hidden + residual); either of the two may be missing: the first
+    layer has no residual yet, and a part that added its output to the stream returns no output."""
+    if hidden is None:
+        return norm.forward(residual), residual
+    if residual is None:
+        return norm.forward(hidden), hidden
+    return norm.add(hidden, residual)
 
 
 register_part("block", "prenorm_residual", PreNormResidualBlock)

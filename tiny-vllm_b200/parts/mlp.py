@@ -6,7 +6,7 @@ gate and up are one packed projection [gate | up]
 
 from __future__ import annotations
 
-from ..ops import linear, linear_norm, linear_silu
+from ..ops import linear, linear_into_stream, linear_norm, linear_silu
 from .base import BuildContext, ParamSpec, Part
 from .registry import register_part
 
@@ -37,9 +37,10 @@ class SwiGLU(Part):
         return linear(linear_silu(x, self.gate_up_weight), self.down_weight)
 
     def forward_normed(self, hidden, residual, norm, ctx):
-        """forward(norm(hidden + residual)) and the new residual stream."""
+        """forward(norm(hidden + residual)) and the new residual stream; the output is None when
+        the down projection has added it to the stream itself."""
         activated, residual = linear_norm(hidden, residual, norm, self.gate_up_weight, silu=True)
-        return linear(activated, self.down_weight), residual
+        return linear_into_stream(activated, self.down_weight, residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
