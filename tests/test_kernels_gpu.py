@@ -81,7 +81,8 @@ def test_rope_tables_match_the_float32_formula():
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("heads", [(8, 2, 64), (3, 3, 80), (16, 8, 128), (2, 1, 256)])
+@pytest.mark.parametrize("heads", [(8, 2, 64), (3, 3, 80), (16, 8, 128), (2, 1, 256), (5, 5, 16), (40, 8, 32),
+                                   (36, 4, 128)])
 def test_qk_norm_rope_store(dtype, heads):
     nq, nkv, d = heads
     torch.manual_seed(d)

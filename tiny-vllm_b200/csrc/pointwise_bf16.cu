@@ -135,8 +135,12 @@ extern "C" int tvb_silu_mul_bf16(const void* gate_up, void* out, int rows, int i
 }
 
 // ------------------------------------- q/k norm + rotation + cache write, fused
-// LANES = head_dim / 8 lanes share a (token, head) row: lane l holds 4 values of the first half
-// (at 4 l) and the 4 values they pair with in the second half.  head_dim is 16, 32, 64, 128 or 256.
+// One warp per token.  LANES = head_dim / 16 lanes share a head: lane l holds 8 values of the first
+// half (at 8 l) and the 8 they pair with in the second half, so every access is 16 bytes.  The
+// warp's 32 / LANES groups of lanes take the token's heads in turn (q, then k, then v), four heads
+// of a group at a time with all their loads issued before the first is used; position, cache slot,
+// rotation angles and norm weights are read once per thread, not once per head.
+// head_dim is 16, 32, 64, 128 or 256.
 template <int HEAD_DIM, typename W>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_store_bf16_kernel(bf16* __restrict__ qkv, const W* __restrict__ q_weight,
@@ -146,67 +150,106 @@ qk_norm_rope_store_bf16_kernel(bf16* __restrict__ qkv, const W* __restrict__ q_w
                                bf16* __restrict__ value_cache, int tokens, int num_q, int num_kv,
                                int page_size, int table_positions, float eps) {
     constexpr int HALF = HEAD_DIM / 2;
-    constexpr int LANES = HEAD_DIM / 8;
+    constexpr int LANES = HEAD_DIM / 16;
+    constexpr int GROUPS = 32 / LANES;
+    constexpr int BATCH = 4;
     const int heads = num_q + 2 * num_kv;
-    const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / LANES;
-    const int lane = threadIdx.x % LANES;
-    const bool live = row < (int64_t)tokens * heads;
-    const int token = live ? (int)(row / heads) : 0, head = live ? (int)(row % heads) : 0;
-    bf16* src = qkv + ((int64_t)token * heads + head) * HEAD_DIM + 4 * lane;
-    const int slot = slots && live ? slots[token] : -1;
-    const bool is_value = head >= num_q + num_kv, is_key = !is_value && head >= num_q;
-    float a[4], b[4];
-    {
-        const uint2 lo = live ? *reinterpret_cast<const uint2*>(src) : make_uint2(0, 0);
-        const uint2 hi = live ? *reinterpret_cast<const uint2*>(src + HALF) : make_uint2(0, 0);
-        a[0] = __uint_as_float(lo.x << 16); a[1] = __uint_as_float(lo.x & 0xffff0000u);
-        a[2] = __uint_as_float(lo.y << 16); a[3] = __uint_as_float(lo.y & 0xffff0000u);
-        b[0] = __uint_as_float(hi.x << 16); b[1] = __uint_as_float(hi.x & 0xffff0000u);
-        b[2] = __uint_as_float(hi.y << 16); b[3] = __uint_as_float(hi.y & 0xffff0000u);
+    const int token = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (token >= tokens) return;                 // the whole warp
+    const int lane = threadIdx.x & 31;
+    const int group = lane / LANES, l = lane % LANES;
+    const int slot = slots ? slots[token] : -1;
+    const bool rotated = cos_table != nullptr;
+    // Every intermediate of the rotation is a bfloat16 (the product of two bfloat16 is exact in
+    // float32, so rounding it once is the packed instruction's own rounding): it runs on pairs.
+    __nv_bfloat162 cs[4], sn[4];
+    float wq_lo[8], wq_hi[8], wk_lo[8], wk_hi[8];
+    if (rotated) {
+        int position = positions[token];
+        position = position < 0 ? 0 : (position >= table_positions ? table_positions - 1 : position);
+        const float4* c4 = reinterpret_cast<const float4*>(cos_table + (int64_t)position * HALF + 8 * l);
+        const float4* s4 = reinterpret_cast<const float4*>(sin_table + (int64_t)position * HALF + 8 * l);
+        const float4 c_lo = c4[0], c_hi = c4[1], s_lo = s4[0], s_hi = s4[1];
+        cs[0] = __floats2bfloat162_rn(c_lo.x, c_lo.y), cs[1] = __floats2bfloat162_rn(c_lo.z, c_lo.w);
+        cs[2] = __floats2bfloat162_rn(c_hi.x, c_hi.y), cs[3] = __floats2bfloat162_rn(c_hi.z, c_hi.w);
+        sn[0] = __floats2bfloat162_rn(s_lo.x, s_lo.y), sn[1] = __floats2bfloat162_rn(s_lo.z, s_lo.w);
+        sn[2] = __floats2bfloat162_rn(s_hi.x, s_hi.y), sn[3] = __floats2bfloat162_rn(s_hi.z, s_hi.w);
     }
-    const W* weight = is_key ? k_weight : q_weight;
-    // every lane of the warp takes part in the shuffles, whatever its row is
-    float squares = 0.0f;
+    const bool normed = q_weight != nullptr;     // the two weights come together
+    if (normed) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(a[e], a[e]), __fmul_rn(b[e], b[e])));
-#pragma unroll
-    for (int delta = LANES / 2; delta > 0; delta >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, delta);
-    if (!live) return;
-    bf16* dst = src;
-    if (is_value || is_key) {
-        if (slot < 0) return;
-        bf16* cache = is_value ? value_cache : key_cache;
-        const int kv_head = is_value ? head - num_q - num_kv : head - num_q;
-        dst = cache + (((int64_t)(slot / page_size) * num_kv + kv_head) * page_size + slot % page_size) * HEAD_DIM +
-              4 * lane;
-    }
-    if (!is_value) {
-        if (weight) {
-            const float inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(squares, 1.0f / (float)HEAD_DIM), eps)));
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                a[e] = round_to<bf16>(__fmul_rn(round_to<bf16>(__fmul_rn(a[e], inverse_rms)), to_float<W>(weight[4 * lane + e])));
-                b[e] = round_to<bf16>(__fmul_rn(round_to<bf16>(__fmul_rn(b[e], inverse_rms)), to_float<W>(weight[4 * lane + e + HALF])));
-            }
-        }
-        if (cos_table) {
-            int position = positions[token];
-            position = position < 0 ? 0 : (position >= table_positions ? table_positions - 1 : position);
-            const float4 c4 = *reinterpret_cast<const float4*>(cos_table + (int64_t)position * HALF + 4 * lane);
-            const float4 s4 = *reinterpret_cast<const float4*>(sin_table + (int64_t)position * HALF + 4 * lane);
-            const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float c = round_to<bf16>(cs[e]), s = round_to<bf16>(sn[e]);
-                const float ac = round_to<bf16>(__fmul_rn(a[e], c)), bs = round_to<bf16>(__fmul_rn(b[e], s));
-                const float bc = round_to<bf16>(__fmul_rn(b[e], c)), as = round_to<bf16>(__fmul_rn(a[e], s));
-                a[e] = __fsub_rn(ac, bs);
-                b[e] = __fadd_rn(bc, as);
-            }
+        for (int e = 0; e < 8; ++e) {
+            wq_lo[e] = to_float<W>(q_weight[8 * l + e]), wq_hi[e] = to_float<W>(q_weight[HALF + 8 * l + e]);
+            wk_lo[e] = to_float<W>(k_weight[8 * l + e]), wk_hi[e] = to_float<W>(k_weight[HALF + 8 * l + e]);
         }
     }
-    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]));
-    *reinterpret_cast<uint2*>(dst + HALF) = make_uint2(pack_bf16x2(b[0], b[1]), pack_bf16x2(b[2], b[3]));
+    bf16* row = qkv + (int64_t)token * heads * HEAD_DIM + 8 * l;
+    const int64_t cache_row = slot >= 0 ? ((int64_t)(slot / page_size) * num_kv * page_size + slot % page_size) : 0;
+
+    // every lane goes round the same number of times: the shuffles below are warp-wide
+    for (int first = 0; first < heads; first += GROUPS * BATCH) {
+        uint4 lo[BATCH], hi[BATCH];
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const int head = first + i * GROUPS + group;
+            lo[i] = hi[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (head < heads) {
+                lo[i] = *reinterpret_cast<const uint4*>(row + (int64_t)head * HEAD_DIM);
+                hi[i] = *reinterpret_cast<const uint4*>(row + (int64_t)head * HEAD_DIM + HALF);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const int head = first + i * GROUPS + group;
+            const bool live = head < heads;
+            const bool is_value = head >= num_q + num_kv, is_key = !is_value && head >= num_q;
+            __align__(16) __nv_bfloat162 a2[4];
+            __align__(16) __nv_bfloat162 b2[4];
+            *reinterpret_cast<uint4*>(a2) = lo[i];
+            *reinterpret_cast<uint4*>(b2) = hi[i];
+            float squares = 0.0f;
+            if (normed) {            // the same for the whole warp
+                float a[8], b[8];
+                unpack_bf16x8(lo[i], a);
+                unpack_bf16x8(hi[i], b);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(a[e], a[e]), __fmul_rn(b[e], b[e])));
+#pragma unroll
+                for (int delta = LANES / 2; delta > 0; delta >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, delta);
+                if (live && !is_value) {
+                    const float inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(squares, 1.0f / (float)HEAD_DIM), eps)));
+                    const float* w_lo = is_key ? wk_lo : wq_lo;
+                    const float* w_hi = is_key ? wk_hi : wq_hi;
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        // round(round(x * inverse rms) * weight), two values at a time
+                        const float2 x = __bfloat1622float2(__floats2bfloat162_rn(__fmul_rn(a[2 * p], inverse_rms), __fmul_rn(a[2 * p + 1], inverse_rms)));
+                        const float2 y = __bfloat1622float2(__floats2bfloat162_rn(__fmul_rn(b[2 * p], inverse_rms), __fmul_rn(b[2 * p + 1], inverse_rms)));
+                        a2[p] = __floats2bfloat162_rn(__fmul_rn(x.x, w_lo[2 * p]), __fmul_rn(x.y, w_lo[2 * p + 1]));
+                        b2[p] = __floats2bfloat162_rn(__fmul_rn(y.x, w_hi[2 * p]), __fmul_rn(y.y, w_hi[2 * p + 1]));
+                    }
+                }
+            }
+            if (!live) continue;
+            bf16* dst = row + (int64_t)head * HEAD_DIM;
+            if (is_value || is_key) {
+                if (slot < 0) continue;
+                const int kv_head = is_value ? head - num_q - num_kv : head - num_q;
+                dst = (is_value ? value_cache : key_cache) + (cache_row + (int64_t)kv_head * page_size) * HEAD_DIM + 8 * l;
+            }
+            if (!is_value && rotated) {
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const __nv_bfloat162 ac = __hmul2(a2[p], cs[p]), bs = __hmul2(b2[p], sn[p]);
+                    const __nv_bfloat162 bc = __hmul2(b2[p], cs[p]), as = __hmul2(a2[p], sn[p]);
+                    a2[p] = __hsub2(ac, bs);
+                    b2[p] = __hadd2(bc, as);
+                }
+            }
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(a2);
+            *reinterpret_cast<uint4*>(dst + HALF) = *reinterpret_cast<const uint4*>(b2);
+        }
+    }
 }
 
 extern "C" int tvb_qk_norm_rope_store_bf16_supports(int head_dim) {
@@ -222,9 +265,8 @@ extern "C" int tvb_qk_norm_rope_store_bf16(void* qkv, const void* q_weight, cons
     if (tokens <= 0) return 0;
     if (!tvb_qk_norm_rope_store_bf16_supports(head_dim) || num_q <= 0 || num_kv < 0 || (slots && page_size <= 0))
         return TVB_BAD_ARGUMENT;
-    const int64_t threads = (int64_t)tokens * (num_q + 2 * num_kv) * (head_dim / 8);
-    const int64_t blocks = (threads + 255) / 256;
-    if (blocks > 2147483647LL) return TVB_BAD_ARGUMENT;
+    if (head_dim % 8 || ((num_q + 2 * num_kv) * head_dim) % 8) return TVB_BAD_ARGUMENT;
+    const int64_t blocks = ((int64_t)tokens + 7) / 8;         // a warp per token, eight to a block
     cudaStream_t s = (cudaStream_t)stream;
 #define QK_LAUNCH(D, WT)                                                                                   \
     qk_norm_rope_store_bf16_kernel<D, WT><<<(unsigned)blocks, 256, 0, s>>>(                                \
