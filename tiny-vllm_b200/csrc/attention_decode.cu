@@ -156,6 +156,10 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         return;
     }
 
+    // Every CTA says that it runs; the stores into the first CTA's shared memory at the end wait
+    // until all of them have said so.
+    cluster_arrive();
+
     // ---- the keys [lo, position] are cut into `splits` pieces of a size that depends on this
     // request alone; piece `split` is this CTA's.  Keys [first, last] of it are in the cache.
     const int lo = window > 0 ? max(0, position - window + 1) : 0;
@@ -353,6 +357,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         if (t4 == 0) { sh.warp_m[warp][g] = m_run; sh.warp_l[warp][g] = l_run; }
     }
     __syncthreads();
+    cluster_wait();
     DecodeShared<HEAD_DIM, HPB, DEC_WARPS>* first_cta = cluster.map_shared_rank(&sh, 0);
     for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
         const int h = index / HEAD_DIM, dim = index % HEAD_DIM;

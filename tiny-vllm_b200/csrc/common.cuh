@@ -84,6 +84,10 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float* f) {
                       pack_bf16x2(f[6], f[7]));
 }
 
+// ---- the cluster's barrier in two halves: arrive early, wait where the others are needed
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+
 // ---- programmatic dependent launch: a kernel launched with the attribute may start while the
 // kernel before it in the stream still runs.  It must call pdl_wait() before it reads what that
 // kernel wrote and before its own first write to global memory; pdl_launch_dependents() lets

@@ -11,9 +11,10 @@
 // instructions without any shuffle.
 //
 // Work is cut as (N / 16 row tiles) x (k blocks dealt round-robin to the 4 warps of the CTAs
-// of a thread-block cluster).  Warps, then CTAs (through distributed shared memory, in rank
-// order) add their partial tiles, so the sum order is fixed and nothing is staged in global
-// memory.  Loads of W are issued before the wait on the previous kernel of the stream
+// of a thread-block cluster).  Warps add their partial tiles, every CTA stores its sum into the
+// shared memory of the cluster's first CTA (distributed shared memory), and after one cluster
+// barrier that CTA adds them in rank order: the sum order is fixed, nothing is staged in global
+// memory, and the other CTAs are done at the barrier.  Loads of W are issued before the wait on the previous kernel of the stream
 // (programmatic dependent launch), since weights do not depend on it.
 //
 // Prologue (optional): x = RMSNorm(h + residual) computed by every CTA for itself into
@@ -85,7 +86,10 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
     constexpr int SETS = MODE == MODE_SILU ? 2 : 1;
     constexpr int MP = 8 * NT;
     __shared__ float warp_part[SM_WARPS][SETS][16][MP];
-    __shared__ float cta_part[SETS][16][MP];
+    // partial tiles of every CTA of the cluster; only the first CTA's copy is used: the others store
+    // theirs into it through distributed shared memory
+    constexpr int MAX_RANKS = NT <= 2 ? 8 : 4;
+    __shared__ float cluster_part[MAX_RANKS][SETS][16][MP];
     constexpr bool PROLOGUE_NORM = NORM == 1 || NORM == 2;
     constexpr bool SCALED = NORM >= 3;
     extern __shared__ __align__(16) unsigned char dynamic_shared[];
@@ -93,6 +97,9 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
 
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = blockIdx.x, ranks = gridDim.x;
+    // Every CTA says that it runs; before the first store into another CTA's shared memory the
+    // epilogue makes sure that all of them have said so.
+    cluster_arrive();
     const int n0 = blockIdx.y * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t4 = lane & 3;
@@ -262,11 +269,15 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
             warp_part[warp][s][g + 8][8 * j + 2 * t4 + 1] = acc[s][j][3];
         }
     __syncthreads();
-    for (int index = threadIdx.x; index < SETS * 16 * MP; index += SM_WARPS * 32) {
-        float total = 0.0f;
+    cluster_wait();
+    {
+        float* slot_at_first = cluster.map_shared_rank(&cluster_part[0][0][0][0], 0) + rank * (SETS * 16 * MP);
+        for (int index = threadIdx.x; index < SETS * 16 * MP; index += SM_WARPS * 32) {
+            float total = 0.0f;
 #pragma unroll
-        for (int wi = 0; wi < SM_WARPS; ++wi) total += (&warp_part[wi][0][0][0])[index];
-        (&cta_part[0][0][0])[index] = total;
+            for (int wi = 0; wi < SM_WARPS; ++wi) total += (&warp_part[wi][0][0][0])[index];
+            slot_at_first[index] = total;       // a store into the first CTA's shared memory
+        }
     }
     // thread -> (row of x, column of the tile), columns fastest: 16 consecutive outputs per row; what the
     // epilogue adds from the stream is asked for before the barrier, so that it arrives meanwhile
@@ -279,7 +290,7 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
         if (MODE == MODE_BF16 && rank == 0 && into.stream && row < m && n0 + col < n)
             from_stream[i] = bf16_bits_to_float(ld_global_u16(into.stream + (int64_t)row * n + n0 + col));
     }
-    cluster.sync();
+    cluster.sync();                             // every CTA's stores have arrived; the others are done
     if (rank == 0) {
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
@@ -289,10 +300,7 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
 #pragma unroll
             for (int s = 0; s < SETS; ++s) {
                 float total = 0.0f;
-                for (int r = 0; r < ranks; ++r) {
-                    const float* other = cluster.map_shared_rank(&cta_part[0][0][0], r);
-                    total += other[(s * 16 + col) * MP + row];
-                }
+                for (int r = 0; r < ranks; ++r) total += cluster_part[r][s][col][row];
                 value[s] = total;
             }
             if (SCALED) {
@@ -335,7 +343,6 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
             }
         }
     }
-    cluster.sync();
 }
 
 template <int NT, int MODE, int NORM>
@@ -396,8 +403,9 @@ extern "C" int tvb_gemm_small_m(const void* x, long long ldx, const void* w, lon
     // enough CTAs per row tile that every warp has about one batch of k blocks, at most 8 per
     // cluster (a power of two)
     const int wanted = (k_blocks + SM_WARPS * SM_BATCH - 1) / (SM_WARPS * SM_BATCH);
+    const int max_ranks = m <= 16 ? 8 : 4;      // what the kernel's shared memory holds partial tiles of
     int ranks = 1;
-    while (ranks < wanted && ranks < 8) ranks *= 2;
+    while (ranks < wanted && ranks < max_ranks) ranks *= 2;
     const int up_offset = mode == MODE_SILU ? n : 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = (m + 7) / 8;
