@@ -71,9 +71,10 @@ __device__ __forceinline__ void dec_mma(float (&d)[4], uint32_t a0, uint32_t a2,
 }
 
 // RMSNorm + half-split rotation of one head by one warp; result rounded to bfloat16, as float.
-// `src` was written by the kernel before this one: read through volatile loads.
+// `src` was written by the kernel before this one: read with plain coherent loads that are all in
+// flight together (volatile ones would go one after the other, a latency each).
 template <int HEAD_DIM, typename W>
-__device__ __forceinline__ void norm_rotate_head(const volatile unsigned short* src, const W* __restrict__ weight,
+__device__ __forceinline__ void norm_rotate_head(const unsigned short* src, const W* __restrict__ weight,
                                                  float eps, const float* __restrict__ cos_row,
                                                  const float* __restrict__ sin_row, float* __restrict__ dst,
                                                  int lane) {
@@ -86,8 +87,8 @@ __device__ __forceinline__ void norm_rotate_head(const volatile unsigned short* 
         const int j = lane + 32 * i;
         a[i] = b[i] = 0.0f;
         if (j < HALF) {
-            a[i] = bf16_bits_to_float(src[j]);
-            b[i] = bf16_bits_to_float(src[j + HALF]);
+            a[i] = bf16_bits_to_float(ld_global_u16(src + j));
+            b[i] = bf16_bits_to_float(ld_global_u16(src + j + HALF));
             squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(a[i], a[i]), __fmul_rn(b[i], b[i])));
         }
     }
@@ -222,8 +223,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     // ---- the new token: q heads of this CTA, and k, v of its kv head
     pdl_wait();                                 // the projection comes from the kernel before this one
     {
-        const volatile unsigned short* token =
-            reinterpret_cast<const volatile unsigned short*>(qkv) + (int64_t)request * heads * HEAD_DIM;
+        const unsigned short* token = reinterpret_cast<const unsigned short*>(qkv) + (int64_t)request * heads * HEAD_DIM;
         const int table_row = min(position, table_positions - 1);
         const float* cos_row = cos_table ? cos_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
         const float* sin_row = sin_table ? sin_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
@@ -235,8 +235,9 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                 norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(num_q + kv_head) * HEAD_DIM, k_weight, eps,
                                               cos_row, sin_row, sh.k_new, lane);
             } else {
-                const volatile unsigned short* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
-                for (int i = lane; i < HEAD_DIM; i += 32) sh.v_new[i] = bf16_bits_to_float(v[i]);
+                const unsigned short* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
+#pragma unroll
+                for (int i = 0; i < HEAD_DIM / 32; ++i) sh.v_new[lane + 32 * i] = bf16_bits_to_float(ld_global_u16(v + lane + 32 * i));
             }
         }
     }
@@ -283,6 +284,8 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         for (int i = 0; i < 4; ++i) o_run[n][i] = 0.0f;
 
     for (int i = 0; i < mine; ++i) {
+        // the next sub-tile is asked for before this one is waited for (asking after the products
+        // instead, with every stage filled up front, measured 1 % slower on the whole step)
         if (i + DEC_STAGES - 1 < mine) issue(i + DEC_STAGES - 1);
         cp_async_commit();
         cp_async_wait<DEC_STAGES - 1>();        // sub-tile i has landed ...
@@ -389,14 +392,36 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     if (split == 0) {
         for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
             const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
-            float m = -INFINITY;
-            for (int r = 0; r < splits; ++r) m = fmaxf(m, sh.part_m[r][h]);
             float l = 0.0f, o = 0.0f;
-            for (int r = 0; r < splits; ++r) {
-                const float pm = sh.part_m[r][h];
-                const float f = pm == -INFINITY ? 0.0f : __expf(pm - m);
-                l += sh.part_l[r][h] * f;
-                o += sh.part_o[r][h][dim] * f;
+            if constexpr (HPB >= 2) {
+                // unrolled over the largest cluster, so that the loads and exponentials of all pieces
+                // are in flight together; the sums keep the rank order.  (With one q head a CTA the
+                // registers of this form would cost the kernel its fourth CTA per SM.)
+                float pm[DEC_MAX_SPLITS], pl[DEC_MAX_SPLITS], po[DEC_MAX_SPLITS];
+                float m = -INFINITY;
+#pragma unroll
+                for (int r = 0; r < DEC_MAX_SPLITS; ++r) {
+                    const bool in = r < splits;
+                    pm[r] = in ? sh.part_m[r][h] : -INFINITY;
+                    pl[r] = in ? sh.part_l[r][h] : 0.0f;
+                    po[r] = in ? sh.part_o[r][h][dim] : 0.0f;
+                    m = fmaxf(m, pm[r]);
+                }
+#pragma unroll
+                for (int r = 0; r < DEC_MAX_SPLITS; ++r) {
+                    const float f = pm[r] == -INFINITY ? 0.0f : __expf(pm[r] - m);
+                    l += pl[r] * f;
+                    o += po[r] * f;
+                }
+            } else {
+                float m = -INFINITY;
+                for (int r = 0; r < splits; ++r) m = fmaxf(m, sh.part_m[r][h]);
+                for (int r = 0; r < splits; ++r) {
+                    const float pm = sh.part_m[r][h];
+                    const float f = pm == -INFINITY ? 0.0f : __expf(pm - m);
+                    l += sh.part_l[r][h] * f;
+                    o += sh.part_o[r][h][dim] * f;
+                }
             }
             out_row[index] = __float2bfloat16_rn(o / l);
         }
