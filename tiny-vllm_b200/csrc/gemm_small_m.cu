@@ -14,8 +14,9 @@
 // of a thread-block cluster).  Warps add their partial tiles, every CTA stores its sum into the
 // shared memory of the cluster's first CTA (distributed shared memory), and after one cluster
 // barrier that CTA adds them in rank order: the sum order is fixed, nothing is staged in global
-// memory, and the other CTAs are done at the barrier.  Loads of W are issued before the wait on the previous kernel of the stream
-// (programmatic dependent launch), since weights do not depend on it.
+// memory, and the other CTAs are done at the barrier.  Loads of W are issued before the wait on
+// the previous kernel of the stream (programmatic dependent launch), since weights do not depend
+// on it, and the kernel behind this one is released at once, so that it can do the same.
 //
 // Prologue (optional): x = RMSNorm(h + residual) computed by every CTA for itself into
 // shared memory while its weights are in flight (tinyvllm/kernels/pointwise.cu:153-211);
