@@ -1,8 +1,8 @@
 """bfloat16 matrix products: which kernel takes which shape.
 
-Up to 16 rows (decode) with a bfloat16 result: the package's weight-streaming kernel (measured
-against cuBLAS per shape: it wins up to 8 rows by 20 to 50 %, is level around 16 and loses
-beyond).  Results in float32 (the logits: vocabulary x width, the one product of a decode step
+Up to 16 rows (decode) with a bfloat16 result and a weight of up to 40 MB (24 MB beyond 8 rows):
+the package's weight-streaming kernel (measured against cuBLAS per shape: it wins up to 8 rows
+by 20 to 50 %, is level around 16 and loses beyond, and loses on large weights).  Results in float32 (the logits: vocabulary x width, the one product of a decode step
 that is long enough to be bound by bandwidth alone) go to cuBLAS with float32 output at every
 row count: 53 us against 84 us at 8 rows.  The packed gate/up product
 with its activation at 128 rows and more (prefill): the package's tcgen05 kernel, which keeps
@@ -38,11 +38,21 @@ def next_weight(weight: torch.Tensor) -> torch.Tensor | None:
 TC_MIN_ROWS = 128
 # rows up to which the weight-streaming kernel is chosen over cuBLAS
 SMALL_M_DISPATCH_ROWS = 16
+# ... and the size of the weight up to which it is: the kernel is built for the latency of small
+# products (many small CTAs, a cluster barrier at the end) and streams at 3 to 4 TB/s at best, while
+# cuBLAS reaches 5.4 to 5.7 TB/s on weights of 100 MB and more.  Measured in CUDA graphs, weights
+# rotated through more than L2 (us, this kernel / cuBLAS): 8 rows 12.6 MB 3.9 / 7.6, 33.6 MB
+# 11.7 / 12.6, 50 MB 16.9 / 11.6, 84 MB 25.2 / 17.6, 201 MB 50 / 37, 524 MB 130 / 93; 16 rows
+# 12.6 MB 5.3 / 7.8, 33.6 MB 16.8 / 9.3, 50 MB 22.4 / 12.8.
+SMALL_M_MAX_WEIGHT_BYTES = 40 << 20
+SMALL_M_MAX_WEIGHT_BYTES_OVER_8_ROWS = 24 << 20
 
 
 def small(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether the weight-streaming kernel takes this product."""
-    return (x.shape[0] <= SMALL_M_DISPATCH_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+    limit = SMALL_M_MAX_WEIGHT_BYTES if x.shape[0] <= 8 else SMALL_M_MAX_WEIGHT_BYTES_OVER_8_ROWS
+    return (x.shape[0] <= SMALL_M_DISPATCH_ROWS and weight.numel() * weight.element_size() <= limit
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1
             and x.stride(0) % 8 == 0 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0)
 
 
