@@ -449,7 +449,7 @@ def test_attention_prefill_tc_refuses():
 
 @pytest.mark.parametrize("window", [None, 150])
 @pytest.mark.parametrize("shape", [(4, 2, 64, 16, 8), (8, 2, 128, 16, 4), (2, 2, 128, 7, 1),
-                                   (8, 1, 256, 32, 5), (16, 8, 128, 16, 8)])
+                                   (8, 1, 256, 32, 5), (16, 8, 128, 16, 8), (16, 2, 128, 16, 8), (8, 1, 64, 8, 3)])
 def test_attention_decode_fused(shape, window):
     """Raw projection in, attention out: against q/k norm + rotation + attention of the plain
     functions, with the new key and value checked in the cache."""

@@ -457,7 +457,8 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
-// 1 if the kernel takes this shape: head sizes 64, 128, 256; groups of 1, 2, 4 or a multiple of 4.
+// 1 if the kernel takes this shape: head sizes 64, 128, 256; groups of 1, 2 or a multiple of 4
+// (a CTA serves 1, 2, 4 or, where the group is a multiple of 8 and the head size at most 128, 8 q heads).
 extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv, int splits) {
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return 0;
     if (num_kv <= 0 || num_q % num_kv) return 0;
@@ -486,7 +487,9 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
         requests > 65535 || max_context <= 0)
         return TVB_BAD_ARGUMENT;
     const int group = num_q / num_kv;
-    const int hpb = group % 4 == 0 ? 4 : group;
+    // q heads a CTA serves (they share its keys): with 8 and more heads per kv head a CTA takes 8, so
+    // that no key is read twice; that costs residency (87 KB of shared memory at head size 128)
+    const int hpb = (group % 8 == 0 && head_dim <= 128) ? 8 : (group % 4 == 0 ? 4 : group);
     cudaStream_t s = (cudaStream_t)stream;
     // Four warps a CTA keep four CTAs on an SM, which is what counts when the grid fills the GPU;
     // a grid of fewer CTAs than SMs (one or two requests) is faster with eight warps a CTA, each
@@ -511,6 +514,7 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
     do {                                                                \
         if (hpb == 1) DECODE_BY_WARPS(D, 1, WT);                        \
         if (hpb == 2) DECODE_BY_WARPS(D, 2, WT);                        \
+        if (hpb == 8) DECODE_BY_WARPS(D, 8, WT);                        \
         DECODE_BY_WARPS(D, 4, WT);                                      \
     } while (0)
 #define DECODE_BY_DIM(WT)                                               \
