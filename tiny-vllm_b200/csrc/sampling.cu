@@ -74,7 +74,7 @@ __device__ __forceinline__ void block_argmax(float& value, int& index, float* va
 }
 
 template <typename T>
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+__global__ void __launch_bounds__(SAMPLE_THREADS, 1)
 sample_rows_kernel(const T* logits, int64_t row_stride, int vocab,   // logits: from the kernel before
                    const int* __restrict__ packed, int capacity, int* __restrict__ tokens) {
     __shared__ float fscratch[32];
@@ -162,15 +162,21 @@ sample_rows_kernel(const T* logits, int64_t row_stride, int vocab,   // logits: 
     const uint32_t draw_lo = (uint32_t)packed[5 * capacity + row], draw_hi = (uint32_t)packed[6 * capacity + row];
     float win = -INFINITY;
     int win_index = 0x7fffffff;
-    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
-        const float s = SCORE(i);
-        const uint32_t key = ordered_key(s);
-        if (key < p_key || !KEPT_K(key, i)) continue;
+    // a thread takes four consecutive tokens at a time: they share one Philox block
+    for (int quad = tid; quad * 4 < vocab; quad += SAMPLE_THREADS) {
         uint32_t words[4];
-        philox4x32_10((uint32_t)(i >> 2), draw_lo, draw_hi, 0u, seed_lo, seed_hi, words);
-        const float u = __fmul_rn(__fadd_rn((float)(words[i & 3] >> 9), 0.5f), 1.0f / 8388608.0f);
-        const float ratio = __fdiv_rn(expf(s), -logf(u));
-        if (ratio > win) { win = ratio; win_index = i; }
+        philox4x32_10((uint32_t)quad, draw_lo, draw_hi, 0u, seed_lo, seed_hi, words);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = quad * 4 + e;
+            if (i >= vocab) break;
+            const float s = SCORE(i);
+            const uint32_t key = ordered_key(s);
+            if (key < p_key || !KEPT_K(key, i)) continue;
+            const float u = __fmul_rn(__fadd_rn((float)(words[e] >> 9), 0.5f), 1.0f / 8388608.0f);
+            const float ratio = __fdiv_rn(expf(s), -logf(u));
+            if (ratio > win) { win = ratio; win_index = i; }
+        }
     }
     block_argmax(win, win_index, fscratch, iscratch);
     if (tid == 0) tokens[row] = win_index == 0x7fffffff ? best_index : win_index;
