@@ -1,5 +1,6 @@
-// Next-token sampling, one block per row of logits: greedy argmax, or temperature
-// with optional top-k and top-p and an exponential race as the draw.
+// Next-token sampling, a cluster of 8 CTAs per row of logits (each takes an eighth of the
+// vocabulary; partial results meet through distributed shared memory): greedy argmax, or
+// temperature with optional top-k and top-p and an exponential race as the draw.
 //
 // Follows tinyvllm/sampling.py: argmax for temperature 0 (:42-43); scores =
 // (logits - max) / temperature in float32 (:82-104); the k largest scores stay
@@ -18,7 +19,14 @@
 // scores, each probe being one pass over the row.
 #include "common.cuh"
 
-#define SAMPLE_THREADS 1024
+#include <cstdint>
+
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
+#define SAMPLE_THREADS 256
+#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+#define SAMPLE_CTAS 8           // CTAs (one cluster) that share a row
 
 __device__ __forceinline__ uint32_t ordered_key(float f) {
     const uint32_t b = __float_as_uint(f);
@@ -38,61 +46,143 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t
     out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
 
-__device__ __forceinline__ int block_sum_int(int v, int* scratch) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int delta = 16; delta > 0; delta >>= 1) v += __shfl_xor_sync(0xffffffffu, v, delta);
-    __syncthreads();
-    if (lane == 0) scratch[warp] = v;
-    __syncthreads();
-    int total = lane < (SAMPLE_THREADS >> 5) ? scratch[lane] : 0;
-#pragma unroll
-    for (int delta = 16; delta > 0; delta >>= 1) total += __shfl_xor_sync(0xffffffffu, total, delta);
-    return total;
-}
+// What the CTAs of a row's cluster tell one another: every reduction below ends with each CTA's
+// partial result in slot [buffer][rank] of every CTA's copy, written through distributed shared
+// memory, and one cluster barrier; the buffers alternate, so a slot is not written again before
+// every CTA has read it (it has to pass the barrier in between).
+struct SampleShared {
+    float warp_f[SAMPLE_WARPS];
+    int warp_i[SAMPLE_WARPS];
+    float part_f[2][SAMPLE_CTAS];
+    int part_i[2][SAMPLE_CTAS];
+};
 
-// argmax of (value, smaller index wins ties) over the block; every thread gets it
-__device__ __forceinline__ void block_argmax(float& value, int& index, float* vals, int* idxs) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+struct RowTeam {
+    cg::cluster_group cluster;
+    SampleShared* sh;
+    int rank;
+    int phase;
+
+    // partial (f, i) of this CTA, held by thread 0, to every CTA of the cluster; then the barrier
+    __device__ __forceinline__ void publish(float f, int i) {
+        if (threadIdx.x == 0) {
 #pragma unroll
-    for (int delta = 16; delta > 0; delta >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, value, delta);
-        const int oi = __shfl_xor_sync(0xffffffffu, index, delta);
-        if (ov > value || (ov == value && oi < index)) { value = ov; index = oi; }
+            for (int r = 0; r < SAMPLE_CTAS; ++r) {
+                SampleShared* other = cluster.map_shared_rank(sh, r);
+                other->part_f[phase][rank] = f;
+                other->part_i[phase][rank] = i;
+            }
+        }
+        cluster.sync();
     }
-    __syncthreads();
-    if (lane == 0) { vals[warp] = value; idxs[warp] = index; }
-    __syncthreads();
-    value = lane < (SAMPLE_THREADS >> 5) ? vals[lane] : -INFINITY;
-    index = lane < (SAMPLE_THREADS >> 5) ? idxs[lane] : 0x7fffffff;
+
+    __device__ __forceinline__ int sum(int v) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-    for (int delta = 16; delta > 0; delta >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, value, delta);
-        const int oi = __shfl_xor_sync(0xffffffffu, index, delta);
-        if (ov > value || (ov == value && oi < index)) { value = ov; index = oi; }
+        for (int delta = 16; delta > 0; delta >>= 1) v += __shfl_xor_sync(0xffffffffu, v, delta);
+        __syncthreads();
+        if (lane == 0) sh->warp_i[warp] = v;
+        __syncthreads();
+        int total = 0;
+#pragma unroll
+        for (int w = 0; w < SAMPLE_WARPS; ++w) total += sh->warp_i[w];
+        publish(0.0f, total);
+        total = 0;
+#pragma unroll
+        for (int r = 0; r < SAMPLE_CTAS; ++r) total += sh->part_i[phase][r];
+        phase ^= 1;
+        return total;
     }
-}
+
+    // warps, then CTAs, in a fixed order
+    __device__ __forceinline__ float sum(float v) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        v = warp_sum(v);
+        __syncthreads();
+        if (lane == 0) sh->warp_f[warp] = v;
+        __syncthreads();
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SAMPLE_WARPS; ++w) total = __fadd_rn(total, sh->warp_f[w]);
+        publish(total, 0);
+        total = 0.0f;
+#pragma unroll
+        for (int r = 0; r < SAMPLE_CTAS; ++r) total = __fadd_rn(total, sh->part_f[phase][r]);
+        phase ^= 1;
+        return total;
+    }
+
+    // argmax of (value, smaller index wins ties); every thread of every CTA gets it
+    __device__ __forceinline__ void argmax(float& value, int& index) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int delta = 16; delta > 0; delta >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, value, delta);
+            const int oi = __shfl_xor_sync(0xffffffffu, index, delta);
+            if (ov > value || (ov == value && oi < index)) { value = ov; index = oi; }
+        }
+        __syncthreads();
+        if (lane == 0) { sh->warp_f[warp] = value; sh->warp_i[warp] = index; }
+        __syncthreads();
+        value = sh->warp_f[0]; index = sh->warp_i[0];
+#pragma unroll
+        for (int w = 1; w < SAMPLE_WARPS; ++w) {
+            const float ov = sh->warp_f[w];
+            const int oi = sh->warp_i[w];
+            if (ov > value || (ov == value && oi < index)) { value = ov; index = oi; }
+        }
+        publish(value, index);
+        value = sh->part_f[phase][0]; index = sh->part_i[phase][0];
+#pragma unroll
+        for (int r = 1; r < SAMPLE_CTAS; ++r) {
+            const float ov = sh->part_f[phase][r];
+            const int oi = sh->part_i[phase][r];
+            if (ov > value || (ov == value && oi < index)) { value = ov; index = oi; }
+        }
+        phase ^= 1;
+    }
+};
 
 template <typename T>
-__global__ void __launch_bounds__(SAMPLE_THREADS, 1)
+__global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const T* logits, int64_t row_stride, int vocab,   // logits: from the kernel before
                    const int* __restrict__ packed, int capacity, int* __restrict__ tokens) {
-    __shared__ float fscratch[32];
-    __shared__ int iscratch[32];
+    __shared__ SampleShared shared;
+    RowTeam team{cg::this_cluster(), &shared, (int)(blockIdx.x % SAMPLE_CTAS), 0};
+    cluster_arrive();                       // this CTA runs; waited for before the first remote store
     pdl_wait();
-    const int row = blockIdx.x, tid = threadIdx.x;
+    const int row = blockIdx.x / SAMPLE_CTAS, tid = threadIdx.x;
     const T* x = logits + (int64_t)row * row_stride;
+    // this CTA's part of the row: whole groups of four tokens (they share a block of noise)
+    const int part = ((vocab + SAMPLE_CTAS - 1) / SAMPLE_CTAS + 3) / 4 * 4;
+    const int begin = min(vocab, team.rank * part), end = min(vocab, begin + part);
 
     float best = -INFINITY;
     int best_index = 0x7fffffff;
-    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
-        const float v = to_float<T>(x[i]);
-        if (v > best) { best = v; best_index = i; }
+    int scalar_from = begin;
+    if (sizeof(T) == 4 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        // float32 rows on a 16-byte boundary: four logits a load (begin is a multiple of four)
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const int quads_end = end / 4;
+#pragma unroll 4
+        for (int q = begin / 4 + tid; q < quads_end; q += SAMPLE_THREADS) {
+            const float4 v = x4[q];
+            if (v.x > best) { best = v.x; best_index = 4 * q; }
+            if (v.y > best) { best = v.y; best_index = 4 * q + 1; }
+            if (v.z > best) { best = v.z; best_index = 4 * q + 2; }
+            if (v.w > best) { best = v.w; best_index = 4 * q + 3; }
+        }
+        scalar_from = max(begin, quads_end * 4);
     }
-    block_argmax(best, best_index, fscratch, iscratch);
+    for (int i = scalar_from + tid; i < end; i += SAMPLE_THREADS) {
+        const float v = to_float<T>(x[i]);
+        if (v > best || (v == best && i < best_index)) { best = v; best_index = i; }
+    }
+    cluster_wait();
+    team.argmax(best, best_index);
     const float temp = __int_as_float(packed[row]);
-    if (!(temp > 0.0f) || best_index == 0x7fffffff) {
-        if (tid == 0) tokens[row] = best_index == 0x7fffffff ? 0 : best_index;
+    if (!(temp > 0.0f) || best_index == 0x7fffffff) {           // the same in every CTA of the row
+        if (tid == 0 && team.rank == 0) tokens[row] = best_index == 0x7fffffff ? 0 : best_index;
         return;
     }
     const float row_max = best;
@@ -107,25 +197,25 @@ sample_rows_kernel(const T* logits, int64_t row_stride, int vocab,   // logits: 
         for (int bit = 31; bit >= 0; --bit) {
             const uint32_t candidate = k_key | (1u << bit);
             int count = 0;
-            for (int i = tid; i < vocab; i += SAMPLE_THREADS) count += ordered_key(SCORE(i)) >= candidate;
-            if (block_sum_int(count, iscratch) >= k) k_key = candidate;
+            for (int i = begin + tid; i < end; i += SAMPLE_THREADS) count += ordered_key(SCORE(i)) >= candidate;
+            if (team.sum(count) >= k) k_key = candidate;
         }
         int greater = 0, equal = 0;
-        for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+        for (int i = begin + tid; i < end; i += SAMPLE_THREADS) {
             const uint32_t key = ordered_key(SCORE(i));
             greater += key > k_key;
             equal += key == k_key;
         }
-        greater = block_sum_int(greater, iscratch);
-        equal = block_sum_int(equal, iscratch);
+        greater = team.sum(greater);
+        equal = team.sum(equal);
         const int wanted = k - greater;
         if (equal > wanted) {              // ties: the first `wanted` of them by token id
             int lo = 0, hi = vocab;
             while (lo < hi) {
                 const int mid = lo + (hi - lo) / 2;
                 int count = 0;
-                for (int i = tid; i < mid; i += SAMPLE_THREADS) count += ordered_key(SCORE(i)) == k_key;
-                if (block_sum_int(count, iscratch) >= wanted) hi = mid; else lo = mid + 1;
+                for (int i = begin + tid; i < min(end, mid); i += SAMPLE_THREADS) count += ordered_key(SCORE(i)) == k_key;
+                if (team.sum(count) >= wanted) hi = mid; else lo = mid + 1;
             }
             k_index_limit = lo;
         }
@@ -136,22 +226,22 @@ sample_rows_kernel(const T* logits, int64_t row_stride, int vocab,   // logits: 
     const float p_limit = __int_as_float(packed[capacity + row]);
     uint32_t p_key = 0;
     if (p_limit < 1.0f) {
-        float part = 0.0f;
-        for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+        float mass = 0.0f;
+        for (int i = begin + tid; i < end; i += SAMPLE_THREADS) {
             const float s = SCORE(i);
-            if (KEPT_K(ordered_key(s), i)) part += expf(s);
+            if (KEPT_K(ordered_key(s), i)) mass += expf(s);
         }
-        const float total = block_sum(part, fscratch);
+        const float total = team.sum(mass);
         uint32_t lo = 0, hi = 0xffffffffu;
         while (lo < hi) {
             const uint32_t mid = lo + (hi - lo) / 2;
             float above = 0.0f;
-            for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+            for (int i = begin + tid; i < end; i += SAMPLE_THREADS) {
                 const float s = SCORE(i);
                 const uint32_t key = ordered_key(s);
                 if (key > mid && KEPT_K(key, i)) above += expf(s);
             }
-            above = block_sum(above, fscratch);
+            above = team.sum(above);
             if (__fdiv_rn(above, total) <= p_limit) hi = mid; else lo = mid + 1;
         }
         p_key = lo;
@@ -163,13 +253,13 @@ sample_rows_kernel(const T* logits, int64_t row_stride, int vocab,   // logits: 
     float win = -INFINITY;
     int win_index = 0x7fffffff;
     // a thread takes four consecutive tokens at a time: they share one Philox block
-    for (int quad = tid; quad * 4 < vocab; quad += SAMPLE_THREADS) {
+    for (int quad = begin / 4 + tid; begin < end && quad * 4 < end; quad += SAMPLE_THREADS) {
         uint32_t words[4];
         philox4x32_10((uint32_t)quad, draw_lo, draw_hi, 0u, seed_lo, seed_hi, words);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int i = quad * 4 + e;
-            if (i >= vocab) break;
+            if (i >= end) break;
             const float s = SCORE(i);
             const uint32_t key = ordered_key(s);
             if (key < p_key || !KEPT_K(key, i)) continue;
@@ -178,8 +268,8 @@ sample_rows_kernel(const T* logits, int64_t row_stride, int vocab,   // logits: 
             if (ratio > win) { win = ratio; win_index = i; }
         }
     }
-    block_argmax(win, win_index, fscratch, iscratch);
-    if (tid == 0) tokens[row] = win_index == 0x7fffffff ? best_index : win_index;
+    team.argmax(win, win_index);
+    if (tid == 0 && team.rank == 0) tokens[row] = win_index == 0x7fffffff ? best_index : win_index;
 #undef SCORE
 #undef KEPT_K
 }
@@ -192,7 +282,7 @@ extern "C" int tvb_sample_rows(const void* logits, long long row_stride, int row
     if (rows <= 0) return 0;
     if (vocab <= 0 || capacity < rows) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    TvbLaunch launch(dim3(rows), dim3(SAMPLE_THREADS), 0, s, pdl);
+    TvbLaunch launch(dim3(rows * SAMPLE_CTAS), dim3(SAMPLE_THREADS), 0, s, pdl, SAMPLE_CTAS);
     cudaError_t e;
     if (dtype == TVB_F32)
         e = cudaLaunchKernelEx(&launch.config, sample_rows_kernel<float>, (const float*)logits,
