@@ -71,7 +71,7 @@ def test_decode_runs_give_the_tokens_of_single_steps(dtype, model_folders):
                  SamplingParams(max_new_tokens=30, temperature=1.1, top_p=0.9, seed=11, ignore_eos=True),
                  SamplingParams(max_new_tokens=14, ignore_eos=True)]
     results = {}
-    for run_steps in (1, 4):
+    for run_steps in (1, 4, 32):
         engine = Engine.from_config(engine_config(folder, name, dtype=dtype, decode_run_steps=run_steps))
         try:
             # stop tokens: whatever the first request produces as its 6th token ends it there
@@ -94,5 +94,45 @@ def test_decode_runs_give_the_tokens_of_single_steps(dtype, model_folders):
                 assert engine.steps_run > steps          # some calls ran several decode steps
         finally:
             engine.close()
-    assert results[1] == results[4]
+    assert results[1] == results[4] == results[32]
     assert results[1][0][1] == "stop" and len(results[1][0][0]) <= 6
+
+
+def test_a_request_cancelled_while_a_run_is_in_flight_leaves_the_others_alone(model_folders):
+    """Steps of a run are launched ahead of the ones read: a cancel between two calls ends the run
+    after what was launched, the other requests get the tokens they get without it, and every page
+    comes back."""
+    from tinyvllm_b200 import GenerateRequest, SamplingParams
+    from tinyvllm_b200.engine.engine import Engine
+
+    name, dtype = "e", "bfloat16"
+    config = TINY_CONFIGS[name]
+    folder = model_folders[name]
+    prompts = [random_tokens(config.vocab_size, n, 700 + n) for n in (11, 30, 5)]
+    sampling = SamplingParams(max_new_tokens=40, ignore_eos=True)
+    engine = Engine.from_config(engine_config(folder, name, dtype=dtype, decode_run_steps=1))
+    try:
+        alone = engine.generate([GenerateRequest(tuple(p), sampling) for p in prompts])
+    finally:
+        engine.close()
+    engine = Engine.from_config(engine_config(folder, name, dtype=dtype, decode_run_steps=32))
+    try:
+        ids = [engine.submit(p, sampling) for p in prompts]
+        outputs, calls, cancelled_at = {}, 0, None
+        while engine.has_unfinished():
+            if engine._run is not None and cancelled_at is None and calls >= 6:
+                assert engine.cancel(ids[1])
+                cancelled_at = calls
+            for done in engine.step().finished:
+                outputs[done.request_id] = done
+            calls += 1
+        assert cancelled_at is not None and engine._run is None
+        assert outputs[ids[1]].finish_reason == "cancelled"
+        cut = list(outputs[ids[1]].output_token_ids)
+        assert 0 < len(cut) < 40 and cut == list(alone[1].output_token_ids)[:len(cut)]
+        for i in (0, 2):
+            assert list(outputs[ids[i]].output_token_ids) == list(alone[i].output_token_ids)
+        engine.runner.manager.check()
+        assert all(pool.free_count == pool.num_pages for pool in engine.runner.manager.pools)
+    finally:
+        engine.close()

@@ -315,3 +315,84 @@ def test_runs_and_single_steps_produce_the_same_requests():
         for rid in outputs[0]:
             a, b = outputs[0][rid], outputs[1][rid]
             assert a[1] == b[1] and len(a[0]) == len(b[0]), (seed, rid, a, b)
+
+
+def test_a_run_read_step_by_step_keeps_ended_requests_pages_until_it_ends():
+    """begin_run / commit_run_step / end_run: the tokens of commit_run, but a request that ends
+    inside the run (stop token, cancel) keeps its pages while later steps may still write them."""
+    scheduler, cache = make(pages=32, page_size=4, seqs=3, eos=(9,))
+    scheduler.add(request(0, 6, new=20))
+    scheduler.add(request(1, 3, new=20, ignore_eos=True))
+    scheduler.add(request(2, 5, new=20))
+    run_step(scheduler)
+    run = scheduler.schedule_decode_run(4)
+    assert run.steps == 4
+    scheduler.begin_run(run)
+    with pytest.raises(RuntimeError, match="in flight"):
+        scheduler.schedule()
+    with pytest.raises(RuntimeError, match="in flight"):
+        scheduler.schedule_decode_run(4)
+    pages_of_0 = cache.block_table(0, 0)
+    free = cache.free_pages(0)
+    assert scheduler.commit_run_step(run, {0: 5, 1: 9, 2: 4}) == [(0, 5), (1, 9), (2, 4)]
+    assert scheduler.commit_run_step(run, {0: 9, 1: 9, 2: 4}) == [(0, 9), (1, 9), (2, 4)]     # request 0 stops here
+    assert scheduler.decoding == [1, 2] and run.closing == [0]
+    assert cache.is_open(0) and cache.block_table(0, 0) == pages_of_0 and cache.free_pages(0) == free
+    assert scheduler.cancel(2)                                       # cancelled while the run is in flight
+    assert run.closing == [0, 2] and cache.is_open(2)
+    done = scheduler.take_finished()                                 # reported at once all the same
+    assert sorted((r.request_id, r.finish_reason) for r in done) == [(0, "stop"), (2, "cancelled")]
+    assert scheduler.commit_run_step(run, {0: 1, 1: 9, 2: 1}) == [(1, 9)]                     # a third step was launched
+    scheduler.end_run(run)                                           # the fourth never was
+    cache.check()
+    assert not cache.is_open(0) and not cache.is_open(2) and cache.is_open(1)
+    assert cache.length(1) == 3 + 3 and scheduler.requests[1].computed_tokens == 6
+    assert len(cache.block_table(1, 0)) == 2                         # 6 tokens: the page taken for the 7th went back
+    assert cache.free_pages(0) == 32 - 2
+    assert scheduler.run_in_flight is None
+    step, _ = run_step(scheduler)
+    assert [i.request_id for i in step.items] == [1]
+    with pytest.raises(RuntimeError):
+        scheduler.commit_run_step(run, {1: 1})
+
+
+def test_runs_read_step_by_step_and_cut_short_produce_the_same_requests():
+    """Random workloads drained with runs that are read step by step and cut short at random,
+    against single steps: same lengths and reasons, no page lost."""
+    for seed in range(8):
+        outputs = []
+        for streamed in (False, True):
+            rng = random.Random(seed)
+            cut = random.Random(seed + 100)
+            scheduler, cache = make(pages=40, page_size=4, seqs=3, budget=24, chunk=8, max_len=64, eos=(7,),
+                                    window=6 if seed % 2 else None)
+            for rid in range(6):
+                scheduler.add(request(rid, rng.randrange(1, 20), new=rng.randrange(1, 12)))
+            counters = {}
+
+            def token_of(rid):
+                counters[rid] = counters.get(rid, 0) + 1
+                return (rid * 31 + counters[rid] * 5) % 11          # sometimes the stop token 7
+
+            guard = 0
+            while scheduler.has_unfinished():
+                run = scheduler.schedule_decode_run(6) if streamed else None
+                if run is not None:
+                    scheduler.begin_run(run)
+                    launched = cut.randrange(1, run.steps + 1)
+                    for _ in range(launched):
+                        live = [i.request_id for i in run.items
+                                if i.request_id in scheduler.requests and not scheduler.requests[i.request_id].status.terminal]
+                        tokens = {i.request_id: 0 for i in run.items}
+                        tokens.update({rid: token_of(rid) for rid in live})
+                        scheduler.commit_run_step(run, tokens)
+                    scheduler.end_run(run)
+                else:
+                    run_step(scheduler, token_of)
+                cache.check()
+                guard += 1
+                assert guard < 1000
+            outputs.append({r.request_id: (tuple(r.output_token_ids), r.finish_reason)
+                            for r in scheduler.take_finished()})
+            assert all(pool.free_count == pool.num_pages for pool in cache.pools)
+        assert outputs[0] == outputs[1], seed

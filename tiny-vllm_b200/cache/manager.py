@@ -276,16 +276,28 @@ class CacheManager:
                 request.length == 0, tuple(slots), tuple(tables)))
         return StepCachePlan(tuple(entries), taken)
 
-    def commit(self, plan: StepCachePlan) -> None:
-        """The step ran: lengths advance, windows let go of what they passed."""
+    def commit(self, plan: StepCachePlan, written: int | None = None) -> None:
+        """The step ran: lengths advance, windows let go of what they passed.  ``written``: every
+        entry wrote only its first ``written`` tokens (a run of decode steps that was cut short);
+        the pages taken for the rest go back."""
         if plan.state != "planned":
             raise CacheError(f"the plan is already {plan.state}")
+        if written is not None and not (type(written) is int and 0 <= written
+                                        and all(written <= entry.count for entry in plan.entries)):
+            raise CacheError("an entry cannot have written more tokens than were planned for it")
         plan.state = "committed"
         size = self.page_size
         for entry in plan.entries:
             request = self._requests[entry.request_id]
             request.planned = False
-            request.length = entry.start + entry.count
+            request.length = entry.start + (entry.count if written is None else written)
+            if written is not None and written < entry.count:
+                for group, table in enumerate(request.tables):
+                    keep = ceil_div(request.length, size)
+                    extra = table[keep:]
+                    if extra:
+                        del table[keep:]
+                        self.pools[group].give([p for p in reversed(extra) if p >= 0], entry.request_id)
             for group, table in enumerate(request.tables):
                 first = self.first_needed(group, request.length)
                 passed = [i for i in range(min(len(table), first // size)) if table[i] >= 0]

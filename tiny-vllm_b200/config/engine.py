@@ -3,7 +3,8 @@
 Field names, defaults and checks follow tinyvllm/config.py:15-92 where the
 reference has them.  Added: ``dtype="float32"`` (a true 32-bit path),
 ``weights``/``seed`` (random weights instead of a checkpoint), ``graph_batch_sizes``,
-``decode_run_steps`` (decode steps the engine runs back to back before it looks at their tokens).
+``decode_run_steps`` (decode steps the engine plans at once and launches ahead of the one whose
+tokens it reads; 1: every step is planned, run and read by itself).
 Dropped: ``attention_backend`` (there is one backend), ``enable_prefix_caching``
 (not built), float16.
 """
@@ -48,7 +49,7 @@ class EngineConfig:
     graph_batch_sizes: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
     # While nothing waits, up to this many decode steps run back to back, each fed the step before's
     # tokens on the device; the host reads their tokens together afterwards.  1: one step a time.
-    decode_run_steps: int = 4
+    decode_run_steps: int = 32
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

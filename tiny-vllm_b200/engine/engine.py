@@ -98,6 +98,7 @@ class Engine:
         self._failed: str | None = None
         self.steps_run = 0
         self.graph_steps = 0
+        self._run = None            # (scheduled run, run in flight on the graphs, request ids) between calls
 
     # ---------------------------------------------------------- construction
     @classmethod
@@ -177,11 +178,14 @@ class Engine:
     def step(self) -> StepEvents:
         """Run one step of whatever the scheduler picks; tokens and finished requests."""
         self._check_usable()
+        if self._run is not None:
+            return self._continue_run()
         now = self._clock()
         if self.decode_run_steps > 1 and self.graphs.bucket_for(len(self.scheduler.decoding)) is not None:
             run = self.scheduler.schedule_decode_run(self.decode_run_steps, now)
             if run is not None:
-                return self._step_run(run)
+                self._start_run(run)
+                return self._continue_run()
         scheduled = self.scheduler.schedule(now)
         if scheduled is None:
             return StepEvents((), tuple(RequestOutput.of(r) for r in self.scheduler.take_finished()))
@@ -197,25 +201,61 @@ class Engine:
         finished = tuple(RequestOutput.of(r) for r in self.scheduler.take_finished())
         return StepEvents(tuple(events), finished)
 
-    def _step_run(self, run) -> StepEvents:
-        """Several decode steps back to back (see DecodeGraphs.run_many); their tokens in step order."""
+    # A run of decode steps is planned at once and read step by step: a call of step() launches
+    # steps until RUN_AHEAD of them are not read yet, waits for the oldest and returns its tokens,
+    # so the GPU works on the next step while the caller has this one.  The run ends early when a
+    # request of it ends or a newcomer waits (what was launched is still read and counted); the
+    # pages of requests that ended inside it go back when it ends.
+    RUN_AHEAD = 2
+
+    def _start_run(self, run) -> None:
         requests = self.scheduler.requests
         ids = [item.request_id for item in run.items]
         try:
             first = [requests[i].tokens(item.start, item.start + 1)[0] for i, item in zip(ids, run.items)]
             params = [requests[i].sampling for i in ids]
             draws = [len(requests[i].output_token_ids) for i in ids]
-            rows = self.graphs.run_many(run.cache_plan, first, params, draws, run.steps)
-            kernels.check_finished_launches()
-            events = self.scheduler.commit_run(run, [dict(zip(ids, row)) for row in rows], self._clock())
+            flight = self.graphs.start_run(run.cache_plan, first, params, draws, run.steps)
+            if flight is None:
+                raise RuntimeError("no decode graph holds the rows of the run")
+            self.scheduler.begin_run(run)
         except BaseException as exc:
             self._failed = repr(exc)
             if run.cache_plan.state == "planned":
                 self.scheduler.cache.rollback(run.cache_plan)
             raise
-        self.steps_run += run.steps
-        self.graph_steps += run.steps
-        finished = tuple(RequestOutput.of(r) for r in self.scheduler.take_finished())
+        self._run = (run, flight, ids)
+
+    def _continue_run(self) -> StepEvents:
+        run, flight, ids = self._run
+        scheduler = self.scheduler
+        events: list = []
+        try:
+            def must_stop() -> bool:
+                return bool(run.closing or scheduler.waiting or scheduler.prefilling)
+
+            def read_one() -> None:
+                tokens = flight.read()
+                kernels.check_finished_launches()
+                events.extend(scheduler.commit_run_step(run, dict(zip(ids, tokens)), self._clock()))
+                self.steps_run += 1
+                self.graph_steps += 1
+
+            while flight.launched < run.steps and not must_stop() and flight.launched < flight.read_steps + self.RUN_AHEAD:
+                flight.launch()
+            if flight.read_steps < flight.launched:
+                read_one()
+            if flight.launched == run.steps or must_stop():
+                while flight.read_steps < flight.launched:       # what was launched ahead still counts
+                    read_one()
+                scheduler.end_run(run)
+                if flight.launched < run.steps:
+                    self.graphs.forget_tables(flight.bucket)
+                self._run = None
+        except BaseException as exc:
+            self._failed = repr(exc)
+            raise
+        finished = tuple(RequestOutput.of(r) for r in scheduler.take_finished())
         return StepEvents(tuple(events), finished)
 
     @torch.inference_mode()
@@ -266,5 +306,8 @@ class Engine:
         return [outputs[i] for i in ids]
 
     def close(self) -> None:
+        if self._run is not None:                  # steps in flight still write to the cache
+            torch.cuda.synchronize()
+            self._run = None
         self._closed = True
         self.graphs = None

@@ -200,35 +200,79 @@ class DecodeGraphs:
         return bucket.tokens[:rows], bucket.logits[:rows]
 
     @torch.inference_mode()
-    def run_many(self, plan, first_tokens, params, draws, steps: int) -> list[list[int]] | None:
+    def start_run(self, plan, first_tokens, params, draws, steps: int) -> "RunInFlight | None":
         """``steps`` decode steps of the same requests back to back: the plan holds ``steps`` tokens
         per request, step i runs its i-th.  The tokens a step samples are the next step's input on
         the device (the host only uploads positions, slots and sampling arguments, which it knows
-        in advance) and are copied to pinned memory after every step; the host waits once, at the
-        end, so its work for step i + 1 runs while the GPU is at step i.  Returns the tokens
-        [steps][rows], or None if no graph holds the rows."""
+        in advance) and are copied to pinned memory after every step.  The caller launches steps
+        (:meth:`RunInFlight.launch`) ahead of the ones it reads (:meth:`RunInFlight.read`), so the
+        GPU does not wait for the host between two steps, nor between the last step the host has
+        seen and the next.  None if no graph holds the rows."""
         rows = len(first_tokens)
         bucket = self.bucket_for(rows)
         if bucket is None:
             return None
-        planned = plan.entries
-        self.runner.storage.clear_state([p.state_slot for p in planned if p.fresh_state])
+        self.runner.storage.clear_state([p.state_slot for p in plan.entries if p.fresh_state])
         if bucket.history is None or bucket.history.shape[0] < steps:
             bucket.history = torch.zeros((steps, bucket.size), dtype=torch.int32, pin_memory=True)
-        ids_end = int(bucket.offsets[1])
-        for index in range(steps):
-            self._fill(bucket, planned, rows, first_tokens if index == 0 else None, index, params,
-                       [d + index for d in draws])
-            if index == 0:
-                bucket.device.copy_(bucket.host, non_blocking=True)
-            else:
-                bucket.device_view(0).copy_(bucket.tokens, non_blocking=True)
-                bucket.device[ids_end:].copy_(bucket.host[ids_end:], non_blocking=True)
-            bucket.copied = torch.cuda.Event()
-            bucket.copied.record()
-            bucket.graph.replay()
-            bucket.history[index].copy_(bucket.tokens, non_blocking=True)
+        return RunInFlight(self, bucket, plan.entries, rows, list(first_tokens), list(params), list(draws), steps)
+
+    def run_many(self, plan, first_tokens, params, draws, steps: int) -> list[list[int]] | None:
+        """All steps of a run launched, then all read: the tokens [steps][rows], or None if no
+        graph holds the rows."""
+        run = self.start_run(plan, first_tokens, params, draws, steps)
+        if run is None:
+            return None
+        for _ in range(steps):
+            run.launch()
+        return [run.read() for _ in range(steps)]
+
+    def forget_tables(self, bucket: _Bucket) -> None:
+        """The next step uploads every row's block table whole (after a run that was cut short,
+        whose last pages went back and may come again in another order)."""
+        for known in bucket.row_tables:
+            for r in range(len(known)):
+                known[r] = None
+
+
+class RunInFlight:
+    """A run of decode steps on one bucket's graph: ``launch`` enqueues the next step, ``read``
+    waits for the oldest step not read yet and returns its tokens."""
+
+    def __init__(self, graphs: DecodeGraphs, bucket: _Bucket, planned, rows: int, first_tokens, params, draws,
+                 steps: int) -> None:
+        self.graphs, self.bucket, self.planned, self.rows = graphs, bucket, planned, rows
+        self.first_tokens, self.params, self.draws, self.steps = first_tokens, params, draws, steps
+        self.launched = 0
+        self.read_steps = 0
+        self.done: list[torch.cuda.Event] = []
+
+    @torch.inference_mode()
+    def launch(self) -> None:
+        if self.launched >= self.steps:
+            raise RuntimeError("every step of the run has been launched")
+        bucket, index = self.bucket, self.launched
+        self.graphs._fill(bucket, self.planned, self.rows, self.first_tokens if index == 0 else None, index,
+                          self.params, [d + index for d in self.draws])
+        if index == 0:
+            bucket.device.copy_(bucket.host, non_blocking=True)
+        else:
+            ids_end = int(bucket.offsets[1])
+            bucket.device_view(0).copy_(bucket.tokens, non_blocking=True)
+            bucket.device[ids_end:].copy_(bucket.host[ids_end:], non_blocking=True)
+        bucket.copied = torch.cuda.Event()
+        bucket.copied.record()
+        bucket.graph.replay()
+        bucket.history[index].copy_(bucket.tokens, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
-        done.synchronize()
-        return bucket.history[:steps, :rows].tolist()
+        self.done.append(done)
+        self.launched += 1
+
+    def read(self) -> list[int]:
+        if self.read_steps >= self.launched:
+            raise RuntimeError("no launched step is left to read")
+        self.done[self.read_steps].synchronize()
+        tokens = self.bucket.history[self.read_steps, :self.rows].tolist()
+        self.read_steps += 1
+        return tokens

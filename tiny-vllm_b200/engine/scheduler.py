@@ -104,6 +104,9 @@ class ScheduledRun:
     items: tuple[WorkItem, ...]
     cache_plan: StepCachePlan
     steps: int
+    # while the run is read step by step (begin_run .. end_run):
+    steps_read: int = 0
+    closing: list = field(default_factory=list)      # requests that ended meanwhile; their pages go back at the end
 
 
 class Scheduler:
@@ -129,6 +132,7 @@ class Scheduler:
         self.prefilling: list[int] = []
         self.decoding: list[int] = []
         self.finished: list[Request] = []
+        self.run_in_flight: ScheduledRun | None = None
         self._prefer_waiting = False
 
     # -------------------------------------------------------------- demand
@@ -221,6 +225,8 @@ class Scheduler:
 
     def schedule(self, now_ns: int = 0) -> ScheduledStep | None:
         """The next step, with its pages taken; None when there is nothing to run."""
+        if self.run_in_flight is not None:
+            raise RuntimeError("a run of decode steps is in flight: end it before the next step is planned")
         admitted = self._admit(now_ns)
         active_prefills = list(self.prefilling)
         candidates = (admitted + active_prefills) if self._prefer_waiting else (active_prefills + admitted)
@@ -283,6 +289,8 @@ class Scheduler:
         run), and only as many steps as every request may still take: none reaches its token limit
         or the context limit before the run's last step.  A request that meets a stop token inside
         the run ends there; what the run computed for it beyond is dropped with its pages."""
+        if self.run_in_flight is not None:
+            raise RuntimeError("a run of decode steps is in flight: end it before the next is planned")
         if max_steps < 2 or not self.decoding or self.waiting or self.prefilling:
             return None
         if len(self.decoding) > min(self.max_num_seqs, self.max_num_batched_tokens):
@@ -293,12 +301,14 @@ class Scheduler:
             steps = min(steps, request.remaining_new_tokens, self.max_model_len - request.total_tokens)
         if steps < 2:
             return None
-        items = tuple(WorkItem(request_id, self.requests[request_id].computed_tokens, steps, True)
-                      for request_id in self.decoding)
-        plan = self.cache.plan([(item.request_id, item.count) for item in items])
-        if plan is None:
-            return None
-        return ScheduledRun(items, plan, steps)
+        while steps >= 2:                    # a shorter run if the pool has no pages for the whole one
+            items = tuple(WorkItem(request_id, self.requests[request_id].computed_tokens, steps, True)
+                          for request_id in self.decoding)
+            plan = self.cache.plan([(item.request_id, item.count) for item in items])
+            if plan is not None:
+                return ScheduledRun(items, plan, steps)
+            steps //= 2
+        return None
 
     def commit_run(self, run: ScheduledRun, sampled: Sequence[dict[int, int]], now_ns: int = 0) -> list[tuple[int, int]]:
         """The run ran.  ``sampled[i]`` maps request id to the token of the run's i-th step.
@@ -326,6 +336,52 @@ class Scheduler:
                 elif request.remaining_new_tokens <= 0 or request.total_tokens >= self.max_model_len:
                     self._finish(request, "length", now_ns)
         return events
+
+    # A run can also be read step by step while its later steps still execute: begin_run, then
+    # commit_run_step for every step that ran (in order), then end_run.  A request that ends at a
+    # step (stop token, limit, cancel) leaves the queues at once, but keeps its pages until
+    # end_run: steps launched ahead may still write to them.
+    def begin_run(self, run: ScheduledRun) -> None:
+        if self.run_in_flight is not None:
+            raise RuntimeError("a run of decode steps is already in flight")
+        self.run_in_flight = run
+
+    def commit_run_step(self, run: ScheduledRun, tokens: dict[int, int], now_ns: int = 0) -> list[tuple[int, int]]:
+        """The run's next step ran; ``tokens`` maps request id to its token.  Returns (request id,
+        token) of the requests that had not ended before."""
+        if run is not self.run_in_flight or run.steps_read >= run.steps:
+            raise RuntimeError("no such step of a run in flight")
+        for item in run.items:
+            if item.request_id not in tokens:
+                raise ValueError(f"no token was sampled for request {item.request_id}")
+        index = run.steps_read
+        run.steps_read += 1
+        events = []
+        for item in run.items:
+            request = self.requests.get(item.request_id)
+            if request is None or request.status.terminal:       # ended earlier in this run, or cancelled
+                continue
+            request.computed_tokens = item.start + index + 1
+            token = int(tokens[item.request_id])
+            request.output_token_ids.append(token)
+            events.append((item.request_id, token))
+            if token in self.eos_token_ids and not request.sampling.ignore_eos:
+                self._finish(request, "stop", now_ns)
+            elif request.remaining_new_tokens <= 0 or request.total_tokens >= self.max_model_len:
+                self._finish(request, "length", now_ns)
+        return events
+
+    def end_run(self, run: ScheduledRun) -> None:
+        """Every launched step of the run has been read (``run.steps_read`` of them): the cache
+        keeps what they wrote, the rest of the plan and the pages of ended requests go back."""
+        if run is not self.run_in_flight:
+            raise RuntimeError("the run is not in flight")
+        self.run_in_flight = None
+        self.cache.commit(run.cache_plan, written=run.steps_read)
+        for request_id in run.closing:
+            if self.cache.is_open(request_id):
+                self.cache.close(request_id)
+        run.closing.clear()
 
     # ------------------------------------------------------------- results
     def abort_step(self, step: ScheduledStep) -> None:
@@ -367,7 +423,11 @@ class Scheduler:
             if request_id in queue:
                 queue.remove(request_id)
         if self.cache.is_open(request_id):
-            self.cache.close(request_id)
+            run = self.run_in_flight
+            if run is not None and any(item.request_id == request_id for item in run.items):
+                run.closing.append(request_id)           # steps launched ahead may still write its pages
+            else:
+                self.cache.close(request_id)
         request.status = RequestStatus.ABORTED if reason == "cancelled" else RequestStatus.FINISHED
         request.finish_reason = reason
         request.finished_ns = now_ns
