@@ -59,6 +59,28 @@ def test_plan_commit_tables_and_slots():
     m.check()
 
 
+def test_commit_of_what_was_written_gives_the_rest_back():
+    """A plan for several tokens per request (a run of decode steps) that ended early."""
+    m = manager(pages=12, page_size=4)
+    m.open("a"), m.open("b")
+    m.commit(m.plan([("a", 7), ("b", 2)]))
+    plan = m.plan([("a", 6), ("b", 6)])              # a: 7..12 (two more pages), b: 2..7 (one more)
+    assert m.free_pages(0) == 12 - 4 - 2
+    kept = m.block_table("a", 0)[:3]
+    with pytest.raises(CacheError, match="more tokens than were planned"):
+        m.commit(plan, written=7)
+    m.commit(plan, written=2)                        # a: 9 tokens = 3 pages, b: 4 tokens = 1 page
+    assert m.length("a") == 9 and m.length("b") == 4
+    assert m.block_table("a", 0) == kept and len(m.block_table("b", 0)) == 1
+    assert m.free_pages(0) == 12 - 3 - 1
+    m.check()
+    m.commit(m.plan([("a", 1), ("b", 1)]))           # and on it goes
+    assert m.length("a") == 10 and len(m.block_table("b", 0)) == 2
+    m.close("a"), m.close("b")
+    m.check()
+    assert m.free_pages(0) == 12
+
+
 def test_all_or_nothing_and_rollback():
     m = manager(pages=4, page_size=4)
     m.open("a"), m.open("b")
@@ -168,6 +190,16 @@ def test_random_orders_keep_every_page_accounted_for(seed):
             elif rng.random() < 0.15:
                 m.rollback(plan)
                 assert [m.free_pages(g) for g in range(2)] == free_before
+            elif rng.random() < 0.2:
+                # a run of steps cut short: every entry wrote only its first tokens
+                written = rng.randrange(0, min(count for _, count in appends) + 1)
+                m.commit(plan, written=written)
+                for rid, _ in appends:
+                    live[rid] += written
+                    assert m.length(rid) == live[rid]
+                    assert len(m.block_table(rid, 0)) == -(-live[rid] // m.page_size)
+                if written == 0:
+                    assert [m.free_pages(g) for g in range(2)] == free_before
             else:
                 for entry in plan.entries:
                     for table in entry.tables:
