@@ -123,7 +123,9 @@ def run_reference(model_dir: Path, config: Qwen3Config, workload: dict):
 
 
 def main() -> None:
-    reference_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py /path/to/tiny-vLLM")
+    reference_root = Path(sys.argv[1])
     sys.path.insert(0, str(reference_root))
     install_cpu_pointwise()
     for name, workload in GOLDEN_WORKLOADS.items():
