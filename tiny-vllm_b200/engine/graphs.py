@@ -121,6 +121,9 @@ class DecodeGraphs:
             with torch.cuda.graph(graph, pool=self._pool, stream=stream):
                 bucket.logits = self.runner.model.forward(ctx)
                 sample_packed(bucket.logits, packed, out=bucket.tokens)
+                # the sampled tokens are the next step's input where the host does not upload others
+                # (inside a run of steps)
+                bucket.device_view(0).copy_(bucket.tokens)
             bucket.launches = kernels.launch_count() - launched
             if self._pool is None:
                 self._pool = graph.pool()
@@ -257,8 +260,7 @@ class RunInFlight:
         if index == 0:
             bucket.device.copy_(bucket.host, non_blocking=True)
         else:
-            ids_end = int(bucket.offsets[1])
-            bucket.device_view(0).copy_(bucket.tokens, non_blocking=True)
+            ids_end = int(bucket.offsets[1])            # the token ids are there: the graph left them
             bucket.device[ids_end:].copy_(bucket.host[ids_end:], non_blocking=True)
         bucket.copied = torch.cuda.Event()
         bucket.copied.record()
