@@ -136,3 +136,37 @@ def test_a_request_cancelled_while_a_run_is_in_flight_leaves_the_others_alone(mo
         assert all(pool.free_count == pool.num_pages for pool in engine.runner.manager.pools)
     finally:
         engine.close()
+
+
+def test_streamed_tokens_are_the_generated_ones(model_folders, capsys):
+    """LLM.stream yields every token as it comes and the outputs of generate; the command line
+    prints them with --stream."""
+    import json
+
+    from tinyvllm_b200 import LLM, SamplingParams
+    from tinyvllm_b200.__main__ import main
+
+    name = "b"
+    folder = model_folders[name]
+    prompts = [random_tokens(TINY_CONFIGS[name].vocab_size, n, 900 + n) for n in (4, 31)]
+    sampling = SamplingParams(max_new_tokens=12, ignore_eos=True)
+    with LLM(engine_config(folder, name)) as llm:
+        want = [list(o.output_token_ids) for o in llm.generate(prompts, sampling)]
+        tokens, outputs = {0: [], 1: []}, {}
+        for index, item in llm.stream(prompts, sampling):
+            if isinstance(item, int):
+                assert index not in outputs                      # tokens come before the request's output
+                tokens[index].append(item)
+            else:
+                outputs[index] = item
+        assert [tokens[0], tokens[1]] == want
+        assert [list(outputs[i].output_token_ids) for i in (0, 1)] == want
+    main(["--model", str(folder), "--dtype", "float32", "--max-new-tokens", "12", "--ignore-eos", "--stream",
+          "--kv-block-size", str(PAGE_SIZES[name]), "--kv-cache-mib", "16", "--max-model-len", "512",
+          "--prompt-ids", ",".join(map(str, prompts[0])), "--prompt-ids", ",".join(map(str, prompts[1]))])
+    lines = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    streamed = {0: [], 1: []}
+    for line in lines[:-1]:
+        streamed[line["prompt"]].append(line["token_id"])
+    assert [streamed[0], streamed[1]] == want
+    assert [record["output_token_ids"] for record in lines[-1]["outputs"]] == want

@@ -4,10 +4,11 @@ Option names, meanings and defaults are those of ``python -m tinyvllm``
 (tinyvllm/__main__.py:58-163) where the engine has the feature: --model,
 --prompt (repeatable), --dtype, --max-new-tokens, --temperature, --top-k,
 --top-p, --seed, --ignore-eos, --enforce-eager, --max-model-len, --max-num-seqs,
---max-num-batched-tokens, --prefill-chunk-size, --kv-cache-mib; prefill
-reservations are zero as there (:137-138).  Added: --prompt-ids (token ids, the
-engine's native input), --random-weights SEED, --kv-block-size, float32 as a
-dtype.  Not offered: chat, streaming, attention backends, prefix caching.
+--max-num-batched-tokens, --prefill-chunk-size, --kv-cache-mib, --stream (here:
+one JSON line per token id as it comes; the reference streams the text of one
+prompt); prefill reservations are zero as there (:137-138).  Added: --prompt-ids
+(token ids, the engine's native input), --random-weights SEED, --kv-block-size,
+float32 as a dtype.  Not offered: chat, attention backends, prefix caching.
 Prints one JSON object ``{"outputs": [...]}`` (:155-163).
 """
 
@@ -57,6 +58,8 @@ def main(argv=None) -> None:
                         help="Per-request prefill query-token limit per engine step")
     parser.add_argument("--kv-cache-mib", type=int, default=512)
     parser.add_argument("--kv-block-size", type=int, default=16)
+    parser.add_argument("--stream", action="store_true",
+                        help="print every token id as it is generated, one JSON object a line, before the outputs")
     parser.add_argument("--random-weights", type=int, metavar="SEED", default=None,
                         help="ignore model.safetensors and draw the weights from this seed")
     args = parser.parse_args(argv)
@@ -75,7 +78,16 @@ def main(argv=None) -> None:
         seed=args.random_weights or 0)
     prompts = args.prompt if args.prompt is not None else args.prompt_ids
     with LLM(config) as llm:
-        outputs = llm.generate(prompts, sampling)
+        if args.stream:
+            # one line per token as it comes, then the outputs as without the flag
+            outputs = [None] * len(prompts)
+            for index, item in llm.stream(prompts, sampling):
+                if isinstance(item, int):
+                    print(json.dumps({"prompt": index, "token_id": item}), flush=True)
+                else:
+                    outputs[index] = item
+        else:
+            outputs = llm.generate(prompts, sampling)
     records = [{**asdict(output), "completion_token_count": output.completion_token_count,
                 "total_token_count": output.total_token_count} for output in outputs]
     print(json.dumps({"outputs": records}, ensure_ascii=False))

@@ -91,6 +91,31 @@ class LLM:
                                       output.prompt_token_count, output.finish_reason))
         return results
 
+    def stream(self, prompts, sampling: SamplingParams | None = None):
+        """Like :meth:`generate`, but a generator: yields (index of the prompt, token id) as the
+        tokens come (after every decode step) and, when a request has ended, (index, TextOutput).
+        The engine has to be idle."""
+        engine = self.engine
+        sampling = SamplingParams() if sampling is None else sampling
+        if not isinstance(sampling, SamplingParams):
+            raise TypeError("sampling must be SamplingParams")
+        if engine.has_unfinished():
+            raise RuntimeError("stream() needs an idle engine")
+        if isinstance(prompts, str) or (isinstance(prompts, Sequence) and prompts
+                                        and isinstance(prompts[0], int)):
+            prompts = (prompts,)
+        token_batches = [self._encode(prompt) for prompt in prompts]
+        index_of = {engine.submit(tokens, sampling): index for index, tokens in enumerate(token_batches)}
+        while engine.has_unfinished() or index_of:
+            events = engine.step()
+            for request_id, token in events.tokens:
+                yield index_of[request_id], token
+            for output in events.finished:
+                text = self.tokenizer.decode(output.output_token_ids) if self.tokenizer is not None else ""
+                yield index_of.pop(output.request_id), TextOutput(
+                    output.request_id, text, output.output_token_ids, output.prompt_token_count,
+                    output.finish_reason)
+
     def close(self) -> None:
         if self._engine is not None:
             self._engine.close()
