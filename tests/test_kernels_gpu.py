@@ -621,7 +621,7 @@ def test_gemm_small_m_with_norm_prologue(shape, weight_dtype):
 
 @pytest.mark.parametrize("weight_dtype", [torch.float32, torch.bfloat16], ids=["w32", "w16"])
 @pytest.mark.parametrize("shape", [(8, 1024, 512, 3072), (1, 256, 48, 96), (13, 1000, 264, 40), (16, 2048, 1000, 64),
-                                   (27, 320, 72, 130)])
+                                   (27, 320, 72, 130), (5, 512, 2048, 96), (9, 128, 5120, 48)])
 def test_gemm_small_m_adds_to_the_stream_and_the_next_product_norms_it(shape, weight_dtype):
     """Two products with a pre-norm between them and no norm kernel: the first adds its result to
     the residual stream and stores the rows' sums of squares tile by tile, the second normalises
