@@ -10,7 +10,8 @@ one decode step of a batch of 8 requests whose contexts start at 2,048 tokens
 * ``e2e``: the same through the public token-level API (``Engine.submit`` /
   ``Engine.step``), which every step uploads the step's inputs from pinned host
   memory and copies the sampled tokens back to pinned host memory (the engine
-  runs up to four decode steps back to back and looks at their tokens together).
+  plans up to 32 decode steps at once, keeps two launched ahead of the one it
+  reads, and a call of ``step`` returns the tokens of one of them).
 * ``prefill``: one prompt of 2,048 tokens through the step function.
 * ``roofline``: bytes a decode step must read (every weight once + the cache of the
   live requests) / time / measured HBM bandwidth.
@@ -150,8 +151,19 @@ def random_prompt(rng: random.Random, count: int) -> list[int]:
 
 
 def new_tokens_of(steps: int, warmup: int) -> int:
-    """Tokens a request of the decode measurement may generate (a call of step() runs up to four)."""
-    return steps + 5 * warmup + 32
+    """Tokens a request of the decode measurement may generate: the warm-up and the timed steps of
+    either measurement, and room for the steps a run has launched ahead when it is cut off."""
+    return steps + warmup + 64
+
+
+def clear_engine(engine) -> None:
+    """Cancel whatever the engine holds and let a run in flight end, so that every page is back."""
+    scheduler = engine.scheduler
+    for request_id in list(scheduler.waiting) + list(scheduler.prefilling) + list(scheduler.decoding):
+        engine.cancel(request_id)
+    while engine.in_run:                # the steps launched ahead are read; the run's pages go back
+        engine.step()
+    scheduler.take_finished()
 
 
 def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloat16", eager: bool = False,
@@ -202,9 +214,7 @@ def run_decode(engine, batch: int, steps: int, warmup: int, sampler: ClockSample
 
     def fresh_batch():
         """``batch`` requests with their prompts in the cache, about to decode their second token."""
-        for request_id in list(engine.scheduler.decoding):
-            engine.cancel(request_id)
-        engine.scheduler.take_finished()
+        clear_engine(engine)
         for _ in range(batch):
             engine.submit(random_prompt(rng, PROMPT_TOKENS), sampling)
         while engine.scheduler.prefilling or engine.scheduler.waiting:      # untimed prefill
@@ -270,9 +280,7 @@ def run_decode(engine, batch: int, steps: int, warmup: int, sampler: ClockSample
     clocks = sampler.summary(mark, sampler.mark()) if sampler else None
     device_ms = start.elapsed_time(end)
     assert kernels.launch_count() == launches_before      # everything ran from the graph
-    for request_id in list(scheduler.decoding):
-        engine.cancel(request_id)
-    engine.scheduler.take_finished()
+    clear_engine(engine)
     return {
         "tokens_per_s": batch * steps / (device_ms / 1e3), "ms_per_step": device_ms / steps,
         "e2e_tokens_per_s": batch * e2e_steps / (e2e_ms / 1e3), "h2d": h2d_bytes, "d2h": d2h_bytes,
@@ -324,8 +332,7 @@ def eager_profile(args, warmup: int) -> int:
         for _ in range(warmup + args.steps):
             engine.step()
         torch.cuda.synchronize()
-        for request_id in list(engine.scheduler.decoding):
-            engine.cancel(request_id)
+        clear_engine(engine)
         print("eager profile run: ok", run_prefill(engine, repeats=1), "ms prefill")
     return 0
 

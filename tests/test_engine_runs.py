@@ -5,6 +5,8 @@ newcomer, a stop token or a cancel) can be compared with one step at a time."""
 
 import random
 
+import pytest
+
 from tinyvllm_b200.cache.manager import CacheGroup, CacheManager
 from tinyvllm_b200.engine.engine import Engine
 from tinyvllm_b200.engine.scheduler import Scheduler
@@ -35,12 +37,26 @@ class StandInRunner:
     def __init__(self, manager):
         self.manager = manager
         self.calls = 0
+        self.fail_prepare = 0           # so many calls of prepare raise
+        self.fail_launch = False
 
-    def forward(self, entries, plan):
+    def prepare(self, entries, plan):              # the host half: nothing runs yet
+        if self.fail_prepare:
+            self.fail_prepare -= 1
+            raise RuntimeError("lowering failed")
+        return entries, plan
+
+    def launch(self, prepared):                    # the device half
+        entries, plan = prepared
+        if self.fail_launch:
+            raise RuntimeError("the model failed")
         self.calls += 1
         by_id = {p.request_id: p for p in plan.entries}
         rows = [token_at(e.request_id, by_id[e.request_id].start + len(e.tokens) - 1) for e in entries if e.want]
         return Tokens(rows) if rows else None
+
+    def forward(self, entries, plan):
+        return self.launch(self.prepare(entries, plan))
 
 
 class StandInSampler:
@@ -54,6 +70,8 @@ class StandInFlight:
         self.launched = self.read_steps = 0
         self.bucket = object()
 
+    fail_read_at = None                 # the read of this step raises
+
     def launch(self):
         assert self.launched < self.steps
         self.launched += 1
@@ -61,6 +79,8 @@ class StandInFlight:
 
     def read(self):
         assert self.read_steps < self.launched
+        if self.fail_read_at == self.read_steps:
+            raise RuntimeError("the device did not answer")
         tokens = [token_at(p.request_id, p.start + self.read_steps) for p in self.planned]
         self.read_steps += 1
         return tokens
@@ -75,7 +95,7 @@ class StandInGraphs:
     def bucket_for(self, rows):
         return object() if 0 < rows <= self.largest else None
 
-    def run(self, plan, entries, params, draws):
+    def prepare(self, plan, entries, params, draws):
         return None                     # single steps take the eager path of the stand-in runner
 
     def start_run(self, plan, first_tokens, params, draws, steps):
@@ -86,12 +106,12 @@ class StandInGraphs:
         self.forgotten += 1
 
 
-def make_engine(run_steps, pages=64, seqs=4):
+def make_engine(run_steps, pages=64, seqs=4, **engine_arguments):
     cache = CacheManager([CacheGroup((0,), 1, 16, None)], 4, pages, seqs)
     scheduler = Scheduler(cache, max_num_seqs=seqs, max_num_batched_tokens=32, prefill_chunk_size=16,
                           max_model_len=96, eos_token_ids=(STOP,))
     graphs = StandInGraphs()
-    engine = Engine(StandInRunner(cache), scheduler, graphs=graphs, decode_run_steps=run_steps)
+    engine = Engine(StandInRunner(cache), scheduler, graphs=graphs, decode_run_steps=run_steps, **engine_arguments)
     engine.sampler = StandInSampler()
     return engine, cache, graphs
 
@@ -182,3 +202,146 @@ def test_a_newcomer_and_a_cancel_end_a_run_after_what_was_launched():
         engine.step()
     cache.check()
     assert all(pool.free_count == pool.num_pages for pool in cache.pools)
+
+
+# ---------------------------------------------------------------- failures (made on the host)
+def all_pages_free(cache) -> bool:
+    cache.check()
+    return all(pool.free_count == pool.num_pages for pool in cache.pools)
+
+
+def test_a_failure_while_lowering_gives_the_pages_back_and_the_engine_goes_on():
+    """Nothing of the step was launched (tinyvllm/engine.py:354-365): the plan is rolled back, the
+    requests keep their places, the next call runs them."""
+    engine, cache, _ = make_engine(1)
+    engine.submit(list(range(1, 20)), SamplingParams(max_new_tokens=4, ignore_eos=True), request_id=0)
+    engine.runner.fail_prepare = 1
+    with pytest.raises(RuntimeError, match="lowering failed"):
+        engine.step()
+    cache.check()
+    assert cache.is_open(0) and cache.length(0) == 0 and cache.block_table(0, 0) == ()
+    assert engine._failed is None
+    outputs = {}
+    while engine.has_unfinished():
+        for done in engine.step().finished:
+            outputs[done.request_id] = done
+    assert outputs[0].finish_reason == "length" and len(outputs[0].output_token_ids) == 4
+    # the same tokens as an engine that never failed
+    other, _, _ = make_engine(1)
+    other.submit(list(range(1, 20)), SamplingParams(max_new_tokens=4, ignore_eos=True), request_id=0)
+    expected = {}
+    while other.has_unfinished():
+        for done in other.step().finished:
+            expected[done.request_id] = done
+    assert outputs[0].output_token_ids == expected[0].output_token_ids
+    assert all_pages_free(cache)
+
+
+def test_a_failure_after_launch_stops_the_engine_and_loses_no_page():
+    """The model raised (tinyvllm/engine.py:367-387, :543-564): fail-stop."""
+    engine, cache, _ = make_engine(1)
+    engine.submit([1, 2, 3], SamplingParams(max_new_tokens=8, ignore_eos=True), request_id=0)
+    engine.step()
+    engine.submit([4] * 9, SamplingParams(max_new_tokens=8, ignore_eos=True), request_id=1)
+    engine.runner.fail_launch = True
+    with pytest.raises(RuntimeError, match="the model failed"):
+        engine.step()
+    assert engine._failed is not None and "the model failed" in engine._failed
+    assert all_pages_free(cache) and cache.open_requests() == ()
+    for call in (engine.step, lambda: engine.submit([1], None), lambda: engine.cancel(0),
+                 lambda: engine.generate([])):
+        with pytest.raises(RuntimeError, match="stopped after a failed step"):
+            call()
+
+
+def test_a_failed_read_inside_a_run_stops_the_engine_and_loses_no_page():
+    engine, cache, graphs = make_engine(32)
+    engine.submit([1, 2, 3], SamplingParams(max_new_tokens=60, ignore_eos=True), request_id=0)
+    engine.submit([4, 5], SamplingParams(max_new_tokens=60, ignore_eos=True), request_id=1)
+    engine.step()
+    engine.step()                                    # the run starts
+    _, flight, _ = engine._run
+    flight.fail_read_at = 2
+    engine.step()
+    with pytest.raises(RuntimeError, match="did not answer"):
+        engine.step()
+    assert engine._failed is not None and engine._run is None and engine.scheduler.run_in_flight is None
+    assert all_pages_free(cache) and cache.open_requests() == ()
+    with pytest.raises(RuntimeError, match="stopped after a failed step"):
+        engine.step()
+
+
+def test_a_run_that_cannot_start_is_rolled_back():
+    engine, cache, graphs = make_engine(32)
+    engine.submit([1, 2, 3], SamplingParams(max_new_tokens=60, ignore_eos=True), request_id=0)
+    engine.step()
+    held = len(cache.block_table(0, 0))
+
+    def refuse(*arguments):
+        raise RuntimeError("no pinned memory")
+
+    graphs.start_run, start_run = refuse, graphs.start_run
+    with pytest.raises(RuntimeError, match="no pinned memory"):
+        engine.step()
+    cache.check()
+    assert engine._failed is None and len(cache.block_table(0, 0)) == held
+    graphs.start_run = start_run
+    while engine.has_unfinished():
+        engine.step()
+    assert all_pages_free(cache)
+
+
+# ------------------------------------------------------------------- arrivals and the clock
+class Clock:
+    def __init__(self):
+        self.now = 0
+        self.slept = []
+
+    def __call__(self):
+        return self.now
+
+    def sleep(self, seconds):
+        self.slept.append(seconds)
+        self.now += int(round(seconds * 1e9))
+
+
+def test_requests_take_part_from_their_arrival_time_on():
+    clock = Clock()
+    engine, cache, _ = make_engine(1, clock=clock, sleep=clock.sleep)
+    ms = 1_000_000
+    for rid in range(4):                             # 20 ms apart, submitted all at once
+        engine.submit([rid + 1] * 5, SamplingParams(max_new_tokens=3, ignore_eos=True), request_id=rid,
+                      arrival_ns=rid * 20 * ms)
+    assert engine.scheduler.next_arrival_ns == 20 * ms
+    first = engine.step(now_ns=0)
+    assert [rid for rid, _ in first.tokens] == [0]
+    assert engine.scheduler.requests[1].status.value == "pending"
+    events = engine.step(now_ns=20 * ms)
+    with pytest.raises(ValueError, match="backwards"):
+        engine.step(now_ns=19 * ms)
+    assert sorted(rid for rid, _ in events.tokens) == [0, 1]
+    assert engine.cancel(3) and engine.scheduler.next_arrival_ns == 40 * ms
+    done = {}
+    now = 20 * ms
+    while engine.has_unfinished():
+        now += 10 * ms
+        for output in engine.step(now_ns=now).finished:
+            done[output.request_id] = output
+    assert sorted(done) == [0, 1, 2, 3] and done[3].finish_reason == "cancelled"
+    assert done[2].admitted_ns >= 40 * ms and done[2].arrival_ns == 40 * ms
+    assert done[1].first_token_ns == 20 * ms
+    assert all_pages_free(cache)
+
+
+def test_generate_sleeps_until_the_next_arrival():
+    from tinyvllm_b200.engine.engine import GenerateRequest
+
+    clock = Clock()
+    engine, cache, _ = make_engine(1, clock=clock, sleep=clock.sleep)
+    sampling = SamplingParams(max_new_tokens=2, ignore_eos=True)
+    outputs = engine.generate([GenerateRequest((1, 2, 3), sampling, arrival_ns=0),
+                               GenerateRequest((4, 5), sampling, arrival_ns=50_000_000)])
+    assert [len(o.output_token_ids) for o in outputs] == [2, 2]
+    assert clock.slept and abs(sum(clock.slept) - 0.05) < 1e-9      # idle once, until the second arrived
+    assert outputs[1].admitted_ns >= 50_000_000
+    assert all_pages_free(cache)

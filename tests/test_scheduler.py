@@ -396,3 +396,69 @@ def test_runs_read_step_by_step_and_cut_short_produce_the_same_requests():
                             for r in scheduler.take_finished()})
             assert all(pool.free_count == pool.num_pages for pool in cache.pools)
         assert outputs[0] == outputs[1], seed
+
+
+# ------------------------------------------------------------------------- arrivals
+def arriving(rid, prompt_len, at, new=2):
+    made = request(rid, prompt_len, new=new)
+    made.arrival_ns = at
+    return made
+
+
+def test_requests_ahead_of_the_clock_are_kept_aside_and_join_in_time_order():
+    scheduler, cache = make()
+    scheduler.add(arriving(0, 3, at=300), now_ns=0)
+    scheduler.add(arriving(1, 3, at=100), now_ns=0)
+    scheduler.add(arriving(2, 3, at=100), now_ns=0)           # same time: the one submitted first goes first
+    scheduler.add(arriving(3, 3, at=0), now_ns=0)             # already there
+    assert list(scheduler.waiting) == [3] and scheduler.next_arrival_ns == 100
+    assert scheduler.requests[0].status is RequestStatus.PENDING and scheduler.has_unfinished()
+    assert scheduler.schedule(0).items[0].request_id == 3
+    assert scheduler.advance(99) == 0 and scheduler.advance(100) == 2
+    assert list(scheduler.waiting) == [1, 2] and scheduler.next_arrival_ns == 300
+    assert scheduler.cancel(0, 150) and scheduler.next_arrival_ns is None
+    assert scheduler.advance(1000) == 0                        # the cancelled one never joins
+    with pytest.raises(ValueError, match="backwards"):
+        scheduler.advance(999)
+    finished = {r.request_id: r for r in scheduler.take_finished()}
+    assert finished[0].finish_reason == "cancelled" and finished[0].status is RequestStatus.ABORTED
+    cache.check()
+
+
+def test_a_request_that_can_generate_nothing_ends_when_it_arrives():
+    scheduler, _ = make()
+    scheduler.add(arriving(0, 3, at=50, new=0), now_ns=0)
+    assert scheduler.take_finished() == [] and scheduler.has_unfinished()
+    scheduler.advance(60)
+    done = scheduler.take_finished()
+    assert [r.finish_reason for r in done] == ["length"] and done[0].finished_ns == 60
+    assert not scheduler.has_unfinished()
+
+
+def test_shutdown_gives_everything_back_and_refuses_more_work():
+    scheduler, cache = make()
+    scheduler.add(request(0, 9, new=6))
+    scheduler.add(request(1, 5, new=6))
+    run_step(scheduler)
+    scheduler.add(arriving(2, 3, at=10**9), now_ns=0)
+    step = scheduler.schedule()                                 # an open plan
+    scheduler.shutdown(step.cache_plan)
+    cache.check()
+    assert cache.open_requests() == () and all(p.free_count == p.num_pages for p in cache.pools)
+    assert not scheduler.has_unfinished() and scheduler.stopped
+    with pytest.raises(RuntimeError, match="shut down"):
+        scheduler.schedule()
+    with pytest.raises(RuntimeError, match="shut down"):
+        scheduler.add(request(5, 2))
+
+
+def test_two_requests_with_one_id_differ_in_their_opening():
+    _, cache = make()
+    cache.open("a")
+    first = cache.plan([("a", 3)])
+    cache.commit(first)
+    cache.close("a")
+    cache.open("a")
+    second = cache.plan([("a", 3)])
+    assert first.entries[0].request_id == second.entries[0].request_id
+    assert first.entries[0].opening != second.entries[0].opening

@@ -127,6 +127,7 @@ class _Request:
     length: int = 0                                   # tokens whose keys are written
     tables: list[list[int]] = field(default_factory=list)   # per group, -1 = given back
     planned: bool = False
+    opening: int = 0                                  # which call of open() made it (ids may come again)
 
 
 @dataclass(frozen=True)
@@ -141,6 +142,8 @@ class PlannedEntry:
     slots: tuple[tuple[int, ...], ...]        # per group: cache slot of each new token
     tables: tuple                             # per group: the request's block table (the live list:
                                               # read it before the step is committed, do not change it)
+    opening: int = 0                          # number of the open() that admitted the request: two
+                                              # requests with one id, one after the other, differ in it
 
 
 @dataclass
@@ -163,6 +166,7 @@ class CacheManager:
         self.pools = [PagePool(count) for count in pages_per_group]
         self.slots = SlotPool(num_state_slots)
         self._requests: dict[object, _Request] = {}
+        self._openings = 0
 
     # ------------------------------------------------------------ requests
     def open(self, request_id) -> int:
@@ -172,7 +176,8 @@ class CacheManager:
         slot = self.slots.take()
         if slot is None:
             raise CacheError("no state slot is free")
-        self._requests[request_id] = _Request(slot, 0, [[] for _ in self.groups])
+        self._openings += 1
+        self._requests[request_id] = _Request(slot, 0, [[] for _ in self.groups], False, self._openings)
         return slot
 
     def close(self, request_id) -> None:
@@ -273,7 +278,7 @@ class CacheManager:
             request.planned = True
             entries.append(PlannedEntry(
                 request_id, request.length, count, request.state_slot,
-                request.length == 0, tuple(slots), tuple(tables)))
+                request.length == 0, tuple(slots), tuple(tables), request.opening))
         return StepCachePlan(tuple(entries), taken)
 
     def commit(self, plan: StepCachePlan, written: int | None = None) -> None:

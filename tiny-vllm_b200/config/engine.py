@@ -17,16 +17,20 @@ from pathlib import Path
 from typing import Literal
 
 DTYPES = ("bfloat16", "float32")
+WEIGHT_MODES = ("checkpoint", "random")
+
+# field -> smallest value it may take; all of these are plain ints (bool is not an int here)
+_INT_FIELDS = {
+    "max_model_len": 1, "max_num_seqs": 1, "max_num_batched_tokens": 1, "prefill_chunk_size": 1,
+    "kv_block_size": 1, "kv_cache_memory_bytes": 1, "decode_run_steps": 1,
+    "prefill_reserve_tokens": 0, "prefill_reserve_requests": 0, "seed": 0,
+}
 
 
-def _positive_int(name: str, value) -> None:
-    if type(value) is not int or value <= 0:
-        raise ValueError(f"{name} must be a positive integer, got {value!r}")
-
-
-def _non_negative_int(name: str, value) -> None:
-    if type(value) is not int or value < 0:
-        raise ValueError(f"{name} must be a non-negative integer, got {value!r}")
+def _int_at_least(name: str, value, least: int) -> None:
+    if type(value) is not int or value < least:
+        kind = "a positive integer" if least == 1 else f"an integer of at least {least}"
+        raise ValueError(f"{name} must be {kind}, got {value!r}")
 
 
 @dataclass(frozen=True)
@@ -53,40 +57,50 @@ class EngineConfig:
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:
-        model = Path(self.model).expanduser().resolve()
-        object.__setattr__(self, "model", model)
-        if not model.is_dir():
-            raise ValueError(f"model directory does not exist: {model}")
-        if self.dtype not in DTYPES:
-            raise ValueError(f"unsupported dtype: {self.dtype}")
-        if self.weights not in ("checkpoint", "random"):
-            raise ValueError(f"unsupported weights mode: {self.weights}")
-        if type(self.enforce_eager) is not bool:
-            raise TypeError("enforce_eager must be bool")
-        for name in ("max_model_len", "max_num_seqs", "max_num_batched_tokens",
-                     "prefill_chunk_size", "kv_block_size", "kv_cache_memory_bytes", "decode_run_steps"):
-            _positive_int(name, getattr(self, name))
-        for name in ("prefill_reserve_tokens", "prefill_reserve_requests", "seed"):
-            _non_negative_int(name, getattr(self, name))
+        folder = Path(self.model).expanduser().resolve()
+        if not folder.is_dir():
+            raise ValueError(f"the model folder {folder} does not exist")
+        object.__setattr__(self, "model", folder)
+        self._check_choices()
+        for name, least in _INT_FIELDS.items():
+            _int_at_least(name, getattr(self, name), least)
         sizes = tuple(self.graph_batch_sizes)
         for size in sizes:
-            _positive_int("graph_batch_sizes entry", size)
+            _int_at_least("graph_batch_sizes entry", size, 1)
         object.__setattr__(self, "graph_batch_sizes", tuple(sorted(set(sizes))))
+        self._check_memory_share()
+        self._check_step_budget()
 
-        utilization = self.gpu_memory_utilization
-        if type(utilization) not in (int, float):
+    def _check_choices(self) -> None:
+        if self.dtype not in DTYPES:
+            raise ValueError(f"dtype is one of {', '.join(DTYPES)}, not {self.dtype!r}")
+        if self.weights not in WEIGHT_MODES:
+            raise ValueError(f"weights is one of {', '.join(WEIGHT_MODES)}, not {self.weights!r}")
+        if type(self.enforce_eager) is not bool:
+            raise TypeError("enforce_eager must be bool")
+
+    def _check_memory_share(self) -> None:
+        share = self.gpu_memory_utilization
+        if isinstance(share, bool) or not isinstance(share, (int, float)):
             raise TypeError("gpu_memory_utilization must be a number")
-        if not math.isfinite(utilization) or not 0.0 < utilization < 1.0:
-            raise ValueError("gpu_memory_utilization must be between 0 and 1")
+        if not (math.isfinite(share) and 0.0 < share < 1.0):
+            raise ValueError(f"gpu_memory_utilization must lie between 0 and 1 (both excluded), got {share}")
 
-        tokens, requests = self.prefill_reserve_tokens, self.prefill_reserve_requests
-        if (tokens == 0) != (requests == 0):
-            raise ValueError("prefill reservations must both be zero or both positive")
-        if not tokens < self.max_num_batched_tokens:
-            raise ValueError("prefill token reservation leaves no decode capacity")
-        if not requests < self.max_num_seqs:
-            raise ValueError("prefill request reservation leaves no decode capacity")
-        if tokens < requests:
-            raise ValueError("each reserved prefill request needs one token")
+    def _check_step_budget(self) -> None:
+        """A step holds up to max_num_batched_tokens tokens of up to max_num_seqs requests.  While
+        requests decode, part of that room may be kept for prompt portions: so many tokens for so
+        many requests.  The part kept must leave room to decode, and a portion must fit a step."""
+        kept_tokens, kept_requests = self.prefill_reserve_tokens, self.prefill_reserve_requests
+        if bool(kept_tokens) != bool(kept_requests):
+            raise ValueError("prefill_reserve_tokens and prefill_reserve_requests are both zero or both "
+                             f"positive (got {kept_tokens} and {kept_requests})")
+        if kept_tokens < kept_requests:
+            raise ValueError(f"{kept_requests} requests cannot share {kept_tokens} kept tokens: "
+                             "each needs at least one")
+        if kept_tokens >= self.max_num_batched_tokens or kept_requests >= self.max_num_seqs:
+            raise ValueError(
+                f"keeping {kept_tokens} tokens and {kept_requests} requests of a step for prefills leaves "
+                f"nothing of its {self.max_num_batched_tokens} tokens or {self.max_num_seqs} requests to decode with")
         if self.prefill_chunk_size > self.max_num_batched_tokens:
-            raise ValueError("prefill chunk exceeds the step token budget")
+            raise ValueError(f"prefill_chunk_size={self.prefill_chunk_size}: a prompt portion (chunk) does not "
+                             f"fit into a step of {self.max_num_batched_tokens} tokens")

@@ -6,8 +6,13 @@ returns an engine; ``submit``/``step``/``generate``/``cancel``/``close`` are the
 token-level API.  Start-up follows tinyvllm/bootstrap.py:59-208 (KV sizing
 :19-56, :109-145), the step follows tinyvllm/engine.py:303-387 and
 tinyvllm/executor.py:125-141: plan, lower, run, sample, one device-to-host read
-of the sampled ids, commit.  A failure after the pages of a step are taken
-stops the engine for good (fail-stop, tinyvllm/engine.py:367-387, :543-564).
+of the sampled ids, commit.  A step fails in one of two ways
+(tinyvllm/engine.py:354-387, :543-564): while it is lowered on the host, before
+anything of it was launched, its pages go back and the engine stays usable;
+once it has been launched, the engine stops for good (fail-stop): every request
+is dropped with its pages and later calls are refused.  Requests may carry an
+arrival time ahead of the clock and ``step`` may be told the time
+(tinyvllm/engine.py:179-256, :303-306, :426-435).
 """
 
 from __future__ import annotations
@@ -37,6 +42,7 @@ class GenerateRequest:
     prompt_token_ids: tuple[int, ...]
     sampling: SamplingParams
     request_id: int | None = None
+    arrival_ns: int | None = None         # None: it arrives when it is submitted
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "prompt_token_ids", tuple(self.prompt_token_ids))
@@ -84,18 +90,42 @@ def plan_pages(kv_cache_memory_bytes: int, bytes_per_page: int, free_bytes: int,
     return pages
 
 
+def check_memory_ceiling(used_bytes: int, total_bytes: int, utilization: float) -> None:
+    """After everything is set up (cache, graphs and their pools, library work areas): the device
+    must not hold more than its allowed share (tinyvllm/bootstrap.py:171-185)."""
+    allowed = int(total_bytes * utilization)
+    if used_bytes > allowed:
+        raise ValueError(
+            f"the engine holds {used_bytes} bytes of the device after start-up, more than the {allowed} "
+            f"that gpu_memory_utilization={utilization} allows: lower kv_cache_memory_bytes, set "
+            "enforce_eager, or free device memory")
+
+
+@dataclass
+class _LoweredStep:
+    """A scheduled step after its host half: what the device half needs."""
+
+    sample_ids: list
+    params: list
+    draws: list
+    bucket: object = None                 # (bucket, rows) of a decode graph, or
+    prepared: object = None               # a PreparedStep of the step runner
+
+
 class Engine:
     def __init__(self, runner: StepRunner, scheduler: Scheduler, *, graphs: DecodeGraphs | None = None,
-                 clock=time.monotonic_ns, decode_run_steps: int = 1) -> None:
+                 clock=time.monotonic_ns, decode_run_steps: int = 1, sleep=time.sleep) -> None:
         self.runner = runner
         self.scheduler = scheduler
         self.graphs = graphs
         self.decode_run_steps = decode_run_steps if graphs is not None else 1
         self.sampler = Sampler()
         self._clock = clock
+        self._sleep = sleep
         self._next_id = 0
         self._closed = False
         self._failed: str | None = None
+        self._last_now: int | None = None
         self.steps_run = 0
         self.graph_steps = 0
         self._run = None            # (scheduled run, run in flight on the graphs, request ids) between calls
@@ -140,6 +170,11 @@ class Engine:
                 graphs = DecodeGraphs(runner, sizes, max_model_len=config.max_model_len)
                 graphs.capture()
                 runner.enable_step_graphs()       # prefill and mixed steps whose shape comes back
+            # graph pools and library work areas exist now: measure again
+            torch.cuda.synchronize(device)
+            torch.cuda.empty_cache()
+            free, total = torch.cuda.mem_get_info(device)
+            check_memory_ceiling(total - free, total, config.gpu_memory_utilization)
         log.info("engine ready: %s, %s, %d pages of %d tokens per group, %.1f MiB of weights",
                  spec.architecture, config.dtype, pages, config.kv_block_size,
                  model.weight_bytes() / 2**20)
@@ -153,7 +188,9 @@ class Engine:
             raise RuntimeError(f"the engine stopped after a failed step: {self._failed}")
 
     def submit(self, prompt_token_ids: Sequence[int], sampling: SamplingParams | None = None,
-               *, request_id: int | None = None) -> int:
+               *, request_id: int | None = None, arrival_ns: int | None = None) -> int:
+        """Hand a request to the engine.  With ``arrival_ns`` ahead of the clock it is kept aside
+        and takes part from the first step whose time is at or past it."""
         self._check_usable()
         sampling = sampling if sampling is not None else SamplingParams()
         prompt = tuple(prompt_token_ids)
@@ -162,44 +199,87 @@ class Engine:
                 raise ValueError(f"{token!r} is not a token id below {self.runner.vocab_size}")
         if request_id is None:
             request_id = self._next_id
+        if type(request_id) is not int or request_id < 0:
+            raise ValueError("request_id must be a non-negative int")
+        now = self._now(None)
+        if arrival_ns is None:
+            arrival_ns = now
+        elif type(arrival_ns) is not int or arrival_ns < 0:
+            raise ValueError("arrival_ns must be a non-negative int")
+        self.scheduler.add(Request(request_id, prompt, sampling, arrival_ns=arrival_ns), now)
         self._next_id = max(self._next_id, request_id + 1)
-        now = self._clock()
-        self.scheduler.add(Request(request_id, prompt, sampling, arrival_ns=now), now)
         return request_id
 
     def cancel(self, request_id: int) -> bool:
         self._check_usable()
-        return self.scheduler.cancel(request_id, self._clock())
+        return self.scheduler.cancel(request_id, self._now(None))
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
 
+    @property
+    def in_run(self) -> bool:
+        """Whether a run of decode steps is in flight (its remaining steps are read by ``step``)."""
+        return self._run is not None
+
+    def _now(self, now_ns: int | None) -> int:
+        """The time of a call: the caller's, else the clock's, never earlier than the last one the
+        scheduler was told (a caller that passes times drives the clock alone)."""
+        if now_ns is None:
+            now_ns = self._clock()
+            if self._last_now is not None:
+                now_ns = max(now_ns, self._last_now)
+        elif type(now_ns) is not int or now_ns < 0:
+            raise ValueError("now_ns must be a non-negative int")
+        self._last_now = now_ns
+        return now_ns
+
     # ----------------------------------------------------------------- step
-    def step(self) -> StepEvents:
-        """Run one step of whatever the scheduler picks; tokens and finished requests."""
+    def step(self, now_ns: int | None = None) -> StepEvents:
+        """Run one step of whatever the scheduler picks; tokens and finished requests.  ``now_ns``
+        sets the time of the step (arrivals up to it take part, timestamps read it); without it the
+        engine's clock is read."""
         self._check_usable()
+        now = self._now(now_ns)
+        explicit = now_ns is not None
+        self.scheduler.advance(now)
         if self._run is not None:
-            return self._continue_run()
-        now = self._clock()
+            return self._continue_run(now if explicit else None)
         if self.decode_run_steps > 1 and self.graphs.bucket_for(len(self.scheduler.decoding)) is not None:
             run = self.scheduler.schedule_decode_run(self.decode_run_steps, now)
             if run is not None:
                 self._start_run(run)
-                return self._continue_run()
+                return self._continue_run(now if explicit else None)
         scheduled = self.scheduler.schedule(now)
         if scheduled is None:
             return StepEvents((), tuple(RequestOutput.of(r) for r in self.scheduler.take_finished()))
         try:
-            sampled = self._execute(scheduled)
-            events = self.scheduler.commit(scheduled, sampled, self._clock())
+            lowered = self._lower(scheduled)
+        except BaseException:
+            # nothing of the step was launched: its pages go back, the requests keep their places
+            # and the next call plans them again
+            self.scheduler.abort_step(scheduled)
+            raise
+        try:
+            sampled = self._launch(scheduled, lowered)
+            events = self.scheduler.commit(scheduled, sampled, now if explicit else self._now(None))
         except BaseException as exc:
-            self._failed = repr(exc)
-            if scheduled.cache_plan.state == "planned":
-                self.scheduler.abort_step(scheduled)
+            self._fail_stop(exc, scheduled.cache_plan)
             raise
         self.steps_run += 1
         finished = tuple(RequestOutput.of(r) for r in self.scheduler.take_finished())
         return StepEvents(tuple(events), finished)
+
+    def _fail_stop(self, cause: BaseException, open_plan=None) -> None:
+        """A step failed after it was launched: what it left in the cache cannot be trusted.  The
+        engine keeps the reason as text (not the exception: its traceback would hold tensors), drops
+        every request with its pages and refuses all later calls."""
+        self._failed = f"{type(cause).__name__}: {cause}"
+        self._run = None
+        try:
+            self.scheduler.shutdown(open_plan)
+        except BaseException as cleanup:          # noqa: BLE001 (the first failure is the one reported)
+            cause.add_note(f"giving the cache back failed too: {cleanup!r}")
 
     # A run of decode steps is planned at once and read step by step: a call of step() launches
     # steps until RUN_AHEAD of them are not read yet, waits for the oldest and returns its tokens,
@@ -218,15 +298,15 @@ class Engine:
             flight = self.graphs.start_run(run.cache_plan, first, params, draws, run.steps)
             if flight is None:
                 raise RuntimeError("no decode graph holds the rows of the run")
-            self.scheduler.begin_run(run)
-        except BaseException as exc:
-            self._failed = repr(exc)
+        except BaseException:
+            # host work only so far: the plan goes back and the engine stays usable
             if run.cache_plan.state == "planned":
                 self.scheduler.cache.rollback(run.cache_plan)
             raise
+        self.scheduler.begin_run(run)
         self._run = (run, flight, ids)
 
-    def _continue_run(self) -> StepEvents:
+    def _continue_run(self, fixed_now: int | None = None) -> StepEvents:
         run, flight, ids = self._run
         scheduler = self.scheduler
         events: list = []
@@ -237,7 +317,8 @@ class Engine:
             def read_one() -> None:
                 tokens = flight.read()
                 kernels.check_finished_launches()
-                events.extend(scheduler.commit_run_step(run, dict(zip(ids, tokens)), self._clock()))
+                when = fixed_now if fixed_now is not None else self._now(None)
+                events.extend(scheduler.commit_run_step(run, dict(zip(ids, tokens)), when))
                 self.steps_run += 1
                 self.graph_steps += 1
 
@@ -253,13 +334,15 @@ class Engine:
                     self.graphs.forget_tables(flight.bucket)
                 self._run = None
         except BaseException as exc:
-            self._failed = repr(exc)
+            self._fail_stop(exc)
             raise
         finished = tuple(RequestOutput.of(r) for r in scheduler.take_finished())
         return StepEvents(tuple(events), finished)
 
     @torch.inference_mode()
-    def _execute(self, scheduled: ScheduledStep) -> dict[int, int]:
+    def _lower(self, scheduled: ScheduledStep) -> _LoweredStep:
+        """The host half of a step: entries from the requests' tokens, sampling arguments, and the
+        step's fields lowered into pinned memory (of a decode graph if one holds the step)."""
         requests = self.scheduler.requests
         entries, params, draws, sample_ids = [], [], [], []
         for item in scheduled.items:
@@ -270,30 +353,40 @@ class Engine:
                 params.append(request.sampling)
                 draws.append(len(request.output_token_ids))
                 sample_ids.append(item.request_id)
+        lowered = _LoweredStep(sample_ids, params, draws)
         decode_only = all(item.count == 1 and item.sample for item in scheduled.items)
-        tokens_device = None
         if decode_only and self.graphs is not None:
-            replayed = self.graphs.run(scheduled.cache_plan, entries, params, draws)
-            if replayed is not None:
-                tokens_device = replayed[0]
-                self.graph_steps += 1
-        if tokens_device is None:
-            logits = self.runner.forward(entries, scheduled.cache_plan)
+            lowered.bucket = self.graphs.prepare(scheduled.cache_plan, entries, params, draws)
+        if lowered.bucket is None:
+            lowered.prepared = self.runner.prepare(entries, scheduled.cache_plan)
+        return lowered
+
+    @torch.inference_mode()
+    def _launch(self, scheduled: ScheduledStep, lowered: _LoweredStep) -> dict[int, int]:
+        """The device half: run the step, sample, read the tokens (the step's one device-to-host read)."""
+        tokens_device = None
+        if lowered.bucket is not None:
+            tokens_device = self.graphs.launch(lowered.bucket, scheduled.cache_plan)[0]
+            self.graph_steps += 1
+        else:
+            logits = self.runner.launch(lowered.prepared)
             if logits is not None:
-                tokens_device = self.sampler.sample(logits, params, draws)
+                tokens_device = self.sampler.sample(logits, lowered.params, lowered.draws)
         if tokens_device is None:
             return {}
-        host = tokens_device.tolist()              # the step's one device-to-host read
+        host = tokens_device.tolist()
         kernels.check_finished_launches()
-        return dict(zip(sample_ids, host))
+        return dict(zip(lowered.sample_ids, host))
 
     # ------------------------------------------------------------- generate
     def generate(self, requests: Sequence[GenerateRequest]) -> list[RequestOutput]:
-        """Run ``requests`` to the end; outputs in the order given."""
+        """Run ``requests`` to the end; outputs in the order given.  While nothing can run because
+        every request left arrives later, the engine sleeps until the next arrival."""
         self._check_usable()
         if self.has_unfinished():
             raise RuntimeError("generate() needs an idle engine")
-        ids = [self.submit(r.prompt_token_ids, r.sampling, request_id=r.request_id) for r in requests]
+        ids = [self.submit(r.prompt_token_ids, r.sampling, request_id=r.request_id, arrival_ns=r.arrival_ns)
+               for r in requests]
         outputs: dict[int, RequestOutput] = {}
         while True:
             events = self.step()
@@ -303,6 +396,13 @@ class Engine:
                 for request in self.scheduler.take_finished():
                     outputs[request.request_id] = RequestOutput.of(request)
                 break
+            scheduler = self.scheduler
+            if not (events.tokens or scheduler.waiting or scheduler.prefilling or scheduler.decoding):
+                ahead = scheduler.next_arrival_ns
+                if ahead is not None:
+                    delay = (ahead - self._clock()) / 1e9
+                    if delay > 0:
+                        self._sleep(delay)
         return [outputs[i] for i in ids]
 
     def close(self) -> None:
@@ -311,3 +411,6 @@ class Engine:
             self._run = None
         self._closed = True
         self.graphs = None
+        drop = getattr(self.runner, "drop_graphs", None)
+        if drop is not None:
+            drop()

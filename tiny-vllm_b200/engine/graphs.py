@@ -20,6 +20,7 @@ import torch
 from ..ops import attention as attention_ops
 from ..ops import kernels
 from ..sampling.sampler import ROW_WORDS, pack_rows, sample_packed
+from .capture import capture
 from .step import StepContext
 
 
@@ -44,7 +45,9 @@ class _Bucket:
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits = None
         self.launches = 0
-        # per group and row: (request, entries written, leading entries given back) of the last step
+        self.guarded = (False, False)     # kernels with bounded waits inside the graph (gemm_tc, attention_prefill_tc)
+        # per group and row: (request and the open() that admitted it, entries written, leading
+        # entries given back) of the last step
         self.row_tables = [[None] * size for _ in range(groups)]
         self.copied: torch.cuda.Event | None = None      # the last upload has left the pinned buffer
         self.history: torch.Tensor | None = None         # pinned [steps, size]: the tokens of a run's steps
@@ -101,10 +104,11 @@ class DecodeGraphs:
     def capture(self) -> None:
         """Capture every batch size (largest first, so the graphs share one memory pool)."""
         if self.split_chunks:
-            model = self.runner.model
-            heads = max((getattr(b.mixer, "num_heads", 0) * (getattr(b.mixer, "head_dim", 0) + 2))
-                        for b in model.blocks)
-            self.runner.reserve_workspace(self.largest * heads * self.split_chunks)
+            # scratch the blocks' kernels may ask for must exist before anything is recorded
+            need = max((block.scratch_floats(self.largest, self.split_chunks)
+                        for block in self.runner.model.blocks), default=0)
+            if need > 0:
+                self.runner.reserve_workspace(need)
         stream = torch.cuda.Stream(device=self.runner.device)
         for bucket in reversed(self.buckets):
             self._fill_padding(bucket)
@@ -118,13 +122,16 @@ class DecodeGraphs:
             stream.synchronize()
             graph = torch.cuda.CUDAGraph()
             launched = kernels.launch_count()
-            with torch.cuda.graph(graph, pool=self._pool, stream=stream):
+            guarded = kernels.guarded_launch_counts()
+            with capture(graph, pool=self._pool, stream=stream):
                 bucket.logits = self.runner.model.forward(ctx)
                 sample_packed(bucket.logits, packed, out=bucket.tokens)
                 # the sampled tokens are the next step's input where the host does not upload others
                 # (inside a run of steps)
                 bucket.device_view(0).copy_(bucket.tokens)
             bucket.launches = kernels.launch_count() - launched
+            now = kernels.guarded_launch_counts()
+            bucket.guarded = (now[0] > guarded[0], now[1] > guarded[1])
             if self._pool is None:
                 self._pool = graph.pool()
             bucket.graph = graph
@@ -169,7 +176,8 @@ class DecodeGraphs:
             for r, p in enumerate(planned):
                 table = p.tables[g]
                 before = known[r]
-                if before is None or before[0] != p.request_id or before[1] > len(table):
+                who = (p.request_id, p.opening)       # an id may come again for another request
+                if before is None or before[0] != who or before[1] > len(table):
                     tables[r, :len(table)] = table
                     first_live = 0
                 else:
@@ -179,28 +187,39 @@ class DecodeGraphs:
                 while first_live < len(table) and table[first_live] < 0:
                     tables[r, first_live] = -1
                     first_live += 1
-                known[r] = (p.request_id, len(table), first_live)
+                known[r] = (who, len(table), first_live)
             for r in range(rows, size):
                 known[r] = None
         packed = bucket.host_view(len(bucket.sizes) - 1).reshape(ROW_WORDS, size)
         packed[:] = pack_rows(params, draws, capacity=size)
 
-    @torch.inference_mode()
-    def run(self, plan, entries, params, draws) -> tuple[torch.Tensor, torch.Tensor] | None:
-        """Replay the graph for a step of single tokens; (tokens, logits) views of the first
-        ``len(entries)`` rows, valid until the next replay.  None if no graph holds the step."""
+    def prepare(self, plan, entries, params, draws) -> "tuple[_Bucket, int] | None":
+        """Lower a step of single tokens into the pinned buffer of the smallest graph that holds it
+        (host work only); None if no graph does."""
         rows = len(entries)
         bucket = self.bucket_for(rows)
         if bucket is None:
             return None
-        planned = plan.entries
-        self.runner.storage.clear_state([p.state_slot for p in planned if p.fresh_state])
-        self._fill(bucket, planned, rows, [entry.tokens[0] for entry in entries], 0, params, draws)
+        self._fill(bucket, plan.entries, rows, [entry.tokens[0] for entry in entries], 0, params, draws)
+        return bucket, rows
+
+    @torch.inference_mode()
+    def launch(self, prepared, plan) -> tuple[torch.Tensor, torch.Tensor]:
+        """Upload what :meth:`prepare` wrote and replay the graph: (tokens, logits) views of the
+        step's rows, valid until the next replay."""
+        bucket, rows = prepared
+        self.runner.storage.clear_state([p.state_slot for p in plan.entries if p.fresh_state])
         bucket.device.copy_(bucket.host, non_blocking=True)
         bucket.copied = torch.cuda.Event()
         bucket.copied.record()
         bucket.graph.replay()
+        kernels.note_guarded_launches(*bucket.guarded)
         return bucket.tokens[:rows], bucket.logits[:rows]
+
+    def run(self, plan, entries, params, draws) -> tuple[torch.Tensor, torch.Tensor] | None:
+        """:meth:`prepare` and :meth:`launch` in one call; None if no graph holds the step."""
+        prepared = self.prepare(plan, entries, params, draws)
+        return None if prepared is None else self.launch(prepared, plan)
 
     @torch.inference_mode()
     def start_run(self, plan, first_tokens, params, draws, steps: int) -> "RunInFlight | None":
@@ -265,6 +284,7 @@ class RunInFlight:
         bucket.copied = torch.cuda.Event()
         bucket.copied.record()
         bucket.graph.replay()
+        kernels.note_guarded_launches(*bucket.guarded)
         bucket.history[index].copy_(bucket.tokens, non_blocking=True)
         done = torch.cuda.Event()
         done.record()

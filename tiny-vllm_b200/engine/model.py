@@ -51,7 +51,7 @@ class Model:
 
     def cache_needs(self) -> list:
         """What each entry of the run list needs of the cache."""
-        return [self.blocks[step.layer].mixer.cache_need() for step in self.order]
+        return [self.blocks[step.layer].cache_need() for step in self.order]
 
     def cache_sources(self) -> list:
         return [step.cache_from for step in self.order]

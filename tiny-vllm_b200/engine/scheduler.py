@@ -1,6 +1,7 @@
 """Continuous batching with chunked prefill over the cache manager.
 
-Requests wait in arrival order, are admitted while a state slot is free and
+A request whose arrival time lies ahead is kept aside until the clock reaches it.
+Requests then wait in arrival order, are admitted while a state slot is free and
 their whole lifetime fits into the page pools, run as prompt portions under a
 token budget and then as single decoded tokens, and give everything back when
 they finish or are cancelled.
@@ -17,11 +18,14 @@ Policy and limits follow tinyvllm/scheduler.py: limits :92-150, up-front
 refusal :241-269, lifetime demand and skipping admission :758-866, decodes
 first :449-459, prefill reservation :427-447, portions :461-501 and :898-951,
 commit and finish reasons :617-699, cancel :954-1000, immediate finish
-:1058-1066.  The cache transaction is ``CacheManager.plan/commit/rollback``.
+:1058-1066, arrivals ahead of the clock :226-236 and :1045-1069, giving
+everything up after a failed step :702-729.  The cache transaction is
+``CacheManager.plan/commit/rollback``.
 """
 
 from __future__ import annotations
 
+import heapq
 from collections import deque
 from dataclasses import dataclass, field
 from enum import Enum
@@ -32,6 +36,7 @@ from ..sampling.params import SamplingParams
 
 
 class RequestStatus(Enum):
+    PENDING = "pending"          # its arrival time has not come yet
     WAITING = "waiting"
     RUNNING = "running"
     FINISHED = "finished"
@@ -114,9 +119,11 @@ class Scheduler:
                  prefill_chunk_size: int, max_model_len: int, prefill_reserve_tokens: int = 0,
                  prefill_reserve_requests: int = 0, eos_token_ids=()) -> None:
         if prefill_chunk_size > max_num_batched_tokens:
-            raise ValueError("prefill chunk exceeds the step token budget")
-        if (prefill_reserve_tokens == 0) != (prefill_reserve_requests == 0):
-            raise ValueError("prefill reservations must both be zero or both positive")
+            raise ValueError(f"a prompt portion of {prefill_chunk_size} tokens does not fit into a step "
+                             f"of {max_num_batched_tokens} tokens")
+        if bool(prefill_reserve_tokens) != bool(prefill_reserve_requests):
+            raise ValueError("room is kept for prefills either in tokens and in requests, or in neither "
+                             f"(got {prefill_reserve_tokens} tokens, {prefill_reserve_requests} requests)")
         if max_num_seqs > cache.slots.num_slots:
             raise ValueError("max_num_seqs exceeds the state slots of the cache")
         self.cache = cache
@@ -134,6 +141,10 @@ class Scheduler:
         self.finished: list[Request] = []
         self.run_in_flight: ScheduledRun | None = None
         self._prefer_waiting = False
+        self._ahead: list[tuple[int, int, int]] = []      # heap of (arrival_ns, order of submission, request id)
+        self._submitted = 0
+        self._now_ns: int | None = None
+        self.stopped = False                              # shutdown() was called: nothing is scheduled any more
 
     # -------------------------------------------------------------- demand
     def _written_tokens(self, request: Request) -> int:
@@ -172,15 +183,54 @@ class Scheduler:
                                  f"the pool has {self.cache.pools[group].num_pages}")
 
     def add(self, request: Request, now_ns: int = 0) -> None:
+        """Take a request in.  With ``request.arrival_ns`` later than ``now_ns`` it is kept aside
+        and joins the waiting queue when :meth:`advance` is told a time at or past its arrival."""
+        self._refuse_if_stopped()
         if request.request_id in self.requests:
             raise ValueError(f"request id {request.request_id} is in use")
         self.validate(request.prompt_token_ids, request.sampling)
         self.requests[request.request_id] = request
+        self._submitted += 1
+        if request.arrival_ns > now_ns:
+            request.status = RequestStatus.PENDING
+            heapq.heappush(self._ahead, (request.arrival_ns, self._submitted, request.request_id))
+            return
+        self._arrive(request, now_ns)
+
+    def _arrive(self, request: Request, now_ns: int) -> None:
         if request.sampling.max_new_tokens == 0 or len(request.prompt_token_ids) == self.max_model_len:
             self._finish(request, "length", now_ns)     # nothing can be generated
             return
         request.status = RequestStatus.WAITING
         self.waiting.append(request.request_id)
+
+    def _still_ahead(self, entry: tuple[int, int, int]) -> bool:
+        request = self.requests.get(entry[2])
+        return (request is not None and request.status is RequestStatus.PENDING
+                and request.arrival_ns == entry[0])
+
+    @property
+    def next_arrival_ns(self) -> int | None:
+        """Arrival time of the earliest request still kept aside (cancelled ones do not count)."""
+        while self._ahead and not self._still_ahead(self._ahead[0]):
+            heapq.heappop(self._ahead)
+        return self._ahead[0][0] if self._ahead else None
+
+    def advance(self, now_ns: int) -> int:
+        """The clock reads ``now_ns`` (it never runs backwards): requests whose time has come join
+        the waiting queue in the order of their arrival times.  Returns how many did."""
+        if type(now_ns) is not int or now_ns < 0:
+            raise ValueError("now_ns must be a non-negative int")
+        if self._now_ns is not None and now_ns < self._now_ns:
+            raise ValueError(f"the clock ran backwards: {now_ns} after {self._now_ns}")
+        self._now_ns = now_ns
+        arrived = 0
+        while self._ahead and self._ahead[0][0] <= now_ns:
+            entry = heapq.heappop(self._ahead)
+            if self._still_ahead(entry):
+                self._arrive(self.requests[entry[2]], now_ns)
+                arrived += 1
+        return arrived
 
     def cancel(self, request_id: int, now_ns: int = 0) -> bool:
         request = self.requests.get(request_id)
@@ -188,11 +238,33 @@ class Scheduler:
             return False
         if request_id in self.waiting:
             self.waiting.remove(request_id)
-        self._finish(request, "cancelled", now_ns)
+        self._finish(request, "cancelled", now_ns)       # one kept aside: its heap entry is skipped later
         return True
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.prefilling or self.decoding)
+        return bool(self.waiting or self.prefilling or self.decoding or self.next_arrival_ns is not None)
+
+    def _refuse_if_stopped(self) -> None:
+        if self.stopped:
+            raise RuntimeError("the scheduler was shut down after a failed step")
+
+    def shutdown(self, open_plan: StepCachePlan | None = None) -> None:
+        """Give everything up after a step that failed on the device: the plan that was open is
+        rolled back, every request lets go of its pages and slot, all queues are emptied and
+        nothing is scheduled any more.  What the requests had produced is lost with them."""
+        self.stopped = True
+        run, self.run_in_flight = self.run_in_flight, None
+        for plan in (open_plan, run.cache_plan if run is not None else None):
+            if plan is not None and plan.state == "planned":
+                self.cache.rollback(plan)
+        for request_id in list(self.cache.open_requests()):
+            self.cache.close(request_id)
+        self.requests.clear()
+        self.waiting.clear()
+        self.prefilling.clear()
+        self.decoding.clear()
+        self.finished.clear()
+        self._ahead.clear()
 
     def take_finished(self) -> list[Request]:
         done, self.finished = self.finished, []
@@ -225,6 +297,7 @@ class Scheduler:
 
     def schedule(self, now_ns: int = 0) -> ScheduledStep | None:
         """The next step, with its pages taken; None when there is nothing to run."""
+        self._refuse_if_stopped()
         if self.run_in_flight is not None:
             raise RuntimeError("a run of decode steps is in flight: end it before the next step is planned")
         admitted = self._admit(now_ns)
@@ -289,6 +362,7 @@ class Scheduler:
         run), and only as many steps as every request may still take: none reaches its token limit
         or the context limit before the run's last step.  A request that meets a stop token inside
         the run ends there; what the run computed for it beyond is dropped with its pages."""
+        self._refuse_if_stopped()
         if self.run_in_flight is not None:
             raise RuntimeError("a run of decode steps is in flight: end it before the next is planned")
         if max_steps < 2 or not self.decoding or self.waiting or self.prefilling:

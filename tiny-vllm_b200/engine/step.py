@@ -16,6 +16,7 @@ entry, not only its last token; there is no per-request loop on the host.
 
 from __future__ import annotations
 
+import logging
 from dataclasses import dataclass
 from typing import Sequence
 
@@ -25,6 +26,10 @@ import torch
 from ..cache.manager import CacheManager, StepCachePlan
 from ..cache.storage import CacheStorage, bytes_per_page, group_runs
 from ..ops import attention as attention_ops
+from ..ops import kernels
+from .capture import capture
+
+log = logging.getLogger("tinyvllm_b200")
 
 
 class StepError(ValueError):
@@ -100,6 +105,17 @@ class _StepGraph:
     logits: torch.Tensor | None
     ctx: StepContext                      # keeps the views the graph reads alive
     last_used: int = 0                    # step count at its last replay
+    guarded: tuple = (False, False)       # kernels with bounded waits inside (gemm_tc, attention_prefill_tc)
+
+
+@dataclass
+class PreparedStep:
+    """A lowered step: its context on the device, the graph that replays it (if one was captured
+    for its signature) and whether it is to be captured after it has run."""
+
+    ctx: StepContext
+    graph: _StepGraph | None = None
+    capture: bool = False
 
 
 class StepRunner:
@@ -130,12 +146,13 @@ class StepRunner:
         self._step_graphs: dict[tuple, _StepGraph] = {}
         self._step_seen: dict[tuple, int] = {}
         self._step_graph_pool = None
+        self._step_graph_stream = None
         self._step_count = 0
         self.decode_splits = attention_ops.decode_splits(self.max_model_len)
-        # prefill tiles are cut for the tcgen05 attention kernel if every mixer says it takes them
+        # prefill tiles are cut for the tcgen05 attention kernel if every block says it takes them
         blocks = getattr(model, "blocks", ())
         self.tensor_memory_tiles = self.dtype == torch.bfloat16 and len(blocks) > 0 and all(
-            getattr(block.mixer, "takes_tensor_memory_tiles", lambda page: False)(page_size)
+            getattr(block, "takes_tensor_memory_tiles", lambda page: False)(page_size)
             for block in blocks)
 
     # ------------------------------------------------------------- sizing
@@ -311,14 +328,15 @@ class StepRunner:
         self._step_graph_limit = limit
 
     @torch.inference_mode()
-    def forward(self, entries: Sequence[StepEntry], plan: StepCachePlan) -> torch.Tensor | None:
-        """The step's logits, through a captured graph if this kind of step has one."""
+    def prepare(self, entries: Sequence[StepEntry], plan: StepCachePlan) -> "PreparedStep":
+        """Lower a step: its fields go into pinned memory and up to the device, and a captured graph
+        is looked up.  No kernel that touches the cache or the model is launched here, so a failure
+        in this half leaves nothing to undo but the cache plan."""
         if self._step_graph_limit <= 0:
-            return self.execute(self.build_context(entries, plan))
+            return PreparedStep(self.build_context(entries, plan), None, False)
         chosen = {}
 
         def arena_of(signature, count):
-            chosen["signature"] = signature
             self._step_count += 1
             graph = self._step_graphs.get(signature)
             if graph is not None:
@@ -339,28 +357,65 @@ class StepRunner:
             return None
 
         ctx = self.build_context(entries, plan, arena_of=arena_of)
-        graph = chosen.get("graph")
+        return PreparedStep(ctx, chosen.get("graph"), bool(chosen.get("capture")))
+
+    @torch.inference_mode()
+    def launch(self, prepared: "PreparedStep") -> torch.Tensor | None:
+        """Run a prepared step: the logits at its wanted places (None if there are none)."""
+        graph = prepared.graph
         if graph is not None:
             graph.graph.replay()
+            # the replay launched the kernels with bounded waits behind the back of their wrappers
+            kernels.note_guarded_launches(*graph.guarded)
             return graph.logits
-        logits = self.execute(ctx)
-        if chosen.get("capture"):
-            self._capture_step(ctx)
+        logits = self.execute(prepared.ctx)
+        if prepared.capture and self._step_graph_limit > 0:
+            self._capture_step(prepared.ctx)
         return logits
 
+    def forward(self, entries: Sequence[StepEntry], plan: StepCachePlan) -> torch.Tensor | None:
+        """The step's logits, through a captured graph if this kind of step has one."""
+        return self.launch(self.prepare(entries, plan))
+
     def _capture_step(self, ctx: StepContext) -> None:
-        """Record the launches of a step that has just run eagerly on ``ctx`` (nothing runs again)."""
-        graph = torch.cuda.CUDAGraph()
+        """Record the launches of a step that has just run eagerly on ``ctx``.  The step runs once
+        more, on the capture stream, before it is recorded (libraries settle their per-stream
+        work areas outside the capture; the same keys and values go to the same cache slots), and
+        nothing runs while it is recorded.  Graphs are an optimisation: if the capture fails, the
+        runner stays eager from then on and the step's eager logits stand."""
+        if self._step_graph_stream is None:
+            self._step_graph_stream = torch.cuda.Stream(device=self.device)
+        stream = self._step_graph_stream
+        before = kernels.guarded_launch_counts()
         try:
-            with torch.cuda.graph(graph, pool=self._step_graph_pool):
+            stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(stream):
+                self.model.forward(ctx)
+            stream.synchronize()
+            after = kernels.guarded_launch_counts()
+            graph = torch.cuda.CUDAGraph()
+            with capture(graph, pool=self._step_graph_pool, stream=stream):
                 logits = self.model.forward(ctx)
-        except Exception:
-            self._step_graph_limit = 0        # a part that cannot be captured: stay eager from now on
-            torch.cuda.synchronize()
-            raise
+        except Exception as failure:                      # noqa: BLE001 (whatever a part or CUDA raises)
+            self._step_graph_limit = 0
+            self._step_graphs.clear()
+            log.warning("a step could not be captured as a CUDA graph (%r); steps run eagerly from now on",
+                        failure)
+            try:
+                torch.cuda.synchronize(self.device)
+            except Exception:                             # noqa: BLE001 (reported by the next real call)
+                pass
+            return
         if self._step_graph_pool is None:
             self._step_graph_pool = graph.pool()
-        self._step_graphs[ctx.signature] = _StepGraph(graph, ctx.arena, logits, ctx, self._step_count)
+        guarded = (after[0] > before[0], after[1] > before[1])      # what one pass of the step launched
+        ctx.workspace_of = None       # a replay asks for no scratch; without it the graph does not hold the runner
+        self._step_graphs[ctx.signature] = _StepGraph(graph, ctx.arena, logits, ctx, self._step_count, guarded)
+
+    def drop_graphs(self) -> None:
+        """Forget every captured step (their device memory goes back to the allocator)."""
+        self._step_graphs.clear()
+        self._step_seen.clear()
 
     @torch.inference_mode()
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:

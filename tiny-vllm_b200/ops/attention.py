@@ -157,7 +157,10 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
                     scale=mixer.scale, splits=splits, max_context=ctx.max_context, out=out[part],
                     new_in_cache=True)
                 continue
-            chunks = choose_split(count, ctx.max_position)
+            # chunks for the longest context a request may reach, not for this step's: the count is
+            # then the same for every step with these entry sizes, which a recorded step relies on
+            # (the merge walks only the chunks a row's own position reaches)
+            chunks = choose_split(count, max(ctx.max_context - 1, ctx.max_position))
             scratch = None
             if chunks > 0:
                 scratch = ctx.workspace(kernels.attention_rows_scratch_floats(

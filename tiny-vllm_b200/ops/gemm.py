@@ -13,25 +13,34 @@ call the reference's engine makes for every projection (tinyvllm/layers.py:84-85
 
 from __future__ import annotations
 
+import weakref
+
 import torch
 
 from . import kernels
 
 
-# weight (by address) -> the weight the model streams next in a decode step; the weight-streaming
-# kernel asks for it to be brought into L2 while it works on its own
-_next_weight: dict[int, torch.Tensor] = {}
+# weight (by address) -> (that weight, the weight the model streams next in a decode step), both as
+# weak references: the weight-streaming kernel asks for the next one to be brought into L2 while it
+# works on its own.  Weak, so that a model that is dropped frees its memory; the first reference
+# tells a weight from a later tensor that the allocator put at the same address.
+_next_weight: dict[int, tuple[weakref.ref, weakref.ref]] = {}
 
 
 def chain_weights(weights) -> None:
     """Declare the order in which a step streams ``weights`` (the last is followed by the first)."""
     weights = [w for w in weights if w is not None and w.is_cuda and w.dtype == torch.bfloat16]
+    for key in [key for key, (current, _) in _next_weight.items() if current() is None]:
+        del _next_weight[key]
     for current, following in zip(weights, weights[1:] + weights[:1]):
-        _next_weight[current.data_ptr()] = following
+        _next_weight[current.data_ptr()] = (weakref.ref(current), weakref.ref(following))
 
 
 def next_weight(weight: torch.Tensor) -> torch.Tensor | None:
-    return _next_weight.get(weight.data_ptr())
+    found = _next_weight.get(weight.data_ptr())
+    if found is None or found[0]() is not weight:
+        return None
+    return found[1]()
 
 
 # rows from which the tcgen05 kernel's tiles of 128 rows are mostly full

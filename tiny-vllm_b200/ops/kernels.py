@@ -514,6 +514,7 @@ def attention_prefill_tc(q: torch.Tensor, q_token_stride: int, key_cache: torch.
               num_q, num_kv, head_dim, key_cache.shape[2], window or 0, scale, _stream()),
            "attention_prefill_tc")
     _attention_tc_unchecked = True
+    _guarded_counts[1] += 1
     return out
 
 
@@ -659,6 +660,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *, out: tor
     _check(fn(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
               m, n, k, mode, tile_n, _pdl("gemm"), _stream()), "gemm_tc")
     _gemm_tc_unchecked = True
+    _guarded_counts[0] += 1
     return out
 
 
@@ -683,6 +685,25 @@ def wait_probe(code: int = 77) -> tuple[int, int]:
     if status < 0:
         raise KernelError(f"wait_probe failed ({status})")
     return status, waited.value
+
+
+_guarded_counts = [0, 0]
+
+
+def guarded_launch_counts() -> tuple[int, int]:
+    """How often (gemm_tc, attention_prefill_tc), the kernels with bounded waits, were launched
+    through this module so far.  A caller that records a step into a CUDA graph compares the
+    counts around one pass of the step and hands what it finds to :func:`note_guarded_launches`
+    at every replay: a replay launches the kernels without passing through this module."""
+    return _guarded_counts[0], _guarded_counts[1]
+
+
+def note_guarded_launches(gemm: bool, attention: bool) -> None:
+    """Kernels with bounded waits ran without this module seeing it (a graph replay): their status
+    words are read at the next :func:`check_finished_launches`."""
+    global _gemm_tc_unchecked, _attention_tc_unchecked
+    _gemm_tc_unchecked = _gemm_tc_unchecked or bool(gemm)
+    _attention_tc_unchecked = _attention_tc_unchecked or bool(attention)
 
 
 def check_finished_launches() -> None:

@@ -86,7 +86,7 @@ def linear_norm(hidden: torch.Tensor | None, residual: torch.Tensor | None, norm
 
     if hidden is None:
         squares = getattr(residual, "row_squares", None)
-        if (squares is not None and weight.dtype == torch.bfloat16 and type(norm).__name__ == "RMSNorm"
+        if (squares is not None and weight.dtype == torch.bfloat16 and getattr(norm, "folds_into_product", False)
                 and gemm.small(residual, weight) and residual.is_contiguous()
                 and norm.weight.data_ptr() % 16 == 0):
             mode = kernels.GEMM_SILU if silu else kernels.GEMM_BF16
@@ -96,7 +96,7 @@ def linear_norm(hidden: torch.Tensor | None, residual: torch.Tensor | None, norm
         x = norm.forward(residual)
         return (linear_silu(x, weight) if silu else linear(x, weight)), residual
     if (hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and hidden.is_contiguous()
-            and type(norm).__name__ == "RMSNorm" and gemm.small(hidden, weight)
+            and getattr(norm, "folds_into_product", False) and gemm.small(hidden, weight)
             and hidden.shape[0] <= FUSED_NORM_MAX_ROWS
             and kernels.gemm_small_m_takes_norm(hidden.shape[0], hidden.shape[1])):
         mode = kernels.GEMM_SILU if silu else kernels.GEMM_BF16

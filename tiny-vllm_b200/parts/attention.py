@@ -71,6 +71,11 @@ class GQAAttention(Part):
         return kernels.attention_prefill_tc_supports(self.head_dim, self.num_heads, self.num_kv_heads,
                                                      page_size)
 
+    def scratch_floats(self, rows: int, chunks: int) -> int:
+        """float32 scratch the row kernel asks for when it spreads ``chunks`` key chunks of
+        ``rows`` single tokens over the grid."""
+        return kernels.attention_rows_scratch_floats(rows, self.num_heads, self.head_dim, chunks)
+
     # ---------------------------------------------------------------- running
     def forward(self, x, ctx, run: int):
         qkv = linear(x, self.qkv_weight)

@@ -8,7 +8,10 @@ and runs on the tensors of one step.  No part knows the model it is in.
 Kinds of parts and what each must offer
 ---------------------------------------
 norm            ``forward(x) -> y`` and ``add(x, residual) -> (y, new_residual)``,
-                optionally ``add_rows(x, residual, rows) -> y`` on chosen rows
+                optionally ``add_rows(x, residual, rows) -> y`` on chosen rows.  A norm
+                that is y = x * rsqrt(mean(x^2) + eps) * weight with attributes
+                ``weight`` [width] and ``eps`` may set ``folds_into_product = True``:
+                a projection right behind it may then apply it inside its own kernel
 position        ``prepare(ctx)``; handed to the mixer that asked for it
 mixer           ``cache_need() -> KVNeed | StateNeed | None`` and
                 ``forward(x, ctx, run) -> y`` where ``ctx`` is the step's
@@ -18,12 +21,21 @@ mixer           ``cache_need() -> KVNeed | StateNeed | None`` and
                 projection; ``hidden`` is None when the part before added its
                 output to the residual itself, and ``y`` may be None for the
                 same reason), ``streamed_weights()`` (the large weights in the
-                order a step reads them) and ``takes_tensor_memory_tiles(page_size)``
+                order a step reads them), ``takes_tensor_memory_tiles(page_size)``
+                and ``scratch_floats(rows, chunks) -> int`` (float32 scratch its
+                kernels may ask of ``ctx.workspace`` for a step of ``rows`` single
+                tokens whose keys are cut into ``chunks`` chunks; it is set aside
+                before decode steps are captured as graphs)
 feed_forward    ``forward(x, ctx) -> y``, optionally ``forward_normed`` and
                 ``streamed_weights`` as above
 block           ``forward(hidden, residual, ctx, run) -> (hidden, residual)``;
                 ``residual`` is None for the first block, ``hidden`` is None
-                (on the way in or out) when it is in the residual already
+                (on the way in or out) when it is in the residual already.
+                The engine asks the block, never its insides: ``cache_need()``
+                (one per run of the block), ``takes_tensor_memory_tiles(page_size)``
+                and ``scratch_floats(rows, chunks)``; :class:`Block` answers them
+                from an attribute ``mixer``, a block arranged otherwise answers
+                them itself
 embedding       ``forward(token_ids) -> hidden``
 head            ``forward(hidden_rows) -> logits`` (float32)
 """
@@ -124,3 +136,26 @@ class Part:
         for child in self.children():
             found.extend(child.all_parts())
         return found
+
+
+class Block(Part):
+    """Base of block arrangements.  The engine talks to a block only through these methods and
+    ``forward``; the defaults pass the questions on to ``self.mixer``."""
+
+    mixer = None
+
+    def cache_need(self):
+        """What one run of this block needs of the cache: KVNeed, StateNeed or None."""
+        return self.mixer.cache_need() if self.mixer is not None else None
+
+    def takes_tensor_memory_tiles(self, page_size: int) -> bool:
+        """Whether prompt portions of this block may be cut into the tile lists of the
+        tensor-memory attention kernel (a block without attention does not care: True)."""
+        if self.mixer is None:
+            return True
+        asked = getattr(self.mixer, "takes_tensor_memory_tiles", None)
+        return bool(asked(page_size)) if asked is not None else False
+
+    def scratch_floats(self, rows: int, chunks: int) -> int:
+        asked = getattr(self.mixer, "scratch_floats", None) if self.mixer is not None else None
+        return int(asked(rows, chunks)) if asked is not None else 0

@@ -8,11 +8,11 @@ model's final norm) adds it (tinyvllm/models/qwen3.py:386-412).
 
 from __future__ import annotations
 
-from .base import BuildContext, Part
+from .base import Block, BuildContext
 from .registry import register_part
 
 
-class PreNormResidualBlock(Part):
+class PreNormResidualBlock(Block):
     def __init__(self, ctx: BuildContext, *, mixer, feed_forward, norm, mixer_norm_name: str,
                  feed_forward_norm_name: str, mixer_name: str, feed_forward_name: str) -> None:
         self.mixer_norm = ctx.build("norm", norm, ctx.child(mixer_norm_name))

@@ -13,6 +13,9 @@ from .registry import register_part
 
 
 class RMSNorm(Part):
+    # y = x * rsqrt(mean(x^2) + eps) * weight: a projection behind it may apply it in its own kernel
+    folds_into_product = True
+
     def __init__(self, ctx: BuildContext, *, width: int, eps: float, name: str | None = None) -> None:
         self.width = width
         self.eps = float(eps)
