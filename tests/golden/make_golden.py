@@ -16,8 +16,8 @@ Two things are not the reference's own code here, because they cannot run on
 this CPU as shipped:
 * its four pointwise operations are CUDA only (tinyvllm/layers.py:12-16,
   tinyvllm/models/qwen3.py:16); they are replaced by the functions of
-  tests/plain_qwen3.py, so those four formulas rest on reading
-  tinyvllm/kernels/pointwise.cu, not on running it;
+  tests/plain_qwen3.py here; those four formulas are checked against the reference's own
+  kernels separately (make_pointwise_golden.py, run on a GPU, reference_pointwise.npz);
 * its configuration loader goes through a transformers version that is not
   installed; the configuration object is built with ``Qwen3Config.from_hf`` from
   a plain namespace of the same keys (tinyvllm/models/qwen3.py:123-201).

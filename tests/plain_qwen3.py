@@ -88,8 +88,9 @@ def read_weights(model_dir) -> dict[str, torch.Tensor]:
 # --------------------------------------------------------------------------
 
 def embed(table: torch.Tensor, ids: torch.Tensor, dt) -> torch.Tensor:
-    """h = E[ids]  (tinyvllm/models/qwen3.py:480)."""
-    return rnd(table, dt)[ids]
+    """h = E[ids]  (tinyvllm/models/qwen3.py:480); the rows are rounded after the gather, which is
+    the same values as gathering from the rounded table."""
+    return rnd(table[ids], dt)
 
 
 def rope_tables(d: int, max_pos: int, theta: float):
@@ -214,8 +215,9 @@ def mlp_block(w, prefix, x, dt):
     return linear(swiglu(gate_up, dt), w[f"{prefix}.mlp.down_proj.weight"], dt)
 
 
-def forward(cfg: dict, w: dict, ids, dt=F32, order=None) -> torch.Tensor:
-    """Logits [T, V] of one whole sequence, float32.
+def forward(cfg: dict, w: dict, ids, dt=F32, order=None, rows=None) -> torch.Tensor:
+    """Logits [T, V] of one whole sequence, float32; with ``rows`` (positions) only those rows,
+    in that order (every layer still runs over the whole sequence).
 
     Layer arrangement of tinyvllm/models/qwen3.py:386-412 and :458-494: the
     first layer norms the embedding and keeps it as the residual stream;
@@ -245,6 +247,9 @@ def forward(cfg: dict, w: dict, ids, dt=F32, order=None) -> torch.Tensor:
         produced.append(kv)
         x, res = add_rms_norm(a, res, wpost, cfg["eps"], dt)
         h = mlp_block(w, p, x, dt)
+    if rows is not None:
+        keep = torch.as_tensor(list(rows), dtype=torch.long)
+        h, res = h[keep], res[keep]
     x, _ = add_rms_norm(h, res, rnd(w["model.norm.weight"], dt), cfg["eps"], dt)
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     return x @ rnd(head, dt).T

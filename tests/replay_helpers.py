@@ -164,17 +164,61 @@ def read_trace_output(steps: list[dict], out_dir, vocab: int) -> dict:
 _oracle_cache: dict = {}
 
 
-def oracle(folder, requests: dict, dtype: torch.dtype, order=None) -> dict:
-    """{request: logits [T, V]} of the plain implementation (cached per folder and dtype)."""
+class SomeRows:
+    """The oracle's logits at chosen positions of one sequence: ``self[position]`` is a row."""
+
+    def __init__(self, positions, rows: torch.Tensor) -> None:
+        self.rows = {position: rows[i] for i, position in enumerate(positions)}
+        self.largest = rows.abs().max().item()
+
+    def __getitem__(self, position):
+        return self.rows[position]
+
+
+def logit_scale(expected) -> float:
+    return expected.largest if isinstance(expected, SomeRows) else expected.abs().max().item()
+
+
+def oracle(folder, requests: dict, dtype: torch.dtype, order=None, positions=None, weights=None) -> dict:
+    """{request: logits [T, V]} of the plain implementation (cached per folder and dtype).  With
+    ``positions`` = {request: positions} only those rows are made (a wide vocabulary)."""
     cfg = plain.read_config(folder)
-    weights = plain.read_weights(folder)
+    weights = weights if weights is not None else plain.read_weights(folder)
     out = {}
     for rid, tokens in requests.items():
-        key = (str(folder), dtype, tuple(tokens), None if order is None else tuple(order))
+        chosen = None if positions is None else tuple(sorted(positions[rid]))
+        key = (str(folder), dtype, tuple(tokens), None if order is None else tuple(order), chosen)
         if key not in _oracle_cache:
-            _oracle_cache[key] = plain.forward(cfg, weights, tokens, dtype, order=order)
+            logits = plain.forward(cfg, weights, tokens, dtype, order=order, rows=chosen)
+            _oracle_cache[key] = logits if chosen is None else SomeRows(chosen, logits)
         out[rid] = _oracle_cache[key]
     return out
+
+
+def thin(steps: list[dict], keep_every: int, tail: int = 24) -> list[dict]:
+    """The same trace with logits wanted only at every ``keep_every``-th place of a portion and at
+    its last ``tail`` places (a wide vocabulary makes every row expensive)."""
+    thinned = []
+    for step in steps:
+        entries = []
+        for entry in step["entries"]:
+            count = len(entry["tokens"])
+            want = [p for p in entry["want"] if p % keep_every == 0 or p >= count - tail]
+            entries.append({**entry, "want": want})
+        thinned.append({**step, "entries": entries})
+    return thinned
+
+
+def wanted_positions(steps: list[dict]) -> dict:
+    """{request: positions at which the trace wants logits}."""
+    found: dict = {}
+    position: dict = {}
+    for step in steps:
+        for entry in step["entries"]:
+            start = position.get(entry["id"], 0)
+            found.setdefault(entry["id"], set()).update(start + p for p in entry["want"])
+            position[entry["id"]] = start + len(entry["tokens"])
+    return found
 
 
 def compare(got: dict, expected: dict, dtype: torch.dtype, *, what: str = "") -> float:
@@ -184,7 +228,7 @@ def compare(got: dict, expected: dict, dtype: torch.dtype, *, what: str = "") ->
     total, count = 0.0, 0
     for (rid, position), row in sorted(got.items(), key=lambda kv: (str(kv[0][0]), kv[0][1])):
         want = expected[rid][position]
-        scale = expected[rid].abs().max().item()
+        scale = logit_scale(expected[rid])
         assert torch.isfinite(row).all(), f"{what}: request {rid} position {position}: not finite"
         diff = (row - want).abs()
         err = diff.max().item() / scale

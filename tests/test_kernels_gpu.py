@@ -226,6 +226,35 @@ def test_attention_window_edge(dtype, window):
     assert (full[-1] - want[-1]).abs().max() > 1e-3       # the boosted key would have changed the result
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_attention_rows_with_too_few_chunks_stays_inside_its_scratch(dtype):
+    """``max_chunks`` one too small for the longest context: the rows it cannot hold come out as
+    NaN, the others are right, and nothing beyond tokens * heads * max_chunks * (head + 2) floats of
+    the scratch is written.  The buffer handed over is several times larger than needed and filled
+    with a sentinel, so every access of the kernels stays inside allocated memory either way."""
+    kernels = k()
+    nq, nkv, d, page = 4, 2, 32, 8
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[700, 100], queries=[2, 2], seed=9)
+    scale = d ** -0.5
+    want = plain_paged(case, scale, None, dtype)
+    needed = 3                                        # positions up to 699: chunks 0, 1, 2
+    q = case["q"].to(DEV).view(case["q"].shape[0], nq * d)
+    for max_chunks in (needed, needed - 1):
+        stated = kernels.attention_rows_scratch_floats(q.shape[0], nq, d, max_chunks)
+        scratch = torch.full((8 * stated,), 12345.0, dtype=torch.float32, device=DEV)
+        got = kernels.attention_rows(
+            q, nq * d, case["kc"].to(DEV), case["vc"].to(DEV), case["tables"].to(DEV),
+            case["token_row"].to(DEV), case["positions"].to(DEV), num_q=nq, num_kv=nkv, head_dim=d,
+            window=None, scale=scale, scratch=scratch, max_chunks=max_chunks).view(-1, nq, d)
+        torch.cuda.synchronize()
+        assert (scratch[stated:] == 12345.0).all()                   # nothing written past the stated size
+        if max_chunks == needed:
+            close(got, want, dtype, f32=3e-6, bf16=8e-3)
+        else:
+            assert torch.isnan(got[:2].float()).all()                # the rows at positions 698, 699
+            close(got[2:], want[2:], dtype, f32=3e-6, bf16=8e-3)     # the short request is untouched by it
+
+
 def test_attention_padding_rows_give_zeros():
     case = paged_case(torch.float32, nq=2, nkv=1, d=16, page=4, lengths=[9], queries=[2], seed=0)
     case["token_row"][1] = -1

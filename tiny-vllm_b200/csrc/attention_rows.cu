@@ -209,7 +209,16 @@ __global__ void merge_attention_rows_kernel(const float* __restrict__ scratch, i
     total.sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < ATTN_MAX_DIMS; ++i) total.out[i] = 0.0f;
-    for (int chunk = lo / ATTN_CHUNK; chunk <= position / ATTN_CHUNK; ++chunk) {
+    // The scratch holds max_chunks partials a row.  A caller whose max_chunks is too small for this
+    // row's position gets the row as NaN: the first kernel wrote no partial beyond max_chunks - 1,
+    // and reading on would take the next row's (or leave the buffer).
+    const int last_chunk = position / ATTN_CHUNK;
+    if (last_chunk >= max_chunks) {
+        T* bad_row = out + row * head_dim;
+        for (int dim = lane; dim < head_dim; dim += 32) bad_row[dim] = from_float<T>(__int_as_float(0x7fc00000));
+        return;
+    }
+    for (int chunk = lo / ATTN_CHUNK; chunk <= last_chunk; ++chunk) {
         const float* src = scratch + (row * max_chunks + chunk) * (int64_t)(head_dim + 2);
         Partial part;
         part.max = src[0];
@@ -237,7 +246,10 @@ extern "C" long long tvb_attention_rows_scratch_floats(int tokens, int num_q, in
 }
 
 // max_chunks = 0 selects mode rows (no scratch).  Otherwise max_chunks must be at
-// least ceil((largest position + 1) / ATTN_CHUNK) of the batch.
+// least ceil((largest position + 1) / ATTN_CHUNK) of the batch and scratch must hold
+// tokens * num_q * max_chunks * (head_dim + 2) floats.  The host cannot see the positions:
+// a row whose position needs more chunks than max_chunks is written as NaN (and nothing
+// outside the stated scratch is read or written).
 extern "C" int tvb_attention_rows(const void* q, long long q_token_stride, const void* key_cache,
                                   const void* value_cache, const int* block_tables, int table_stride,
                                   const int* token_row, const int* positions, void* out,
@@ -325,7 +337,11 @@ extern "C" int tvb_attention_rows_static(const void* q, long long q_token_stride
                                          int max_chunks, int tokens, int num_q, int num_kv, int head_dim,
                                          int page_size, int window, float scale, int dtype, void* stream) {
     if (tokens <= 0) return 0;
-    if (max_chunks <= 0 || num_q <= 0 || head_dim <= 0) return TVB_BAD_ARGUMENT;
+    // bounds first, so that the product below cannot overflow
+    if (max_chunks <= 0 || max_chunks > 65535 || num_q <= 0 || num_q > 65535 || head_dim <= 0 ||
+        head_dim > 32 * ATTN_MAX_DIMS)
+        return TVB_BAD_ARGUMENT;
+    if (tokens > TVB_STATIC_SCRATCH_FLOATS) return TVB_STATIC_SCRATCH_TOO_SMALL;      // every token needs floats
     if (tvb_attention_rows_scratch_floats(tokens, num_q, head_dim, max_chunks) > TVB_STATIC_SCRATCH_FLOATS)
         return TVB_STATIC_SCRATCH_TOO_SMALL;
     float* scratch = nullptr;

@@ -21,6 +21,12 @@
 // TVB_STATIC_SCRATCH_TOO_SMALL before anything is launched; max_chunks == 0 (no scratch needed)
 // is refused with TVB_BAD_ARGUMENT, use tvb_attention_rows for that.
 //
+// What the caller must get right.  max_chunks has to be at least
+// ceil((largest position in `positions` + 1) / 256): the partials of a row are stored
+// max_chunks to a row.  The positions live on the device, so the call cannot check this; a row
+// whose position needs more chunks than max_chunks comes out as NaN (nothing outside the
+// array is touched).  max_chunks and num_q up to 65,535 and head_dim up to 256 are accepted.
+//
 // First call on a device.  The first call made while a device is current looks up the device
 // address of the array (cudaGetSymbolAddress) and keeps it for that device; later calls reuse
 // it.  Make that first call before any stream capture begins.
