@@ -157,8 +157,8 @@ def test_trace_run_program(dtype_name, model_folders, tmp_path):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 def test_steps_replayed_as_graphs_give_the_eager_logits(dtype, model_folders):
-    """A step whose signature comes back is captured at its second occurrence and replayed from
-    the third: the logits of every occurrence are those of a runner that never captures, bit
+    """A step whose signature keeps coming back is captured at its third occurrence and replayed
+    from the fourth: the logits of every occurrence are those of a runner that never captures, bit
     for bit, also with other steps in between and with pages that are used again."""
     from tinyvllm_b200.engine.step import StepEntry
 
@@ -167,6 +167,8 @@ def test_steps_replayed_as_graphs_give_the_eager_logits(dtype, model_folders):
     eager = make_runner(model_folders[name], dtype, PAGE_SIZES[name], 24, max_requests=4)
     graphed = make_runner(model_folders[name], dtype, PAGE_SIZES[name], 24, max_requests=4)
     graphed.enable_step_graphs(limit=2)
+    # capture eagerly: at the second occurrence, any number of captures in a row, any graph may go
+    graphed.CAPTURE_AT_OCCURRENCE, graphed.CAPTURE_EVERY_STEPS, graphed.KEEP_FOR_STEPS = 2, 0, 0
     shapes = [(150, 3), (150, 3), (40, 2), (150, 3), (150, 3), (40, 2), (40, 2), (7, 1), (150, 3), (7, 1), (7, 1)]
     for step, (count, wanted) in enumerate(shapes):
         tokens = tuple(random_tokens(vocab, count, 1000 + step))
@@ -184,3 +186,33 @@ def test_steps_replayed_as_graphs_give_the_eager_logits(dtype, model_folders):
             assert torch.equal(a, b), f"step {step}"
     assert len(graphed._step_graphs) == 2          # the limit holds: the third shape took the place of the
     assert any(sig[0][0] == 7 for sig in graphed._step_graphs)      # one unused for longest
+
+
+def test_steps_are_captured_sparingly(model_folders):
+    """A capture costs about two steps: a shape is captured at its third occurrence, captures keep a
+    distance of some steps, and a graph in use is not thrown out for a newcomer."""
+    from tinyvllm_b200.engine.step import StepEntry, StepRunner
+
+    name = "e"
+    vocab = TINY_CONFIGS[name].vocab_size
+    runner = make_runner(model_folders[name], torch.bfloat16, PAGE_SIZES[name], 64, max_requests=4)
+    runner.enable_step_graphs(limit=1)
+
+    def step(count, index):
+        runner.open(index)
+        runner.run([StepEntry(index, tuple(random_tokens(vocab, count, index)), (count - 1,))])
+        runner.close(index)
+
+    for index in range(2):
+        step(100, index)
+    assert not runner._step_graphs                              # seen twice: not yet
+    step(100, 2)
+    assert len(runner._step_graphs) == 1                        # the third time
+    (first,) = runner._step_graphs
+    for index in range(3, 3 + StepRunner.CAPTURE_EVERY_STEPS + 4):
+        step(50, index)                                         # another shape, again and again
+    assert list(runner._step_graphs) == [first]                 # the graph was replayed too recently to go
+    runner.KEEP_FOR_STEPS = 4
+    for index in range(40, 46):
+        step(50, index)
+    assert list(runner._step_graphs) != [first] and len(runner._step_graphs) == 1

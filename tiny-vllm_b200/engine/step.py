@@ -148,6 +148,7 @@ class StepRunner:
         self._step_graph_pool = None
         self._step_graph_stream = None
         self._step_count = 0
+        self._last_capture_at = -(1 << 30)
         self.decode_splits = attention_ops.decode_splits(self.max_model_len)
         # prefill tiles are cut for the tcgen05 attention kernel if every block says it takes them
         blocks = getattr(model, "blocks", ())
@@ -319,13 +320,23 @@ class StepRunner:
         return self.model.forward(ctx)
 
     # ------------------------------------------------- steps as CUDA graphs
+    # A capture costs about two eager steps (the step runs once more on the capture stream, then
+    # its launches are recorded and the graph is instantiated), a replay saves about half of one:
+    # a shape is captured when it has come CAPTURE_AT_OCCURRENCE times, at most one capture in
+    # CAPTURE_EVERY_STEPS steps, and a graph that was replayed within the last KEEP_FOR_STEPS steps
+    # is not thrown out for a newcomer.
+    CAPTURE_AT_OCCURRENCE = 3
+    CAPTURE_EVERY_STEPS = 8
+    KEEP_FOR_STEPS = 64
+
     def enable_step_graphs(self, limit: int = 16) -> None:
-        """Steps whose signature (token, row, block and tile counts) comes back are captured as CUDA
-        graphs at their second occurrence and replayed from the third: the host then issues one
-        launch instead of some ten a layer.  At most ``limit`` graphs are kept (the one unused for
-        longest makes room); they share one memory pool.  Only for models whose parts do all per-step work in kernels (no host-side
-        planning from ``host_rows``)."""
+        """Steps whose signature (token, row, block and tile counts) keeps coming back are captured
+        as CUDA graphs (at their third occurrence) and replayed from then on: the host then issues
+        one launch instead of some ten a layer.  At most ``limit`` graphs are kept (one that has not
+        been replayed for a while makes room); they share one memory pool.  Only for models whose
+        parts do all per-step work in kernels (no host-side planning from ``host_rows``)."""
         self._step_graph_limit = limit
+        self._last_capture_at = -(1 << 30)
 
     @torch.inference_mode()
     def prepare(self, entries: Sequence[StepEntry], plan: StepCachePlan) -> "PreparedStep":
@@ -347,14 +358,20 @@ class StepRunner:
             if len(self._step_seen) > 4096:
                 self._step_seen.clear()
             self._step_seen[signature] = seen
-            if seen >= 2:
-                if len(self._step_graphs) >= self._step_graph_limit:
-                    # the graph that has waited longest for its shape to come back makes room
-                    oldest = min(self._step_graphs, key=lambda key: self._step_graphs[key].last_used)
-                    del self._step_graphs[oldest]
-                chosen["capture"] = True
-                return torch.empty(count, dtype=torch.int32, device=self.device)
-            return None
+            if seen < self.CAPTURE_AT_OCCURRENCE or self._step_count - self._last_capture_at < self.CAPTURE_EVERY_STEPS:
+                return None
+            if len(self._step_graphs) >= self._step_graph_limit:
+                # the graph that has waited longest for its shape to come back makes room, unless
+                # even that one was replayed a moment ago
+                oldest = min(self._step_graphs, key=lambda key: self._step_graphs[key].last_used)
+                if self._step_count - self._step_graphs[oldest].last_used < self.KEEP_FOR_STEPS:
+                    return None
+                del self._step_graphs[oldest]
+                if not self._step_graphs:
+                    self._step_graph_pool = None      # the pool went with its last graph
+            self._last_capture_at = self._step_count
+            chosen["capture"] = True
+            return torch.empty(count, dtype=torch.int32, device=self.device)
 
         ctx = self.build_context(entries, plan, arena_of=arena_of)
         return PreparedStep(ctx, chosen.get("graph"), bool(chosen.get("capture")))
@@ -399,6 +416,7 @@ class StepRunner:
         except Exception as failure:                      # noqa: BLE001 (whatever a part or CUDA raises)
             self._step_graph_limit = 0
             self._step_graphs.clear()
+            self._step_graph_pool = None
             log.warning("a step could not be captured as a CUDA graph (%r); steps run eagerly from now on",
                         failure)
             try:
@@ -415,6 +433,7 @@ class StepRunner:
     def drop_graphs(self) -> None:
         """Forget every captured step (their device memory goes back to the allocator)."""
         self._step_graphs.clear()
+        self._step_graph_pool = None
         self._step_seen.clear()
 
     @torch.inference_mode()

@@ -32,7 +32,9 @@ def dtype_tag(dtype: torch.dtype) -> int:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of the current stream of the current device: the same value as
+    # torch.cuda.current_stream().cuda_stream without building a Stream object (this runs once a launch)
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 _launches = 0
