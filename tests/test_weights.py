@@ -18,7 +18,7 @@ def cpu_model(name, dtype):
 
 def load(model, folder, dtype):
     load_checkpoint(model.param_targets(), folder, dtype=dtype, device="cpu",
-                    optional=model._optional_names())
+                    aliases=model._name_aliases())
 
 
 def test_folder_has_config_and_tensors(model_folders):
@@ -104,10 +104,17 @@ def test_one_error_lists_everything(tmp_path):
 
 def test_tied_head_may_be_stored_and_no_shards_is_an_error(tmp_path):
     folder = write_model_folder(tmp_path / "m", TINY_CONFIGS["a"], 0)
-    tensors = load_file(str(folder / "model.safetensors"))
+    tensors = {name: tensor.clone() for name, tensor in load_file(str(folder / "model.safetensors")).items()}
     tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
     save_file(tensors, str(folder / "model.safetensors"))
     load(cpu_model("a", torch.float32), folder, torch.float32)
+    # stored under the head's name only: it is the embedding (tinyvllm/models/qwen3.py:637-641, :682-686)
+    embedding = tensors.pop("model.embed_tokens.weight")
+    tensors["lm_head.weight"] = embedding * 2
+    save_file(tensors, str(folder / "model.safetensors"))
+    model = cpu_model("a", torch.float32)
+    load(model, folder, torch.float32)
+    assert torch.equal(model.embedding.weight, embedding * 2)
     (folder / "model.safetensors").unlink()
     with pytest.raises(WeightsError, match="no .safetensors"):
         load(cpu_model("a", torch.float32), folder, torch.float32)

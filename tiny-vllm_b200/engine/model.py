@@ -78,15 +78,15 @@ class Model:
             streamed.extend(getattr(self.head, "streamed_weights", lambda: [])())
             chain_weights(streamed)
 
-    def _optional_names(self) -> tuple[str, ...]:
-        # a tied head may still be stored beside the embedding (tinyvllm/models/qwen3.py:637-641)
-        if getattr(self.head, "tied_to", None) is not None:
-            return (self.head.name,)
-        return ()
+    def _name_aliases(self) -> dict[str, str]:
+        # a tied head may be stored under its own name, beside the embedding or instead of it: it is
+        # the embedding (tinyvllm/models/qwen3.py:637-641, :682-686)
+        tied = getattr(self.head, "tied_to", None)
+        return {self.head.name: tied} if tied is not None else {}
 
     def load(self, folder: str | Path) -> "Model":
         load_checkpoint(self.param_targets(), folder, dtype=self.dtype, device=self.device,
-                        optional=self._optional_names())
+                        aliases=self._name_aliases())
         self._after_binding()
         return self
 

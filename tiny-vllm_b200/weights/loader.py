@@ -80,19 +80,27 @@ def _routes(targets: Iterable[tuple[Part, ParamSpec]]):
 
 
 def bind_tensors(targets, named_tensors, *, dtype, device, folder="<memory>",
-                 optional: Iterable[str] = ()) -> None:
+                 optional: Iterable[str] = (), aliases: dict[str, str] | None = None) -> None:
     """Fill and bind every declared tensor from ``named_tensors`` (name -> CPU or
     device tensor, or an iterable of such pairs).  ``optional`` names may be
-    present without being used (a tied head stored beside the embedding)."""
+    present without being used.  ``aliases`` maps a name a file may use to the
+    declared name it stands for: the tensor fills the declared one (the one that
+    comes later in the file wins if both are there) and the declared one counts
+    as present.  A tied head stored as ``lm_head.weight`` fills the embedding that
+    way, as the reference does (tinyvllm/models/qwen3.py:637-641, :682-686)."""
     targets = list(targets)
     routes = _routes(targets)
     optional = set(optional)
+    aliases = dict(aliases or {})
     destinations: dict[tuple[int, str], torch.Tensor] = {}
-    seen, unexpected, wrong = set(), [], []
+    in_file, seen, unexpected, wrong = set(), set(), [], []
     items = named_tensors.items() if hasattr(named_tensors, "items") else named_tensors
     for name, tensor in items:
-        if name in seen:
+        if name in in_file:
             raise WeightsError(folder, other=[f"tensor {name} appears twice"])
+        in_file.add(name)
+        if name in aliases and aliases[name] in routes:
+            name = aliases[name]
         seen.add(name)
         route = routes.get(name)
         if route is None:
@@ -116,7 +124,7 @@ def bind_tensors(targets, named_tensors, *, dtype, device, folder="<memory>",
         part.bind(spec.attr, destinations[(id(part), spec.attr)])
 
 
-def load_checkpoint(targets, folder, *, dtype, device, optional=()) -> None:
+def load_checkpoint(targets, folder, *, dtype, device, optional=(), aliases=None) -> None:
     """Read every shard of ``folder`` and bind the tensors to their parts."""
     from safetensors import safe_open
 
@@ -128,4 +136,5 @@ def load_checkpoint(targets, folder, *, dtype, device, optional=()) -> None:
                 for name in shard.keys():
                     yield name, shard.get_tensor(name)
 
-    bind_tensors(targets, stream(), dtype=dtype, device=device, folder=folder, optional=optional)
+    bind_tensors(targets, stream(), dtype=dtype, device=device, folder=folder, optional=optional,
+                 aliases=aliases)
