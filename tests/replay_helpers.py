@@ -16,11 +16,16 @@ import torch
 import plain_qwen3 as plain
 
 TOLERANCE = {
-    # largest |difference| allowed, as a fraction of the largest |logit| of the sequence
-    torch.float32: 2e-5,
-    torch.bfloat16: 4e-2,
+    # largest |difference| allowed, as a fraction of the largest |logit| of the sequence.  Observed on a
+    # B200 over every configuration and way of cutting: float32 up to 1.1e-6 at the tiny sizes and 7.1e-6
+    # at the layer widths of the 8B and 32B sizes (sums over 12,288 and 25,600 terms in another order
+    # than the oracle's); bfloat16 up to 1.5e-2 (both follow the same rounding points; the engine's
+    # products sum in another order and its attention rounds probabilities per tile).
+    torch.float32: 1.2e-5,
+    torch.bfloat16: 2.5e-2,
 }
-MEAN_TOLERANCE = {torch.float32: 2e-6, torch.bfloat16: 6e-3}
+# mean |difference| of a row, averaged over the rows; observed up to 1.0e-6 and 2.0e-3
+MEAN_TOLERANCE = {torch.float32: 2e-6, torch.bfloat16: 3e-3}
 
 
 def whole(requests: dict) -> list[dict]:

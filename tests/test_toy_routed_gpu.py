@@ -50,6 +50,8 @@ def register_routed_parts():
         """Half-split rotation by the angles of position / STRETCH: the tables the attention kernels
         read are this part's own."""
 
+        pairing = "half_split"          # the pairing the fused q/k kernels apply to the tables
+
         def __init__(self, ctx, *, head_dim, theta, max_positions):
             self.head_dim, self.theta, self.max_positions = head_dim, float(theta), max_positions
             self.device = ctx.device
@@ -182,3 +184,24 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
                         ("portions", rh.portions(requests, seed=5, sizes=(2, 3, 7, 13))),
                         ("mixed", rh.mixed(requests, seed=6, live=3, decode_tail=4, sizes=(2, 5, 9)))):
         rh.compare(rh.run_steps(runner, steps), expected, torch.float32, what=f"routed {name}")
+
+
+def test_a_position_encoding_with_another_pairing_is_refused_by_the_fused_kernels(tmp_path):
+    """The attention kernels rotate q and k themselves, with the half-split pairing: a position part
+    that pairs elements otherwise must not reach them with its tables (wrong results would be silent)."""
+    from tinyvllm_b200.config.registry import read_model_config
+    from tinyvllm_b200.engine.model import Model
+    from tinyvllm_b200.engine.step import StepEntry, StepRunner
+    from tinyvllm_b200.ops.kernels import KernelError
+    from tinyvllm_b200.weights.random_init import write_model_folder
+
+    config_class = register_routed_parts()
+    folder = write_model_folder(tmp_path / "routed", config_class(ROUTED), seed=11)
+    model = Model(read_model_config(folder).to_spec(), device="cuda:0", dtype=torch.float32).load(folder)
+    model.blocks[0].mixer.position.pairing = "interleaved"
+    runner = StepRunner(model, page_size=4, num_pages=40, max_requests=2)
+    runner.open("r")
+    with pytest.raises(KernelError, match="half-split pairing.*'interleaved'"):
+        runner.run([StepEntry("r", (1, 2, 3), (2,))])
+    runner.manager.check()
+    assert all(pool.free_count == pool.num_pages for pool in runner.manager.pools)        # the step's pages went back

@@ -115,6 +115,11 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
     position = mixer.position
     cos = sin = None
     if position is not None:
+        if getattr(position, "pairing", None) != "half_split":
+            raise kernels.KernelError(
+                f"the attention kernels rotate q and k from tables with the half-split pairing; the position "
+                f"part {type(position).__name__} declares pairing {getattr(position, 'pairing', None)!r} (a part "
+                "with another pairing needs a kernel of its own, or a mixer that applies it before attention)")
         cos, sin = position.cos, position.sin
     heads = dict(num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.head_dim)
     tiled = qkv.dtype == torch.bfloat16

@@ -12,7 +12,11 @@ norm            ``forward(x) -> y`` and ``add(x, residual) -> (y, new_residual)`
                 that is y = x * rsqrt(mean(x^2) + eps) * weight with attributes
                 ``weight`` [width] and ``eps`` may set ``folds_into_product = True``:
                 a projection right behind it may then apply it inside its own kernel
-position        ``prepare(ctx)``; handed to the mixer that asked for it
+position        built by the mixer that names it in its spec; ``finalize()`` makes its
+                tables.  One whose tables the fused q/k kernels are to apply has
+                float32 ``cos`` and ``sin`` [positions, head_dim / 2] and declares
+                ``pairing = "half_split"``; any other pairing is refused by those
+                kernels with a clear error (it needs a kernel, or a mixer, of its own)
 mixer           ``cache_need() -> KVNeed | StateNeed | None`` and
                 ``forward(x, ctx, run) -> y`` where ``ctx`` is the step's
                 :class:`StepContext` and ``run`` the index in the run list;

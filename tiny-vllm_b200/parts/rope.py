@@ -19,6 +19,11 @@ _TABLES: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 class RopeHalfSplit(Part):
+    # How the fused q/k kernels pair the elements of a head: element j of the first half with
+    # element j of the second, rotated by position * inv_freq_j read from the float32 tables
+    # ``cos`` and ``sin``.  A position part with another pairing must not hand its tables to them.
+    pairing = "half_split"
+
     def __init__(self, ctx: BuildContext, *, head_dim: int, theta: float, max_positions: int) -> None:
         if head_dim % 2:
             raise ValueError("rotary encoding needs an even head size")
