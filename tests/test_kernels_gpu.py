@@ -478,7 +478,11 @@ def test_attention_prefill_tc_refuses():
 
 @pytest.mark.parametrize("window", [None, 150])
 @pytest.mark.parametrize("shape", [(4, 2, 64, 16, 8), (8, 2, 128, 16, 4), (2, 2, 128, 7, 1),
-                                   (8, 1, 256, 32, 5), (16, 8, 128, 16, 8), (16, 2, 128, 16, 8), (8, 1, 64, 8, 3)])
+                                   (8, 1, 256, 32, 5), (16, 8, 128, 16, 8), (16, 2, 128, 16, 8), (8, 1, 64, 8, 3),
+                                   # groups of 5 (40 q heads on 8 kv heads), 3, 6 and 7: fewer heads than the tile
+                                   # holds; 12 = two CTAs of 6; 10 at head size 256 = two of 5 would not fit: five of 2
+                                   (10, 2, 128, 16, 4), (3, 1, 64, 16, 2), (12, 2, 128, 16, 8), (7, 1, 128, 32, 3),
+                                   (24, 2, 64, 16, 2), (10, 1, 256, 16, 2)])
 def test_attention_decode_fused(shape, window):
     """Raw projection in, attention out: against q/k norm + rotation + attention of the plain
     functions, with the new key and value checked in the cache."""
@@ -535,7 +539,8 @@ def test_attention_decode_padding_and_unsupported():
     from tinyvllm_b200.ops.kernels import KernelError
     assert k().attention_decode_supports(128, 16, 8, 8)
     assert not k().attention_decode_supports(48, 4, 2, 8)
-    assert not k().attention_decode_supports(128, 6, 2, 8)       # groups of 3
+    assert k().attention_decode_supports(128, 6, 2, 8)           # groups of 3 run on the tile for 4
+    assert not k().attention_decode_supports(128, 7, 2, 8)       # no whole number of q heads per kv head
     assert not k().attention_decode_supports(128, 16, 8, 9)
     with pytest.raises(KernelError, match="does not take"):
         k().attention_decode(torch.zeros(1, 4 * 48, dtype=torch.bfloat16, device=DEV), num_q=2, num_kv=1,

@@ -4,8 +4,8 @@ The tiny configurations never reach the kernels' real-size choices: the tcgen05 
 thousands of columns, library products for weights of tens of megabytes, eight query heads of a
 key-value head in one CTA of the decode attention, clusters of eight CTAs a request, a vocabulary
 of 151,936 in the head.  Here two layers of the Qwen3-0.6B sizes (full vocabulary, tied head), two
-of the 8B sizes and one of the 32B sizes (query width 8192 beside a hidden width of 5120, untied
-head) are replayed in every way of cutting, in 32-bit and in bfloat16, and compared with the
+of the 8B sizes, one of the 32B sizes (query width 8192 beside a hidden width of 5120, untied
+head) and one of the 14B sizes (five query heads on a key-value head) are replayed in every way of cutting, in 32-bit and in bfloat16, and compared with the
 whole-sequence oracle.  Weights are stored in bfloat16 so that both paths and the oracle read the
 same values; logits are wanted at a subset of the places to keep the oracle affordable.
 """
@@ -33,10 +33,13 @@ def wide_configs():
                           num_attention_heads=32, num_key_value_heads=8, tie_word_embeddings=False, **common),
         "w32": Qwen3Config(vocab_size=5000, hidden_size=5120, intermediate_size=25600, num_hidden_layers=1,
                            num_attention_heads=64, num_key_value_heads=8, tie_word_embeddings=False, **common),
+        # the 14B sizes: five q heads on a kv head (the decode kernel's tile for eight, five rows used)
+        "w14": Qwen3Config(vocab_size=4000, hidden_size=5120, intermediate_size=17408, num_hidden_layers=1,
+                           num_attention_heads=40, num_key_value_heads=8, tie_word_embeddings=False, **common),
     }
 
 
-NAMES = ("w06", "w8", "w32")
+NAMES = ("w06", "w8", "w32", "w14")
 LENGTHS = (6, 150, 70, 300, 41, 120, 33)
 
 

@@ -128,7 +128,9 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const int* __restrict__ slots, bf16* __restrict__ key_cache,
                         bf16* __restrict__ value_cache, const int* __restrict__ block_tables,
                         int table_stride, int page_size, bf16* __restrict__ out, int num_q, int num_kv,
-                        int window, float scale, int write_cache, int warp_slot_capacity) {
+                        int window, float scale, int write_cache, int warp_slot_capacity, int heads_here) {
+    // heads_here <= HPB q heads of one kv head are this CTA's (HPB is what the tile and the shared
+    // arrays hold; rows past heads_here stay zero): groups of 3, 5, 6 or 7 heads run on the next size up
     constexpr int CPR = HEAD_DIM / 8;          // 16-byte chunks of a key's row
     constexpr int KPI = 32 / CPR;              // keys a warp copies per instruction
     constexpr int WARP_KEYS = DEC_TILE;
@@ -141,9 +143,9 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     const int split = blockIdx.x;              // = rank in the cluster
     const int splits = gridDim.x;
     const int group = num_q / num_kv;
-    const int blocks_per_kv = group / HPB;
+    const int blocks_per_kv = group / heads_here;
     const int kv_head = blockIdx.y / blocks_per_kv;
-    const int first_q_head = kv_head * group + (blockIdx.y % blocks_per_kv) * HPB;
+    const int first_q_head = kv_head * group + (blockIdx.y % blocks_per_kv) * heads_here;
     const int request = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = num_q + 2 * num_kv;
@@ -153,7 +155,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     if (row < 0 || position < 0) {              // padding: the whole cluster leaves together
         pdl_wait();
         if (split == 0)
-            for (int i = threadIdx.x; i < HPB * HEAD_DIM; i += blockDim.x) out_row[i] = __float2bfloat16_rn(0.0f);
+            for (int i = threadIdx.x; i < heads_here * HEAD_DIM; i += blockDim.x) out_row[i] = __float2bfloat16_rn(0.0f);
         return;
     }
 
@@ -227,11 +229,11 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         const int table_row = min(position, table_positions - 1);
         const float* cos_row = cos_table ? cos_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
         const float* sin_row = sin_table ? sin_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
-        for (int job = warp; job < (cached_new ? HPB : HPB + 2); job += DEC_WARPS) {
-            if (job < HPB) {
+        for (int job = warp; job < (cached_new ? heads_here : heads_here + 2); job += DEC_WARPS) {
+            if (job < heads_here) {
                 norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(first_q_head + job) * HEAD_DIM, q_weight, eps,
                                               cos_row, sin_row, sh.q[job], lane);
-            } else if (job == HPB) {
+            } else if (job == heads_here) {
                 norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(num_q + kv_head) * HEAD_DIM, k_weight, eps,
                                               cos_row, sin_row, sh.k_new, lane);
             } else {
@@ -256,7 +258,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                 }
             }
         }
-        for (int h = warp; h < HPB; h += DEC_WARPS) {       // score of the new key, one warp a head
+        for (int h = warp; h < heads_here; h += DEC_WARPS) {       // score of the new key, one warp a head
             float dot = 0.0f;
             for (int i = lane; i < HEAD_DIM; i += 32) dot = __fmaf_rn(sh.q[h][i], sh.k_new[i], dot);
             dot = warp_sum(dot);
@@ -270,7 +272,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
 #pragma unroll
     for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
         q_frag[ks][0] = q_frag[ks][1] = 0u;
-        if (g < HPB) {
+        if (g < heads_here) {
             const float* qh = sh.q[g] + ks * 16 + 2 * t4;
             q_frag[ks][0] = pack_bf16x2(qh[0], qh[1]);
             q_frag[ks][1] = pack_bf16x2(qh[8], qh[9]);
@@ -351,7 +353,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     pdl_launch_dependents();
 
     // ---- the warps' partial results, merged below in a fixed order
-    if (g < HPB) {
+    if (g < heads_here) {
 #pragma unroll
         for (int n = 0; n < HEAD_DIM / 8; ++n) {
             sh.warp_o[warp][g][n * 8 + 2 * t4] = o_run[n][0];
@@ -362,7 +364,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     __syncthreads();
     cluster_wait();
     DecodeShared<HEAD_DIM, HPB, DEC_WARPS>* first_cta = cluster.map_shared_rank(&sh, 0);
-    for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
+    for (int index = threadIdx.x; index < heads_here * HEAD_DIM; index += blockDim.x) {
         const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
         float m = -INFINITY;
 #pragma unroll
@@ -390,7 +392,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     // ---- the first CTA merges the pieces in rank order
     cluster.sync();
     if (split == 0) {
-        for (int index = threadIdx.x; index < HPB * HEAD_DIM; index += blockDim.x) {
+        for (int index = threadIdx.x; index < heads_here * HEAD_DIM; index += blockDim.x) {
             const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
             float l = 0.0f, o = 0.0f;
             if constexpr (HPB >= 2) {
@@ -441,29 +443,36 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
                          void* value_cache, const int* block_tables, int table_stride, int page_size,
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
-                         int splits, int write_cache, int max_context, int pdl, cudaStream_t stream) {
+                         int splits, int write_cache, int max_context, int pdl, cudaStream_t stream, int heads_here) {
     auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, W>;
     const int warp_slots = decode_warp_slot_capacity<HEAD_DIM, DEC_WARPS>(max_context, splits);
     const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB, DEC_WARPS>) + (size_t)DEC_WARPS * warp_slots * sizeof(int);
     if (shared > 200 * 1024) return TVB_BAD_ARGUMENT;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (e != cudaSuccess) return (int)e;
-    TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / HPB), requests), dim3(DEC_WARPS * 32), shared,
+    TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / heads_here), requests), dim3(DEC_WARPS * 32), shared,
                      stream, pdl, splits);
     e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
                            cos_table, sin_table, table_positions, positions, token_row, slots,
                            (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
-                           (bf16*)out, num_q, num_kv, window, scale, write_cache, warp_slots);
+                           (bf16*)out, num_q, num_kv, window, scale, write_cache, warp_slots, heads_here);
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
-// 1 if the kernel takes this shape: head sizes 64, 128, 256; groups of 1, 2 or a multiple of 4
-// (a CTA serves 1, 2, 4 or, where the group is a multiple of 8 and the head size at most 128, 8 q heads).
+// q heads of one kv head that a CTA serves: as many of the group as a tile holds (8 at head sizes
+// up to 128, else 4), so that the keys are read as few times as possible: the largest divisor of the
+// group within that.  A group of 5 (40 q heads on 8 kv heads) gives 5, a group of 12 gives 6.
+static int decode_heads_per_cta(int group, int head_dim) {
+    const int most = head_dim <= 128 ? 8 : 4;
+    for (int heads = most < group ? most : group; heads > 1; --heads)
+        if (group % heads == 0) return heads;
+    return 1;
+}
+
+// 1 if the kernel takes this shape: head sizes 64, 128, 256; any whole number of q heads per kv head.
 extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv, int splits) {
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return 0;
-    if (num_kv <= 0 || num_q % num_kv) return 0;
-    const int group = num_q / num_kv;
-    if (!(group == 1 || group == 2 || group % 4 == 0)) return 0;
+    if (num_kv <= 0 || num_q <= 0 || num_q % num_kv) return 0;
     return splits >= 1 && splits <= DEC_MAX_SPLITS;
 }
 
@@ -487,9 +496,10 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
         requests > 65535 || max_context <= 0)
         return TVB_BAD_ARGUMENT;
     const int group = num_q / num_kv;
-    // q heads a CTA serves (they share its keys): with 8 and more heads per kv head a CTA takes 8, so
-    // that no key is read twice; that costs residency (87 KB of shared memory at head size 128)
-    const int hpb = (group % 8 == 0 && head_dim <= 128) ? 8 : (group % 4 == 0 ? 4 : group);
+    // q heads a CTA serves (they share its keys); the tile that holds them is the next of 1, 2, 4, 8.
+    // Eight heads cost residency (87 KB of shared memory at head size 128) but no key is read twice.
+    const int heads_here = decode_heads_per_cta(group, head_dim);
+    const int hpb = heads_here <= 1 ? 1 : heads_here <= 2 ? 2 : heads_here <= 4 ? 4 : 8;
     cudaStream_t s = (cudaStream_t)stream;
     // Four warps a CTA keep four CTAs on an SM, which is what counts when the grid fills the GPU;
     // a grid of fewer CTAs than SMs (one or two requests) is faster with eight warps a CTA, each
@@ -501,10 +511,10 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
             cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
             sm_count = 0;
     }
-    const bool wide = head_dim <= 128 && (long long)requests * num_kv * (group / hpb) * splits <= sm_count;
+    const bool wide = head_dim <= 128 && (long long)requests * num_kv * (group / heads_here) * splits <= sm_count;
 #define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
                     token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
-                    requests, num_q, num_kv, window, scale, splits, write_cache, max_context, pdl, s
+                    requests, num_q, num_kv, window, scale, splits, write_cache, max_context, pdl, s, heads_here
 #define DECODE_BY_WARPS(D, H, WT)                                       \
     do {                                                                \
         if (wide) return launch_decode<D, H, 8, WT>(DECODE_ARGS);       \
