@@ -226,6 +226,9 @@ def test_a_failure_while_lowering_gives_the_pages_back_and_the_engine_goes_on():
         for done in engine.step().finished:
             outputs[done.request_id] = done
     assert outputs[0].finish_reason == "length" and len(outputs[0].output_token_ids) == 4
+    stats = engine.stats()
+    assert stats["lowering_failures"] == 1 and stats["prompt_tokens"] == 19 and stats["decode_tokens"] == 3
+    assert stats["pages_free"] == stats["pages_total"] and stats["decoding"] == 0
     # the same tokens as an engine that never failed
     other, _, _ = make_engine(1)
     other.submit(list(range(1, 20)), SamplingParams(max_new_tokens=4, ignore_eos=True), request_id=0)

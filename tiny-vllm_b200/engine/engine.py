@@ -17,7 +17,9 @@ arrival time ahead of the clock and ``step`` may be told the time
 
 from __future__ import annotations
 
+import contextlib
 import logging
+import os
 import time
 from dataclasses import dataclass
 from typing import Sequence
@@ -35,6 +37,22 @@ from .scheduler import Request, RequestStatus, ScheduledStep, Scheduler
 from .step import StepEntry, StepRunner
 
 log = logging.getLogger("tinyvllm_b200")
+
+# TINYVLLM_B200_NVTX=1: every call of Engine.step and its phases (schedule, lower, launch and read,
+# commit; a decode run's launches and reads) are NVTX ranges, for a timeline in Nsight Systems
+NVTX = os.environ.get("TINYVLLM_B200_NVTX", "0") == "1"
+
+
+@contextlib.contextmanager
+def _range(name: str):
+    if not NVTX:
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
 
 
 @dataclass(frozen=True)
@@ -128,6 +146,9 @@ class Engine:
         self._last_now: int | None = None
         self.steps_run = 0
         self.graph_steps = 0
+        self.prompt_tokens = 0          # tokens of prompt portions run so far
+        self.decode_tokens = 0          # single tokens run so far (one per request and decode step)
+        self.lowering_failures = 0      # steps that failed before launch and were rolled back
         self._run = None            # (scheduled run, run in flight on the graphs, request ids) between calls
 
     # ---------------------------------------------------------- construction
@@ -217,6 +238,22 @@ class Engine:
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
 
+    def stats(self) -> dict:
+        """Counters since the engine was made, and what the cache holds now."""
+        manager = self.runner.manager
+        runner = self.runner
+        return {
+            "steps": self.steps_run, "decode_graph_steps": self.graph_steps,
+            "prompt_tokens": self.prompt_tokens, "decode_tokens": self.decode_tokens,
+            "lowering_failures": self.lowering_failures,
+            "step_graphs": len(getattr(runner, "_step_graphs", ())),
+            "waiting": len(self.scheduler.waiting), "prefilling": len(self.scheduler.prefilling),
+            "decoding": len(self.scheduler.decoding),
+            "pages_free": [pool.free_count for pool in manager.pools],
+            "pages_total": [pool.num_pages for pool in manager.pools],
+            "state_slots_free": manager.slots.free_count,
+        }
+
     @property
     def in_run(self) -> bool:
         """Whether a run of decode steps is in flight (its remaining steps are read by ``step``)."""
@@ -250,23 +287,33 @@ class Engine:
             if run is not None:
                 self._start_run(run)
                 return self._continue_run(now if explicit else None)
-        scheduled = self.scheduler.schedule(now)
+        with _range("schedule"):
+            scheduled = self.scheduler.schedule(now)
         if scheduled is None:
             return StepEvents((), tuple(RequestOutput.of(r) for r in self.scheduler.take_finished()))
         try:
-            lowered = self._lower(scheduled)
+            with _range("lower"):
+                lowered = self._lower(scheduled)
         except BaseException:
             # nothing of the step was launched: its pages go back, the requests keep their places
             # and the next call plans them again
             self.scheduler.abort_step(scheduled)
+            self.lowering_failures += 1
             raise
         try:
-            sampled = self._launch(scheduled, lowered)
-            events = self.scheduler.commit(scheduled, sampled, now if explicit else self._now(None))
+            with _range("launch and read"):
+                sampled = self._launch(scheduled, lowered)
+            with _range("commit"):
+                events = self.scheduler.commit(scheduled, sampled, now if explicit else self._now(None))
         except BaseException as exc:
             self._fail_stop(exc, scheduled.cache_plan)
             raise
         self.steps_run += 1
+        for item in scheduled.items:
+            if item.count == 1 and item.sample and item.start > 0:
+                self.decode_tokens += 1
+            else:
+                self.prompt_tokens += item.count
         finished = tuple(RequestOutput.of(r) for r in self.scheduler.take_finished())
         return StepEvents(tuple(events), finished)
 
@@ -315,15 +362,19 @@ class Engine:
                 return bool(run.closing or scheduler.waiting or scheduler.prefilling)
 
             def read_one() -> None:
-                tokens = flight.read()
+                with _range("read a step of the run"):
+                    tokens = flight.read()
                 kernels.check_finished_launches()
                 when = fixed_now if fixed_now is not None else self._now(None)
-                events.extend(scheduler.commit_run_step(run, dict(zip(ids, tokens)), when))
+                got = scheduler.commit_run_step(run, dict(zip(ids, tokens)), when)
+                events.extend(got)
                 self.steps_run += 1
                 self.graph_steps += 1
+                self.decode_tokens += len(got)
 
             while flight.launched < run.steps and not must_stop() and flight.launched < flight.read_steps + self.RUN_AHEAD:
-                flight.launch()
+                with _range("launch a step of the run"):
+                    flight.launch()
             if flight.read_steps < flight.launched:
                 read_one()
             if flight.launched == run.steps or must_stop():
