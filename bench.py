@@ -15,7 +15,8 @@ weights, bfloat16.
 * ``prefill``: one prompt of 2,048 tokens through the step function.
 * ``roofline``: bytes a decode step must read (every weight once + the cache of the live
   requests) / time / measured HBM bandwidth.
-* ``points``: decode at batch 1 and 64.
+* ``points``: decode at batch 1 and 64; decode at batch 8 from a context of 16,384 tokens (with its
+  fraction of the HBM roofline) and a prefill of 8,192 tokens (with its fraction of the tensor peak).
 
 Every step reads more than the 126 MB of L2 (the weights alone are 1.19 GB), so the inputs are
 larger than L2 and no flush is needed between timed steps.
@@ -277,7 +278,7 @@ def clear_engine(engine) -> None:
 
 
 def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloat16", eager: bool = False,
-                new_tokens: int = 512):
+                new_tokens: int = 512, prompt_tokens: int = PROMPT_TOKENS):
     from tinyvllm_b200 import EngineConfig
     from tinyvllm_b200.engine.engine import Engine
     from tinyvllm_b200.models import Qwen3Config
@@ -285,8 +286,8 @@ def make_engine(folder: str, layers: int, max_num_seqs: int, dtype: str = "bfloa
     config = Qwen3Config(**{**MODEL, "num_hidden_layers": layers})
     Path(folder, "config.json").write_text(json.dumps(config.to_json()))
     kv_bytes_per_token = 2 * layers * MODEL["num_key_value_heads"] * MODEL["head_dim"] * 2
-    context = max(CONTEXT_LIMIT, PROMPT_TOKENS + new_tokens + 16)     # more steps than the workload's 256 fit too
-    kv_budget = kv_bytes_per_token * (max_num_seqs * (PROMPT_TOKENS + new_tokens + 64) + 4096)
+    context = max(CONTEXT_LIMIT, prompt_tokens + new_tokens + 16)     # more steps than the workload's 256 fit too
+    kv_budget = kv_bytes_per_token * (max_num_seqs * (prompt_tokens + new_tokens + 64) + 8192 + 4096)
     engine_config = EngineConfig(
         model=folder, dtype=dtype, weights="random", seed=0, max_model_len=context,
         max_num_seqs=max_num_seqs, max_num_batched_tokens=max(4096, max_num_seqs),
@@ -304,6 +305,10 @@ def decode_bytes(engine, batch: int, mean_context: float) -> float:
     return weights + batch * mean_context * per_token
 
 
+LONG_CONTEXT = 16384           # context of the long-context decode point
+LONG_PREFILL = 8192            # tokens of the long prefill point
+
+
 def prefill_flops(layers: int, tokens: int) -> float:
     h, i, v = MODEL["hidden_size"], MODEL["intermediate_size"], MODEL["vocab_size"]
     nq, nkv, d = MODEL["num_attention_heads"], MODEL["num_key_value_heads"], MODEL["head_dim"]
@@ -312,7 +317,8 @@ def prefill_flops(layers: int, tokens: int) -> float:
     return 2.0 * tokens * linear + 2.0 * attention + 2.0 * h * v
 
 
-def run_decode(engine, batch: int, steps: int, warmup: int, sampler: ClockSampler | None):
+def run_decode(engine, batch: int, steps: int, warmup: int, sampler: ClockSampler | None,
+               prompt_tokens: int = PROMPT_TOKENS):
     """Device-timed and end-to-end decode of ``batch`` requests; a dict of the figures."""
     import torch
 
@@ -327,7 +333,7 @@ def run_decode(engine, batch: int, steps: int, warmup: int, sampler: ClockSample
         """``batch`` requests with their prompts in the cache, about to decode their second token."""
         clear_engine(engine)
         for _ in range(batch):
-            engine.submit(random_prompt(rng, PROMPT_TOKENS), sampling)
+            engine.submit(random_prompt(rng, prompt_tokens), sampling)
         while engine.scheduler.prefilling or engine.scheduler.waiting:      # untimed prefill
             engine.step()
         assert len(engine.scheduler.decoding) == batch
@@ -404,7 +410,7 @@ def run_decode(engine, batch: int, steps: int, warmup: int, sampler: ClockSample
     }
 
 
-def run_prefill(engine, repeats: int = 5):
+def run_prefill(engine, repeats: int = 5, tokens: int = PROMPT_TOKENS):
     import torch
 
     from tinyvllm_b200.engine.step import StepEntry
@@ -414,9 +420,9 @@ def run_prefill(engine, repeats: int = 5):
     times = []
     with torch.inference_mode():
         for index in range(repeats + 2):
-            rid = f"prefill{index}"
+            rid = f"prefill{tokens}-{index}"
             runner.open(rid)
-            entry = StepEntry(rid, tuple(random_prompt(rng, PROMPT_TOKENS)), (PROMPT_TOKENS - 1,))
+            entry = StepEntry(rid, tuple(random_prompt(rng, tokens)), (tokens - 1,))
             torch.cuda.synchronize()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
@@ -484,6 +490,24 @@ def headline(args, warmup: int) -> int:
                     del point_engine
                     gc.collect()
                     torch.cuda.empty_cache()
+            # further context lengths: decode at batch 8 from a context of 16,384 and a prefill of 8,192
+            with tempfile.TemporaryDirectory() as other:
+                long_steps = min(args.steps, 32)
+                long_engine = make_engine(other, args.layers, 8, new_tokens=new_tokens_of(long_steps, warmup),
+                                          prompt_tokens=LONG_CONTEXT)
+                result = run_decode(long_engine, 8, long_steps, warmup, None, prompt_tokens=LONG_CONTEXT)
+                long_bytes = decode_bytes(long_engine, 8, result["mean_context"])
+                points["decode_b8_ctx16k"] = round(result["tokens_per_s"], 1)
+                points["decode_b8_ctx16k_hbm_frac"] = round(
+                    long_bytes / (result["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4)
+                long_ms = run_prefill(long_engine, repeats=3, tokens=LONG_PREFILL)
+                points["prefill_8192"] = round(LONG_PREFILL / (long_ms / 1e3), 1)
+                points["prefill_8192_frac"] = round(
+                    prefill_flops(args.layers, LONG_PREFILL) / (long_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)
+                long_engine.close()
+                del long_engine
+                gc.collect()
+                torch.cuda.empty_cache()
     sampler.stop()
 
     achieved_gbs = bytes_step / (main_run["ms_per_step"] / 1e3) / 1e9
