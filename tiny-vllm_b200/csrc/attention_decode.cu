@@ -14,18 +14,22 @@
 //
 // Every warp walks its keys in tiles of 8 through a ring of cp.async stages of its own in shared
 // memory (16-byte chunks swizzled by the key, so that ldmatrix reads them without bank conflicts);
-// the cache slots of its keys are looked up once, up front, and the first stages are in flight
+// the cache slots of its keys are looked up once, up front, and the first stage is in flight
 // before the kernel waits for the projection (keys and values already in the cache do not depend
-// on it).  The q heads of the CTA are the rows of an m16n8k16 tensor-core tile (rows past HPB are
+// on it, nor do the norm weights and the rotation's table row, which are asked for up front too).
+// The q heads of the CTA are the rows of an m16n8k16 tensor-core tile (rows past HPB are
 // zero): S = Q K^T and O += P V are mma.sync with float32 accumulators (the second product's k of
 // 16 is the tile's 8 keys and 8 zeros), a quarter of the instructions of a dot product spread
-// over lanes.  Small tiles and four warps keep a CTA's shared memory at 47 KB, so that four CTAs
+// over lanes.  Small tiles and four warps keep a CTA's shared memory near 42 KB, so that four CTAs
 // share an SM: measured, residency counts for more here than instructions (tiles of 16 keys were
 // slower than the dot products they replaced, tiles of 8 are faster).  Softmax is float32; P is
 // rounded to bfloat16 for the second product while the denominator sums the unrounded values (as
-// tinyvllm/kernels/paged_decode.cu:322-356 does).  The size of a split follows from the request's
-// own position (and window) alone, so its result does not depend on the batch it is in.
+// tinyvllm/kernels/paged_decode.cu:322-356 does).  The size of a piece follows from the request's
+// own position (and window) alone and is a whole number of tiles: pieces of a request differ by
+// one tile at most, so the CTAs of a cluster reach its barrier together (pieces of whole multiples
+// of 64 keys left the last CTAs of a cluster with little or nothing to do, and the others waiting).
 #include <cooperative_groups.h>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -35,24 +39,46 @@ namespace cg = cooperative_groups;
 #define DEC_STAGES 2        // stages of each warp's ring of keys and values in shared memory
 #define DEC_MAX_SPLITS 8
 
-template <int HEAD_DIM, int HPB, int DEC_WARPS>
-struct DecodeShared {
-    float q[HPB][HEAD_DIM];            // normalised, rotated, rounded q heads
-    float k_new[HEAD_DIM];             // the new key and value as stored (rounded)
-    float v_new[HEAD_DIM];
-    float s_new[HPB];                  // score of the new key for each head
-    float warp_o[DEC_WARPS][HPB][HEAD_DIM];
-    float warp_m[DEC_WARPS][HPB];
-    float warp_l[DEC_WARPS][HPB];
-    // partials of every CTA of the cluster; only the first CTA's copy is used, the others
-    // write theirs into it
-    float part_o[DEC_MAX_SPLITS][HPB][HEAD_DIM];
-    float part_m[DEC_MAX_SPLITS][HPB];
-    float part_l[DEC_MAX_SPLITS][HPB];
-    // per warp: stages of (keys, values) [16 keys][HEAD_DIM] bfloat16, chunk c of key k at c ^ (k & 7)
-    uint4 ring[DEC_WARPS][DEC_STAGES][2][DEC_TILE * HEAD_DIM / 8];
-    // int slot[DEC_WARPS][warp_slot_capacity] follows
+// Where things lie in a CTA's dynamic shared memory (byte offsets; worked out by the launcher).
+// Only what a launch needs is there: partials for `splits` CTAs, not for the largest cluster; the
+// list of cache slots holds one entry per tile of 8 keys where a tile lies inside one page (pages
+// of a multiple of 8 tokens), else one per key; and the warps' partial outputs reuse the rings
+// once the keys have been walked.  The less a CTA takes, the more of them share an SM (up to the
+// four that the registers allow) whatever the context limit, the cluster size and the number of q
+// heads a CTA serves.  (A third stage of the rings, which this leaves room for, was measured and
+// is slower at every batch size, also where it costs no residency.)
+struct DecodeLayout {
+    int q;            // float [HPB][HEAD_DIM]: normalised, rotated, rounded q heads
+    int v_new;        // float [HEAD_DIM]: the new value as stored
+    int s_new;        // float [HPB]: score of the new key for each head
+    int warp_m;       // float [DEC_WARPS][HPB]
+    int warp_l;
+    int part_m;       // float [splits][HPB]: partials of every CTA of the cluster; only the first CTA's
+    int part_l;       //   copy is used, the others write theirs into it
+    int part_o;       // float [splits][HPB][HEAD_DIM]
+    int ring;         // per warp: DEC_STAGES x (keys, values) x [8 keys][HEAD_DIM] bfloat16, chunk c of key k at
+                      //   c ^ (k & 7); after the loop the warp's partial output float [HPB][HEAD_DIM] lies here
+    int slots;        // int [DEC_WARPS][warp_slot_capacity]
+    int total;        // bytes
 };
+
+static DecodeLayout decode_layout(int head_dim, int hpb, int warps, int splits, int warp_slots) {
+    DecodeLayout l;
+    int at = 0;
+    auto take = [&](int bytes) { const int here = at; at += (bytes + 15) / 16 * 16; return here; };
+    l.q = take(hpb * head_dim * 4);
+    l.v_new = take(head_dim * 4);
+    l.s_new = take(hpb * 4);
+    l.warp_m = take(warps * hpb * 4);
+    l.warp_l = take(warps * hpb * 4);
+    l.part_m = take(splits * hpb * 4);
+    l.part_l = take(splits * hpb * 4);
+    l.part_o = take(splits * hpb * head_dim * 4);
+    l.ring = take(warps * DEC_STAGES * 2 * DEC_TILE * head_dim * 2);
+    l.slots = take(warps * warp_slots * 4);
+    l.total = at;
+    return l;
+}
 
 __device__ __forceinline__ void dec_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -70,57 +96,99 @@ __device__ __forceinline__ void dec_mma(float (&d)[4], uint32_t a0, uint32_t a2,
                  : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
 }
 
-// RMSNorm + half-split rotation of one head by one warp; result rounded to bfloat16, as float.
+// One head of the new token in a warp's registers: lane l holds elements l + 32 i of the first half
+// (a) and of the second half (b).  The steps below are RMSNorm and half-split rotation with the
+// roundings of tinyvllm/kernels/pointwise.cu:324-450 (every intermediate rounded to bfloat16).
+template <int HEAD_DIM>
+struct HeadRegs {
+    static constexpr int HALF = HEAD_DIM / 2;
+    static constexpr int PAIRS = (HALF + 31) / 32;
+    float a[PAIRS], b[PAIRS];
+};
+
+// What the steps need beside the head itself; it does not depend on the kernel before this one, so
+// it is asked for before the wait on that kernel.
+template <int HEAD_DIM>
+struct HeadConstants {
+    HeadRegs<HEAD_DIM> q_weight, k_weight, cos, sin;      // cos, sin: rounded to bfloat16
+};
+
+template <int HEAD_DIM, typename W>
+__device__ __forceinline__ void load_head_weight(HeadRegs<HEAD_DIM>& to, const W* __restrict__ weight, int lane) {
+#pragma unroll
+    for (int i = 0; i < HeadRegs<HEAD_DIM>::PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        const bool in = weight != nullptr && j < HeadRegs<HEAD_DIM>::HALF;
+        to.a[i] = in ? to_float<W>(weight[j]) : 1.0f;
+        to.b[i] = in ? to_float<W>(weight[j + HeadRegs<HEAD_DIM>::HALF]) : 1.0f;
+    }
+}
+
 // `src` was written by the kernel before this one: read with plain coherent loads that are all in
 // flight together (volatile ones would go one after the other, a latency each).
-template <int HEAD_DIM, typename W>
-__device__ __forceinline__ void norm_rotate_head(const unsigned short* src, const W* __restrict__ weight,
-                                                 float eps, const float* __restrict__ cos_row,
-                                                 const float* __restrict__ sin_row, float* __restrict__ dst,
-                                                 int lane) {
-    constexpr int HALF = HEAD_DIM / 2;
-    constexpr int PAIRS = (HALF + 31) / 32;
-    float a[PAIRS], b[PAIRS];
-    float squares = 0.0f;
+template <int HEAD_DIM>
+__device__ __forceinline__ void load_head(HeadRegs<HEAD_DIM>& to, const unsigned short* src, int lane) {
 #pragma unroll
-    for (int i = 0; i < PAIRS; ++i) {
+    for (int i = 0; i < HeadRegs<HEAD_DIM>::PAIRS; ++i) {
         const int j = lane + 32 * i;
-        a[i] = b[i] = 0.0f;
-        if (j < HALF) {
-            a[i] = bf16_bits_to_float(ld_global_u16(src + j));
-            b[i] = bf16_bits_to_float(ld_global_u16(src + j + HALF));
-            squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(a[i], a[i]), __fmul_rn(b[i], b[i])));
+        const bool in = j < HeadRegs<HEAD_DIM>::HALF;
+        to.a[i] = in ? bf16_bits_to_float(ld_global_u16(src + j)) : 0.0f;
+        to.b[i] = in ? bf16_bits_to_float(ld_global_u16(src + j + HeadRegs<HEAD_DIM>::HALF)) : 0.0f;
+    }
+}
+
+template <int HEAD_DIM>
+__device__ __forceinline__ void norm_rotate_head(HeadRegs<HEAD_DIM>& x, bool normed, const HeadRegs<HEAD_DIM>& weight,
+                                                 float eps, bool rotated, const HeadRegs<HEAD_DIM>& cos,
+                                                 const HeadRegs<HEAD_DIM>& sin) {
+    constexpr int PAIRS = HeadRegs<HEAD_DIM>::PAIRS;
+    if (normed) {
+        float squares = 0.0f;
+#pragma unroll
+        for (int i = 0; i < PAIRS; ++i)
+            squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(x.a[i], x.a[i]), __fmul_rn(x.b[i], x.b[i])));
+        squares = warp_sum(squares);
+        const float inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(squares, 1.0f / (float)HEAD_DIM), eps)));
+#pragma unroll
+        for (int i = 0; i < PAIRS; ++i) {
+            x.a[i] = round_to<bf16>(__fmul_rn(round_to<bf16>(__fmul_rn(x.a[i], inverse_rms)), weight.a[i]));
+            x.b[i] = round_to<bf16>(__fmul_rn(round_to<bf16>(__fmul_rn(x.b[i], inverse_rms)), weight.b[i]));
         }
     }
-    float inverse_rms = 1.0f;
-    if (weight) {
-        squares = warp_sum(squares);
-        inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(squares, 1.0f / (float)HEAD_DIM), eps)));
-    }
+    if (rotated) {
 #pragma unroll
-    for (int i = 0; i < PAIRS; ++i) {
-        const int j = lane + 32 * i;
-        if (j < HALF) {
-            float x = a[i], y = b[i];
-            if (weight) {
-                x = round_to<bf16>(__fmul_rn(round_to<bf16>(__fmul_rn(x, inverse_rms)), to_float<W>(weight[j])));
-                y = round_to<bf16>(__fmul_rn(round_to<bf16>(__fmul_rn(y, inverse_rms)), to_float<W>(weight[j + HALF])));
-            }
-            if (cos_row) {
-                const float c = round_to<bf16>(cos_row[j]), s = round_to<bf16>(sin_row[j]);
-                const float xc = round_to<bf16>(__fmul_rn(x, c)), ys = round_to<bf16>(__fmul_rn(y, s));
-                const float yc = round_to<bf16>(__fmul_rn(y, c)), xs = round_to<bf16>(__fmul_rn(x, s));
-                x = round_to<bf16>(__fsub_rn(xc, ys));
-                y = round_to<bf16>(__fadd_rn(yc, xs));
-            }
-            dst[j] = x;
-            dst[j + HALF] = y;
+        for (int i = 0; i < PAIRS; ++i) {
+            const float c = cos.a[i], s = sin.a[i];
+            const float xc = round_to<bf16>(__fmul_rn(x.a[i], c)), ys = round_to<bf16>(__fmul_rn(x.b[i], s));
+            const float yc = round_to<bf16>(__fmul_rn(x.b[i], c)), xs = round_to<bf16>(__fmul_rn(x.a[i], s));
+            x.a[i] = round_to<bf16>(__fsub_rn(xc, ys));
+            x.b[i] = round_to<bf16>(__fadd_rn(yc, xs));
         }
     }
 }
 
+// the head to [HEAD_DIM] floats (shared memory) or bfloat16 (a row of the cache)
+template <int HEAD_DIM, typename T>
+__device__ __forceinline__ void store_head(const HeadRegs<HEAD_DIM>& x, T* to, int lane) {
+#pragma unroll
+    for (int i = 0; i < HeadRegs<HEAD_DIM>::PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        if (j < HeadRegs<HEAD_DIM>::HALF) {
+            if constexpr (std::is_same<T, float>::value) {
+                to[j] = x.a[i];
+                to[j + HeadRegs<HEAD_DIM>::HALF] = x.b[i];
+            } else {
+                to[j] = __float2bfloat16_rn(x.a[i]);
+                to[j + HeadRegs<HEAD_DIM>::HALF] = __float2bfloat16_rn(x.b[i]);
+            }
+        }
+    }
+}
+
+// Up to head size 128 registers are held to what lets four CTAs of four warps (two of eight) share
+// an SM; a head of 256 keeps its output tile in twice the registers and is left alone.
 template <int HEAD_DIM, int HPB, int DEC_WARPS, typename W>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+__global__ void __launch_bounds__(DEC_WARPS * 32, HEAD_DIM <= 128 ? 16 / DEC_WARPS : 1)
 decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_table,
                         const float* __restrict__ sin_table, int table_positions,
@@ -128,7 +196,8 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const int* __restrict__ slots, bf16* __restrict__ key_cache,
                         bf16* __restrict__ value_cache, const int* __restrict__ block_tables,
                         int table_stride, int page_size, bf16* __restrict__ out, int num_q, int num_kv,
-                        int window, float scale, int write_cache, int warp_slot_capacity, int heads_here) {
+                        int window, float scale, int write_cache, int warp_slot_capacity, int heads_here,
+                        DecodeLayout layout) {
     // heads_here <= HPB q heads of one kv head are this CTA's (HPB is what the tile and the shared
     // arrays hold; rows past heads_here stay zero): groups of 3, 5, 6 or 7 heads run on the next size up
     constexpr int CPR = HEAD_DIM / 8;          // 16-byte chunks of a key's row
@@ -136,8 +205,19 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     constexpr int WARP_KEYS = DEC_TILE;
     static_assert(HPB <= 8 && 32 % CPR == 0 && DEC_TILE % KPI == 0 && HEAD_DIM % 32 == 0, "shape of the tile");
     extern __shared__ __align__(16) unsigned char shared_raw[];
-    DecodeShared<HEAD_DIM, HPB, DEC_WARPS>& sh = *reinterpret_cast<DecodeShared<HEAD_DIM, HPB, DEC_WARPS>*>(shared_raw);
-    int* slot_s = reinterpret_cast<int*>(shared_raw + sizeof(DecodeShared<HEAD_DIM, HPB, DEC_WARPS>));
+    constexpr int TILE_WORDS = DEC_TILE * HEAD_DIM / 8;                 // 16-byte words of a tile of keys
+    // the arrays of the layout, worked out where they are used (nothing of this stays in registers
+    // through the loop over the keys)
+#define q_s (reinterpret_cast<float*>(shared_raw + layout.q))                  /* [HPB][HEAD_DIM] */
+#define v_new_s (reinterpret_cast<float*>(shared_raw + layout.v_new))
+#define s_new_s (reinterpret_cast<float*>(shared_raw + layout.s_new))
+#define warp_m_s (reinterpret_cast<float*>(shared_raw + layout.warp_m))        /* [DEC_WARPS][HPB] */
+#define warp_l_s (reinterpret_cast<float*>(shared_raw + layout.warp_l))
+    auto ring_of = [&](int w, int stage, int which) {
+        return reinterpret_cast<uint4*>(shared_raw + layout.ring) + ((w * DEC_STAGES + stage) * 2 + which) * TILE_WORDS;
+    };
+    auto warp_o_of = [&](int w) { return reinterpret_cast<float*>(ring_of(w, 0, 0)); };     // [HPB][HEAD_DIM], after the loop
+    int* slot_s = reinterpret_cast<int*>(shared_raw + layout.slots);
 
     cg::cluster_group cluster = cg::this_cluster();
     const int split = blockIdx.x;              // = rank in the cluster
@@ -163,17 +243,36 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     // until all of them have said so.
     cluster_arrive();
 
+    // What the new token's heads are normalised and rotated with does not come from the kernel
+    // before this one: asked for now, it is there when that kernel has ended.
+    const bool cached_new = write_cache == 2;   // the new key and value are in the cache, q is ready
+    HeadRegs<HEAD_DIM> q_norm_weight, k_norm_weight, cos_regs, sin_regs;
+    load_head_weight<HEAD_DIM, W>(q_norm_weight, q_weight, lane);
+    load_head_weight<HEAD_DIM, W>(k_norm_weight, k_weight, lane);
+    {
+        const int table_row = min(position, table_positions - 1);
+        const float* cos_row = cos_table ? cos_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
+        const float* sin_row = sin_table ? sin_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
+#pragma unroll
+        for (int i = 0; i < HeadRegs<HEAD_DIM>::PAIRS; ++i) {
+            const int j = lane + 32 * i;
+            const bool in = cos_row != nullptr && j < HEAD_DIM / 2;
+            cos_regs.a[i] = in ? round_to<bf16>(cos_row[j]) : 1.0f;
+            sin_regs.a[i] = in ? round_to<bf16>(sin_row[j]) : 0.0f;
+            cos_regs.b[i] = sin_regs.b[i] = 0.0f;          // unused
+        }
+    }
+
     // ---- the keys [lo, position] are cut into `splits` pieces of a size that depends on this
     // request alone; piece `split` is this CTA's.  Keys [first, last] of it are in the cache.
     const int lo = window > 0 ? max(0, position - window + 1) : 0;
     const int range_first = lo - lo % 64;
-    const int split_keys = ((position - range_first + splits) / splits + 63) / 64 * 64;
+    const int split_keys = ((position - range_first + splits) / splits + DEC_TILE - 1) / DEC_TILE * DEC_TILE;
     const int own_split = (position - range_first) / split_keys;     // holds the new token
     const int base = range_first + split * split_keys;
     const int first = max(lo, base);
     // write_cache 2: the new token's key and value are in the cache already (and q is ready): it is
     // a key like the others, nothing of it is taken from the projection
-    const bool cached_new = write_cache == 2;
     const int last = min(cached_new ? position : position - 1, base + split_keys - 1);
     const int sub = lane % CPR;                 // which 16-byte chunk of a key's row this lane copies
     const int key_in_instr = lane / CPR;
@@ -188,28 +287,45 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     int first_tile = max(0, (first - base) / WARP_KEYS);
     first_tile += (warp - first_tile % DEC_WARPS + DEC_WARPS) % DEC_WARPS;
     int mine = first_tile < sub_tiles ? (sub_tiles - 1 - first_tile) / DEC_WARPS + 1 : 0;
-    mine = min(mine, warp_slot_capacity / WARP_KEYS);     // the host sizes the list for the context limit
 
-    // cache rows of all keys of this warp, looked up once (-1: no key there)
+    // Cache rows of this warp's keys, looked up once: where a tile of 8 keys lies inside one page,
+    // the row of the tile's first key (-1: the page is not there); else one row per key (-1: no key).
+    const bool by_tile = page_size % DEC_TILE == 0;
+    mine = min(mine, by_tile ? warp_slot_capacity : warp_slot_capacity / WARP_KEYS);     // sized for the context limit
     int* my_slots = slot_s + warp * warp_slot_capacity;
-    for (int e = lane; e < mine * WARP_KEYS; e += 32) {
-        const int key = base + (first_tile + (e / WARP_KEYS) * DEC_WARPS) * WARP_KEYS + e % WARP_KEYS;
-        int slot = -1;
-        if (key >= first && key <= last) {
-            const int page = table[key / page_size];
-            if (page >= 0) slot = (page * num_kv + kv_head) * page_size + key % page_size;
+    if (by_tile) {
+        for (int e = lane; e < mine; e += 32) {
+            const int key0 = base + (first_tile + e * DEC_WARPS) * WARP_KEYS;
+            const int page = table[key0 / page_size];
+            my_slots[e] = page >= 0 ? (page * num_kv + kv_head) * page_size + key0 % page_size : -1;
         }
-        my_slots[e] = slot;
+    } else {
+        for (int e = lane; e < mine * WARP_KEYS; e += 32) {
+            const int key = base + (first_tile + (e / WARP_KEYS) * DEC_WARPS) * WARP_KEYS + e % WARP_KEYS;
+            int slot = -1;
+            if (key >= first && key <= last) {
+                const int page = table[key / page_size];
+                if (page >= 0) slot = (page * num_kv + kv_head) * page_size + key % page_size;
+            }
+            my_slots[e] = slot;
+        }
     }
     __syncwarp();
 
     auto issue = [&](int i) {                   // the i-th sub-tile of this warp into stage i % DEC_STAGES
-        uint4* keys_to = sh.ring[warp][i % DEC_STAGES][0];
-        uint4* values_to = sh.ring[warp][i % DEC_STAGES][1];
+        uint4* keys_to = ring_of(warp, i % DEC_STAGES, 0);
+        uint4* values_to = ring_of(warp, i % DEC_STAGES, 1);
+        const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
 #pragma unroll
         for (int u = 0; u < DEC_TILE / KPI; ++u) {
             const int key = u * KPI + key_in_instr;
-            const int slot = my_slots[i * WARP_KEYS + key];
+            int slot;
+            if (by_tile) {
+                const int tile_slot = my_slots[i];
+                slot = (tile_slot >= 0 && key0 + key >= first && key0 + key <= last) ? tile_slot + key : -1;
+            } else {
+                slot = my_slots[i * WARP_KEYS + key];
+            }
             const int64_t offset = (int64_t)max(slot, 0) * row_stride;
             const int at = key * CPR + (sub ^ (key & 7));
             cp_async_16(keys_to + at, k_base + offset, slot >= 0);
@@ -222,49 +338,54 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         cp_async_commit();
     }
 
-    // ---- the new token: q heads of this CTA, and k, v of its kv head
+    // ---- the new token.  A warp takes q heads warp, warp + DEC_WARPS, ... of this CTA.  In the CTA
+    // whose piece holds the new token it also normalises and rotates the new key for itself (the
+    // same arithmetic in every warp) and has the head's score with it at once, without a round
+    // through shared memory; the warp of head 0 stores the key, the last warp the value.
     pdl_wait();                                 // the projection comes from the kernel before this one
     {
         const unsigned short* token = reinterpret_cast<const unsigned short*>(qkv) + (int64_t)request * heads * HEAD_DIM;
-        const int table_row = min(position, table_positions - 1);
-        const float* cos_row = cos_table ? cos_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
-        const float* sin_row = sin_table ? sin_table + (int64_t)table_row * (HEAD_DIM / 2) : nullptr;
-        for (int job = warp; job < (cached_new ? heads_here : heads_here + 2); job += DEC_WARPS) {
-            if (job < heads_here) {
-                norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(first_q_head + job) * HEAD_DIM, q_weight, eps,
-                                              cos_row, sin_row, sh.q[job], lane);
-            } else if (job == heads_here) {
-                norm_rotate_head<HEAD_DIM, W>(token + (int64_t)(num_q + kv_head) * HEAD_DIM, k_weight, eps,
-                                              cos_row, sin_row, sh.k_new, lane);
-            } else {
-                const unsigned short* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
+        const bool new_here = split == own_split && !cached_new;
+        const bool stores = write_cache == 1 && (blockIdx.y % blocks_per_kv) == 0;
+        int64_t cache_at = -1;
+        if (new_here && stores) {
+            const int slot = slots[request];
+            if (slot >= 0) cache_at = (((int64_t)(slot / page_size) * num_kv + kv_head) * page_size + slot % page_size) * HEAD_DIM;
+        }
+        const bool normed = q_weight != nullptr, rotated = cos_table != nullptr;
+        HeadRegs<HEAD_DIM> q_head, k_head;
+        const bool has_q = warp < heads_here;
+        if (has_q) load_head<HEAD_DIM>(q_head, token + (int64_t)(first_q_head + warp) * HEAD_DIM, lane);
+        if (new_here && has_q) load_head<HEAD_DIM>(k_head, token + (int64_t)(num_q + kv_head) * HEAD_DIM, lane);
+        if (new_here && warp == DEC_WARPS - 1) {
+            const unsigned short* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
 #pragma unroll
-                for (int i = 0; i < HEAD_DIM / 32; ++i) sh.v_new[lane + 32 * i] = bf16_bits_to_float(ld_global_u16(v + lane + 32 * i));
+            for (int i = 0; i < HEAD_DIM / 32; ++i) {
+                const unsigned short bits = ld_global_u16(v + lane + 32 * i);
+                v_new_s[lane + 32 * i] = bf16_bits_to_float(bits);
+                if (cache_at >= 0) reinterpret_cast<unsigned short*>(value_cache + cache_at)[lane + 32 * i] = bits;
+            }
+        }
+        if (new_here && has_q) {
+            norm_rotate_head<HEAD_DIM>(k_head, normed, k_norm_weight, eps, rotated, cos_regs, sin_regs);
+            if (warp == 0 && cache_at >= 0) store_head<HEAD_DIM, bf16>(k_head, key_cache + cache_at, lane);
+        }
+        for (int h = warp; h < heads_here; h += DEC_WARPS) {
+            if (h != warp) load_head<HEAD_DIM>(q_head, token + (int64_t)(first_q_head + h) * HEAD_DIM, lane);
+            norm_rotate_head<HEAD_DIM>(q_head, normed, q_norm_weight, eps, rotated, cos_regs, sin_regs);
+            store_head<HEAD_DIM, float>(q_head, q_s + h * HEAD_DIM, lane);
+            if (new_here) {                     // the head's score with the new key: elements in ascending order a lane
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < HeadRegs<HEAD_DIM>::PAIRS; ++i) dot = __fmaf_rn(q_head.a[i], k_head.a[i], dot);
+#pragma unroll
+                for (int i = 0; i < HeadRegs<HEAD_DIM>::PAIRS; ++i) dot = __fmaf_rn(q_head.b[i], k_head.b[i], dot);
+                dot = warp_sum(dot);
+                if (lane == 0) s_new_s[h] = __fmul_rn(dot, scale);
             }
         }
     }
     __syncthreads();
-
-    if (split == own_split && !cached_new) {
-        if (write_cache == 1 && (blockIdx.y % blocks_per_kv) == 0) {
-            const int slot = slots[request];
-            if (slot >= 0) {
-                const int64_t at = (((int64_t)(slot / page_size) * num_kv + kv_head) * page_size + slot % page_size) * HEAD_DIM;
-                bf16* kd = key_cache + at;
-                bf16* vd = value_cache + at;
-                for (int i = threadIdx.x; i < HEAD_DIM; i += blockDim.x) {
-                    kd[i] = __float2bfloat16_rn(sh.k_new[i]);
-                    vd[i] = __float2bfloat16_rn(sh.v_new[i]);
-                }
-            }
-        }
-        for (int h = warp; h < heads_here; h += DEC_WARPS) {       // score of the new key, one warp a head
-            float dot = 0.0f;
-            for (int i = lane; i < HEAD_DIM; i += 32) dot = __fmaf_rn(sh.q[h][i], sh.k_new[i], dot);
-            dot = warp_sum(dot);
-            if (lane == 0) sh.s_new[h] = __fmul_rn(dot, scale);
-        }
-    }
 
     // ---- q as the a operand: row g of the tile is q head g (zero past HPB), two registers a k step
     const int g = lane >> 2, t4 = lane & 3;
@@ -273,7 +394,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
         q_frag[ks][0] = q_frag[ks][1] = 0u;
         if (g < heads_here) {
-            const float* qh = sh.q[g] + ks * 16 + 2 * t4;
+            const float* qh = q_s + g * HEAD_DIM + ks * 16 + 2 * t4;
             q_frag[ks][0] = pack_bf16x2(qh[0], qh[1]);
             q_frag[ks][1] = pack_bf16x2(qh[8], qh[9]);
         }
@@ -292,8 +413,8 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         cp_async_commit();
         cp_async_wait<DEC_STAGES - 1>();        // sub-tile i has landed ...
         __syncwarp();                           // ... for every lane of the warp
-        const uint4* k_tile = sh.ring[warp][i % DEC_STAGES][0];
-        const uint4* v_tile = sh.ring[warp][i % DEC_STAGES][1];
+        const uint4* k_tile = ring_of(warp, i % DEC_STAGES, 0);
+        const uint4* v_tile = ring_of(warp, i % DEC_STAGES, 1);
         const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
 
         // S[row][key] for the 8 keys of the tile
@@ -352,42 +473,58 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     }
     pdl_launch_dependents();
 
-    // ---- the warps' partial results, merged below in a fixed order
+    // ---- the warps' partial results, merged below in a fixed order; a warp's output goes where its
+    // ring was (every tile it asked for has been used)
+    cp_async_wait<0>();
+    __syncwarp();
     if (g < heads_here) {
+        float* mine_o = warp_o_of(warp) + g * HEAD_DIM;
 #pragma unroll
         for (int n = 0; n < HEAD_DIM / 8; ++n) {
-            sh.warp_o[warp][g][n * 8 + 2 * t4] = o_run[n][0];
-            sh.warp_o[warp][g][n * 8 + 2 * t4 + 1] = o_run[n][1];
+            mine_o[n * 8 + 2 * t4] = o_run[n][0];
+            mine_o[n * 8 + 2 * t4 + 1] = o_run[n][1];
         }
-        if (t4 == 0) { sh.warp_m[warp][g] = m_run; sh.warp_l[warp][g] = l_run; }
+        if (t4 == 0) { warp_m_s[warp * HPB + g] = m_run; warp_l_s[warp * HPB + g] = l_run; }
     }
     __syncthreads();
     cluster_wait();
-    DecodeShared<HEAD_DIM, HPB, DEC_WARPS>* first_cta = cluster.map_shared_rank(&sh, 0);
+    unsigned char* first_cta = cluster.map_shared_rank(shared_raw, 0);
+    float* first_part_m = reinterpret_cast<float*>(first_cta + layout.part_m);       // [splits][HPB]
+    float* first_part_l = reinterpret_cast<float*>(first_cta + layout.part_l);
+    float* first_part_o = reinterpret_cast<float*>(first_cta + layout.part_o);       // [splits][HPB][HEAD_DIM]
+    const float* part_m_s = reinterpret_cast<const float*>(shared_raw + layout.part_m);
+    const float* part_l_s = reinterpret_cast<const float*>(shared_raw + layout.part_l);
+    const float* part_o_s = reinterpret_cast<const float*>(shared_raw + layout.part_o);
     for (int index = threadIdx.x; index < heads_here * HEAD_DIM; index += blockDim.x) {
         const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
         float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, sh.warp_m[w][h]);
+        for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, warp_m_s[w * HPB + h]);
         float l = 0.0f, o = 0.0f;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) {
-            const float f = sh.warp_m[w][h] == -INFINITY ? 0.0f : __expf(sh.warp_m[w][h] - m);
-            l += sh.warp_l[w][h] * f;
-            o += sh.warp_o[w][h][dim] * f;
+            const float f = warp_m_s[w * HPB + h] == -INFINITY ? 0.0f : __expf(warp_m_s[w * HPB + h] - m);
+            l += warp_l_s[w * HPB + h] * f;
+            o += warp_o_of(w)[h * HEAD_DIM + dim] * f;
         }
         if (split == own_split && !cached_new) {   // the new token itself, from shared memory
-            const float s = sh.s_new[h];
+            const float s = s_new_s[h];
             const float new_max = fmaxf(m, s);
             const float f_old = m == -INFINITY ? 0.0f : __expf(m - new_max);
             const float f_new = __expf(s - new_max);
             l = l * f_old + f_new;
-            o = o * f_old + f_new * sh.v_new[dim];
+            o = o * f_old + f_new * v_new_s[dim];
             m = new_max;
         }
-        first_cta->part_o[split][h][dim] = o;   // a store into the first CTA's shared memory
-        if (dim == 0) { first_cta->part_m[split][h] = m; first_cta->part_l[split][h] = l; }
+        if (splits == 1) {                         // nothing to merge with: the same value the merge below gives
+            out_row[index] = __float2bfloat16_rn(o / l);
+            continue;
+        }
+        first_part_o[(split * HPB + h) * HEAD_DIM + dim] = o;   // a store into the first CTA's shared memory
+        if (dim == 0) { first_part_m[split * HPB + h] = m; first_part_l[split * HPB + h] = l; }
     }
+
+    if (splits == 1) return;
 
     // ---- the first CTA merges the pieces in rank order
     cluster.sync();
@@ -404,9 +541,9 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
 #pragma unroll
                 for (int r = 0; r < DEC_MAX_SPLITS; ++r) {
                     const bool in = r < splits;
-                    pm[r] = in ? sh.part_m[r][h] : -INFINITY;
-                    pl[r] = in ? sh.part_l[r][h] : 0.0f;
-                    po[r] = in ? sh.part_o[r][h][dim] : 0.0f;
+                    pm[r] = in ? part_m_s[r * HPB + h] : -INFINITY;
+                    pl[r] = in ? part_l_s[r * HPB + h] : 0.0f;
+                    po[r] = in ? part_o_s[(r * HPB + h) * HEAD_DIM + dim] : 0.0f;
                     m = fmaxf(m, pm[r]);
                 }
 #pragma unroll
@@ -417,12 +554,12 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                 }
             } else {
                 float m = -INFINITY;
-                for (int r = 0; r < splits; ++r) m = fmaxf(m, sh.part_m[r][h]);
+                for (int r = 0; r < splits; ++r) m = fmaxf(m, part_m_s[r * HPB + h]);
                 for (int r = 0; r < splits; ++r) {
-                    const float pm = sh.part_m[r][h];
+                    const float pm = part_m_s[r * HPB + h];
                     const float f = pm == -INFINITY ? 0.0f : __expf(pm - m);
-                    l += sh.part_l[r][h] * f;
-                    o += sh.part_o[r][h][dim] * f;
+                    l += part_l_s[r * HPB + h] * f;
+                    o += part_o_s[(r * HPB + h) * HEAD_DIM + dim] * f;
                 }
             }
             out_row[index] = __float2bfloat16_rn(o / l);
@@ -430,11 +567,19 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     }
 }
 
-template <int HEAD_DIM, int DEC_WARPS>
-static int decode_warp_slot_capacity(int max_context, int splits) {
-    constexpr int WARP_KEYS = DEC_TILE;
-    const int split_keys = ((max_context + splits - 1) / splits + 63) / 64 * 64 + 64;
-    return (split_keys / (WARP_KEYS * DEC_WARPS) + 2) * WARP_KEYS;
+// entries of a warp's list of cache slots: one per tile of 8 keys where tiles lie inside pages, else
+// one per key; sized for the longest piece a request of max_context tokens is cut into
+#undef q_s
+#undef v_new_s
+#undef s_new_s
+#undef warp_m_s
+#undef warp_l_s
+
+template <int DEC_WARPS>
+static int decode_warp_slot_capacity(int max_context, int splits, int page_size) {
+    const int split_keys = ((max_context + 64 + splits - 1) / splits + DEC_TILE - 1) / DEC_TILE * DEC_TILE;
+    const int tiles = split_keys / (DEC_TILE * DEC_WARPS) + 2;
+    return page_size % DEC_TILE == 0 ? tiles : tiles * DEC_TILE;
 }
 
 template <int HEAD_DIM, int HPB, int DEC_WARPS, typename W>
@@ -443,19 +588,25 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
                          void* value_cache, const int* block_tables, int table_stride, int page_size,
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
-                         int splits, int write_cache, int max_context, int pdl, cudaStream_t stream, int heads_here) {
+                         int splits, int write_cache, int max_context, int pdl, cudaStream_t stream, int heads_here,
+                         int sm_count) {
     auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, W>;
-    const int warp_slots = decode_warp_slot_capacity<HEAD_DIM, DEC_WARPS>(max_context, splits);
-    const size_t shared = sizeof(DecodeShared<HEAD_DIM, HPB, DEC_WARPS>) + (size_t)DEC_WARPS * warp_slots * sizeof(int);
-    if (shared > 200 * 1024) return TVB_BAD_ARGUMENT;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    if (e != cudaSuccess) return (int)e;
-    TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / heads_here), requests), dim3(DEC_WARPS * 32), shared,
-                     stream, pdl, splits);
-    e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
-                           cos_table, sin_table, table_positions, positions, token_row, slots,
-                           (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
-                           (bf16*)out, num_q, num_kv, window, scale, write_cache, warp_slots, heads_here);
+    const int warp_slots = decode_warp_slot_capacity<DEC_WARPS>(max_context, splits, page_size);
+    const DecodeLayout layout = decode_layout(HEAD_DIM, HPB, DEC_WARPS, splits, warp_slots);
+    if (layout.total > 200 * 1024) return TVB_BAD_ARGUMENT;
+    static int configured = 0;                   // the largest size asked for so far, per instantiation
+    if (layout.total > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        configured = 200 * 1024;
+    }
+    TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / heads_here), requests), dim3(DEC_WARPS * 32),
+                     (size_t)layout.total, stream, pdl, splits);
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
+                                       cos_table, sin_table, table_positions, positions, token_row, slots,
+                                       (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
+                                       (bf16*)out, num_q, num_kv, window, scale, write_cache, warp_slots, heads_here,
+                                       layout);
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
@@ -514,7 +665,8 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
     const bool wide = head_dim <= 128 && (long long)requests * num_kv * (group / heads_here) * splits <= sm_count;
 #define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
                     token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
-                    requests, num_q, num_kv, window, scale, splits, write_cache, max_context, pdl, s, heads_here
+                    requests, num_q, num_kv, window, scale, splits, write_cache, max_context, pdl, s, heads_here, \
+                    sm_count
 #define DECODE_BY_WARPS(D, H, WT)                                       \
     do {                                                                \
         if (wide) return launch_decode<D, H, 8, WT>(DECODE_ARGS);       \
