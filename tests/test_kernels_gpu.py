@@ -598,6 +598,68 @@ def test_gemm_tc(shape, tile):
     assert bool((wide[:, :8] == 7).all()) and bool((wide[:, n + 8:] == 7).all())
 
 
+@pytest.mark.parametrize("shape", [(1, 64, 384), (8, 520, 1000), (16, 4096, 4104), (17, 1024, 6144),
+                                   (40, 3072, 2048), (64, 8, 256), (100, 776, 3000), (128, 2048, 1280)])
+def test_gemm_stream(shape):
+    """The weight-streaming tcgen05 product alone: every padded batch size (16, 32, 64, 128), tiles
+    cut by n and k edges, tiles shared by several CTAs (their partial sums are added by whoever
+    arrives last) and tiles one CTA has to itself; bfloat16 and float32 results, the activation,
+    the addition to the residual stream."""
+    m, kk, n = shape
+    torch.manual_seed(m + n)
+    x, w = (torch.randn(m, kk) * 0.5).bfloat16(), (torch.randn(n, kk) * 0.05).bfloat16()
+    # make one row and one column stand out, so that a tile written to the wrong place shows
+    x[m // 2] *= 4
+    w[n // 3] *= 4
+    want = x.float() @ w.float().T
+    got = k().gemm_stream(x.to(DEV), w.to(DEV), 0)
+    assert got.dtype == torch.bfloat16 and got.shape == (m, n)
+    assert k().gemm_stream_status() == 0
+    close(got, want, torch.bfloat16, bf16=5e-3)
+    # the sum does not depend on which CTA came last
+    for _ in range(3):
+        assert torch.equal(k().gemm_stream(x.to(DEV), w.to(DEV), 0), got)
+    logits = k().gemm_stream(x.to(DEV), w.to(DEV), 1)
+    assert logits.dtype == torch.float32
+    close(logits, want, torch.float32, f32=2e-5)
+    assert torch.equal(logits.bfloat16(), got)
+    if n % 2 == 0:
+        gate_up = k().gemm_stream(x.to(DEV), w.to(DEV), 2)
+        assert gate_up.shape == (m, n // 2)
+        close(gate_up, plain.swiglu(want, torch.bfloat16), torch.bfloat16, bf16=1e-2)
+    stream = torch.randn(m, n).bfloat16()
+    summed = k().gemm_stream(x.to(DEV), w.to(DEV), 0, add_stream=stream.to(DEV))
+    assert torch.equal(summed.cpu(), (got.cpu().float() + stream.float()).bfloat16())
+    # into a view with a row stride of its own, beside columns that must stay as they are
+    wide = torch.full((m, n + 16), 7.0, dtype=torch.bfloat16, device=DEV)
+    k().gemm_stream(x.to(DEV), w.to(DEV), 0, out=wide[:, 8:n + 8])
+    assert torch.equal(wide[:, 8:n + 8], got)
+    assert bool((wide[:, :8] == 7).all()) and bool((wide[:, n + 8:] == 7).all())
+    assert k().gemm_stream_status() == 0
+    # every launch leaves the counters as it found them
+    from tinyvllm_b200.ops import kernels
+    assert int(kernels._stream_scratch_of(torch.device(DEV))[1].abs().sum()) == 0
+
+
+def test_gemm_stream_rows_do_not_depend_on_the_batch():
+    torch.manual_seed(6)
+    x, w = torch.randn(100, 512).bfloat16().to(DEV), (torch.randn(3000, 512) * 0.05).bfloat16().to(DEV)
+    whole = k().gemm_stream(x, w, 0)
+    for first, count in ((0, 1), (3, 8), (40, 33), (30, 70)):
+        assert torch.equal(whole[first:first + count], k().gemm_stream(x[first:first + count], w, 0))
+    assert k().gemm_stream_status() == 0
+
+
+def test_gemm_stream_refuses():
+    from tinyvllm_b200.ops.kernels import KernelError
+    with pytest.raises(KernelError, match="m <= 128"):
+        k().gemm_stream(torch.zeros(129, 64, dtype=torch.bfloat16, device=DEV),
+                        torch.zeros(16, 64, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(KernelError, match="multiple of 8"):
+        k().gemm_stream(torch.zeros(8, 60, dtype=torch.bfloat16, device=DEV),
+                        torch.zeros(16, 60, dtype=torch.bfloat16, device=DEV))
+
+
 def test_gemm_tc_rows_do_not_depend_on_the_batch():
     torch.manual_seed(5)
     x, w = torch.randn(700, 256).bfloat16().to(DEV), (torch.randn(384, 256) * 0.05).bfloat16().to(DEV)

@@ -1,10 +1,13 @@
 """bfloat16 matrix products: which kernel takes which shape.
 
 Up to 16 rows (decode) with a bfloat16 result and a weight of up to 40 MB (24 MB beyond 8 rows):
-the package's weight-streaming kernel (measured against cuBLAS per shape: it wins up to 8 rows
-by 20 to 50 %, is level around 16 and loses beyond, and loses on large weights).  Results in float32 (the logits: vocabulary x width, the one product of a decode step
-that is long enough to be bound by bandwidth alone) go to cuBLAS with float32 output at every
-row count: 53 us against 84 us at 8 rows.  The packed gate/up product
+the package's weight-streaming kernel for small weights (measured against cuBLAS per shape: it
+wins up to 8 rows by 20 to 50 %, is level around 16 and loses beyond, and loses on large
+weights).  Up to 64 rows and a weight of 400 MB and more (the gate/up product of the largest
+models): the package's stream-k tcgen05 kernel, which reads the weight faster than cuBLAS but has
+a higher fixed cost per launch (figures at STREAM_MIN_WEIGHT_BYTES).  Results in float32 (the
+logits: vocabulary x width) go to cuBLAS with float32 output at every row count: 53 us against
+84 us (small-weight kernel) and 56 us (stream-k kernel) at 8 rows.  The packed gate/up product
 with its activation at 128 rows and more (prefill): the package's tcgen05 kernel, which keeps
 the accumulator in tensor memory and applies SiLU(gate) * up on the way out.  The other
 products with more than 32 rows: cuBLAS through ``torch.nn.functional.linear``, the library
@@ -13,6 +16,7 @@ call the reference's engine makes for every projection (tinyvllm/layers.py:84-85
 
 from __future__ import annotations
 
+import os
 import weakref
 
 import torch
@@ -57,6 +61,23 @@ SMALL_M_MAX_WEIGHT_BYTES = 40 << 20
 SMALL_M_MAX_WEIGHT_BYTES_OVER_8_ROWS = 24 << 20
 
 
+# The stream-k tcgen05 kernel reads a large weight at 6.1 to 6.3 TB/s where cuBLAS reaches 5.5 to
+# 5.8, but a launch costs about 7 us beside the stream itself (set-up, the first copies, and the
+# partial sums of tiles that two CTAs share), and rows of x beyond 32 cost more than they do in
+# cuBLAS.  Measured in CUDA graphs, weights rotated through more than L2 (us, this kernel / cuBLAS,
+# the latter with the activation kernel behind it for gate/up): 8 rows gate/up 201 MB 41.9 / 37.1,
+# 357 MB 64.2 / 63.8, 524 MB 85.6 / 93.6; 64 rows 524 MB 96.3 / 98.9; the head (311 MB, float32
+# out) 56.5 / 53.7; 262 MB with k = 25,600 (every tile shared by four CTAs) 50.6 / 45.6.
+STREAM_MIN_WEIGHT_BYTES = int(os.environ.get("TINYVLLM_B200_STREAM_MIN_MB", "400")) << 20
+STREAM_MAX_ROWS = 64
+
+
+def streamed(x: torch.Tensor, weight: torch.Tensor, mode: int) -> bool:
+    """Whether the stream-k kernel takes this product."""
+    return (x.shape[0] <= STREAM_MAX_ROWS and weight.numel() * weight.element_size() >= STREAM_MIN_WEIGHT_BYTES
+            and kernels.gemm_stream_takes(x, weight, mode))
+
+
 def small(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether the weight-streaming kernel takes this product."""
     limit = SMALL_M_MAX_WEIGHT_BYTES if x.shape[0] <= 8 else SMALL_M_MAX_WEIGHT_BYTES_OVER_8_ROWS
@@ -73,6 +94,8 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype
         raise kernels.KernelError(f"linear_bf16 cannot produce {out_dtype}")
     if out_dtype == torch.float32:
         # float32 results (logits) keep the float32 accumulator unrounded
+        if streamed(x, weight, kernels.GEMM_F32) and (out is None or out.stride(1) == 1):
+            return kernels.gemm_stream(x, weight, kernels.GEMM_F32, out=out)
         if x.stride(1) == 1 and weight.stride(1) == 1 and x.shape[1] % 8 == 0:
             result = torch.mm(x, weight.t(), out_dtype=torch.float32)
         elif x.shape[0] <= 256:
@@ -85,6 +108,8 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype
         return result
     if small(x, weight):
         return kernels.gemm_small_m(x, weight, kernels.GEMM_BF16, out=out, prefetch=next_weight(weight))
+    if streamed(x, weight, kernels.GEMM_BF16) and (out is None or out.stride(1) == 1):
+        return kernels.gemm_stream(x, weight, kernels.GEMM_BF16, out=out)
     if out is not None:
         return torch.mm(x, weight.t(), out=out)
     return torch.nn.functional.linear(x, weight)
@@ -94,6 +119,8 @@ def linear_silu_bf16(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Ten
     """silu(x . gate^T) * (x . up^T) for a packed [gate | up] weight."""
     if small(x, gate_up_weight):
         return kernels.gemm_small_m(x, gate_up_weight, kernels.GEMM_SILU, prefetch=next_weight(gate_up_weight))
+    if streamed(x, gate_up_weight, kernels.GEMM_SILU):
+        return kernels.gemm_stream(x, gate_up_weight, kernels.GEMM_SILU)
     if x.shape[0] >= TC_MIN_ROWS and kernels.gemm_tc_takes(x, gate_up_weight, kernels.GEMM_SILU):
         return kernels.gemm_tc(x, gate_up_weight, kernels.GEMM_SILU)
     return kernels.silu_mul(torch.nn.functional.linear(x, gate_up_weight))

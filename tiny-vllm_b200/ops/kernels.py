@@ -666,6 +666,81 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *, out: tor
     return out
 
 
+# ----------------------------- tcgen05 matrix product (few rows, a large weight)
+STREAM_MAX_ROWS = 128
+_stream_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+_gemm_stream_used = False
+
+
+def _stream_scratch_of(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Workspace (partial sums of tiles that two CTAs share) and counters of the stream-k kernel,
+    one pair per device, sized for the largest launch and never freed: CUDA graphs keep their
+    addresses.  Launches that use them must follow one another (those of one stream do)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    found = _stream_scratch.get(index)
+    if found is None:
+        sms = torch.cuda.get_device_properties(index).multi_processor_count
+        workspace = torch.empty(sms * 2 * 2 * STREAM_MAX_ROWS * 128, dtype=torch.float32, device=device)
+        counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        found = _stream_scratch[index] = (workspace, counters)
+    return found
+
+
+def gemm_stream_takes(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16) -> bool:
+    """Whether :func:`gemm_stream` takes this product: bfloat16, up to 128 rows of x, rows contiguous
+    and 16-byte aligned, k a multiple of 8."""
+    if (x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2
+            or x.shape[1] != w.shape[1] or x.stride(1) != 1 or w.stride(1) != 1):
+        return False
+    rows = w.shape[0]
+    if mode == GEMM_SILU and rows % 2:
+        return False
+    n = rows // 2 if mode == GEMM_SILU else rows
+    return (mode in (GEMM_BF16, GEMM_F32, GEMM_SILU) and 0 < x.shape[0] <= STREAM_MAX_ROWS
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and n * 4 <= (1 << 16) * 128)
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *, out: torch.Tensor | None = None,
+                add_stream: torch.Tensor | None = None) -> torch.Tensor:
+    """x [m <= 128, k] . w [n, k]^T for a large bfloat16 weight, streamed once through the tcgen05
+    tensor cores with the work cut evenly over the SMs.  GEMM_BF16: bfloat16 [m, n], with
+    ``add_stream`` (contiguous bfloat16 [m, n]) round(round(product) + add_stream); GEMM_F32:
+    float32 [m, n]; GEMM_SILU: w is [gate | up] with 2 n rows, the result is
+    silu(x . gate^T) * (x . up^T)."""
+    _need_cuda(x, w, add_stream)
+    if not gemm_stream_takes(x, w, mode):
+        raise KernelError("gemm_stream wants bfloat16 x [m <= 128, k] and w [n, k] with contiguous, 16-byte "
+                          "aligned rows and k a multiple of 8")
+    m, k = x.shape
+    n = w.shape[0] // 2 if mode == GEMM_SILU else w.shape[0]
+    out_dtype = torch.float32 if mode == GEMM_F32 else torch.bfloat16
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    elif out.dtype != out_dtype or out.shape != (m, n) or out.stride(1) != 1:
+        raise KernelError(f"gemm_stream: out must be {out_dtype} [m, n] with contiguous rows")
+    if add_stream is not None and (mode != GEMM_BF16 or add_stream.shape != (m, n)
+                                   or add_stream.dtype != torch.bfloat16 or not add_stream.is_contiguous()):
+        raise KernelError("gemm_stream: add_stream is a contiguous bfloat16 [m, n] of a bfloat16 result")
+    workspace, counters = _stream_scratch_of(x.device)
+    fn = _fn("gemm_stream", "tvb_gemm_stream",
+             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
+              c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    global _gemm_tc_unchecked, _gemm_stream_used
+    _check(fn(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+              m, n, k, mode, _ptr(add_stream), workspace.data_ptr(), counters.data_ptr(), _pdl("gemm"),
+              _stream()), "gemm_stream")
+    _gemm_tc_unchecked = _gemm_stream_used = True
+    _guarded_counts[0] += 1
+    return out
+
+
+def gemm_stream_status() -> int:
+    """0, or which bounded wait of a gemm_stream launch gave up since the last call.  Synchronises
+    the device; reading clears the record."""
+    return _fn("gemm_stream", "tvb_gemm_stream_status", [])()
+
+
 _gemm_tc_unchecked = False
 
 
@@ -693,7 +768,7 @@ _guarded_counts = [0, 0]
 
 
 def guarded_launch_counts() -> tuple[int, int]:
-    """How often (gemm_tc, attention_prefill_tc), the kernels with bounded waits, were launched
+    """How often (gemm_tc or gemm_stream, attention_prefill_tc), the kernels with bounded waits, were launched
     through this module so far.  A caller that records a step into a CUDA graph compares the
     counts around one pass of the step and hands what it finds to :func:`note_guarded_launches`
     at every replay: a replay launches the kernels without passing through this module."""
@@ -716,6 +791,11 @@ def check_finished_launches() -> None:
         if status:
             raise KernelError(f"gemm_tc: a wait inside the kernel ran out (code {status}); "
                               "the results of this step are not valid")
+        if _gemm_stream_used:
+            status = gemm_stream_status()
+            if status:
+                raise KernelError(f"gemm_stream: a wait inside the kernel ran out (code {status}); "
+                                  "the results of this step are not valid")
     if _attention_tc_unchecked:
         status = attention_prefill_tc_status()
         if status:
