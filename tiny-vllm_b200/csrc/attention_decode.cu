@@ -241,7 +241,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
 
     // Every CTA says that it runs; the stores into the first CTA's shared memory at the end wait
     // until all of them have said so.
-    cluster_arrive();
+    cluster_arrive_relaxed();
 
     // What the new token's heads are normalised and rotated with does not come from the kernel
     // before this one: asked for now, it is there when that kernel has ended.

@@ -86,6 +86,10 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float* f) {
 
 // ---- the cluster's barrier in two halves: arrive early, wait where the others are needed
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+// The same without ordering any memory access: for "this CTA runs", said at a kernel's start, where
+// nothing has been written that another CTA will read (a release would make the warp wait for its
+// loads in flight).
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
 
 // ---- programmatic dependent launch: a kernel launched with the attribute may start while the

@@ -100,7 +100,7 @@ gemm_small_m_kernel(const bf16* x, int64_t ldx, const bf16* __restrict__ w, int6
     const int rank = blockIdx.x, ranks = gridDim.x;
     // Every CTA says that it runs; before the first store into another CTA's shared memory the
     // epilogue makes sure that all of them have said so.
-    cluster_arrive();
+    cluster_arrive_relaxed();
     const int n0 = blockIdx.y * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t4 = lane & 3;
