@@ -185,10 +185,12 @@ __device__ __forceinline__ void store_head(const HeadRegs<HEAD_DIM>& x, T* to, i
     }
 }
 
-// Up to head size 128 registers are held to what lets four CTAs of four warps (two of eight) share
-// an SM; a head of 256 keeps its output tile in twice the registers and is left alone.
+// With four warps a CTA (grids that fill the GPU) registers are held to what lets four CTAs share
+// an SM (up to head size 128; a head of 256 keeps its output tile in twice the registers and is
+// left alone).  The wider CTAs are used for grids of fewer CTAs than SMs: one CTA an SM, no cap
+// (the loop wants about 150 registers and is a tenth faster with them than with 128 and spills).
 template <int HEAD_DIM, int HPB, int DEC_WARPS, typename W>
-__global__ void __launch_bounds__(DEC_WARPS * 32, HEAD_DIM <= 128 ? 16 / DEC_WARPS : 1)
+__global__ void __launch_bounds__(DEC_WARPS * 32, HEAD_DIM <= 128 && DEC_WARPS == 4 ? 4 : 1)
 decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_table,
                         const float* __restrict__ sin_table, int table_positions,
