@@ -185,12 +185,13 @@ __device__ __forceinline__ void store_head(const HeadRegs<HEAD_DIM>& x, T* to, i
     }
 }
 
-// With four warps a CTA (grids that fill the GPU) registers are held to what lets four CTAs share
-// an SM (up to head size 128; a head of 256 keeps its output tile in twice the registers and is
-// left alone).  The wider CTAs are used for grids of fewer CTAs than SMs: one CTA an SM, no cap
-// (the loop wants about 150 registers and is a tenth faster with them than with 128 and spills).
-template <int HEAD_DIM, int HPB, int DEC_WARPS, typename W>
-__global__ void __launch_bounds__(DEC_WARPS * 32, HEAD_DIM <= 128 && DEC_WARPS == 4 ? 4 : 1)
+// RESIDENT: the CTAs that are to share an SM, which caps the registers.  The loop wants about 150
+// and is up to a tenth faster with them than with 128 and spills, so the cap follows the grid:
+// four CTAs of four warps an SM (128 registers) only where the grid needs them, three (160) for
+// grids of up to three CTAs an SM, none for the eight-warp CTAs of grids smaller than the GPU and
+// for a head of 256, which keeps its output tile in twice the registers.
+template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, typename W>
+__global__ void __launch_bounds__(DEC_WARPS * 32, RESIDENT)
 decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_table,
                         const float* __restrict__ sin_table, int table_positions,
@@ -584,7 +585,7 @@ static int decode_warp_slot_capacity(int max_context, int splits, int page_size)
     return page_size % DEC_TILE == 0 ? tiles : tiles * DEC_TILE;
 }
 
-template <int HEAD_DIM, int HPB, int DEC_WARPS, typename W>
+template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, typename W>
 static int launch_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                          const float* cos_table, const float* sin_table, int table_positions,
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
@@ -592,7 +593,7 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
                          int splits, int write_cache, int max_context, int pdl, cudaStream_t stream, int heads_here,
                          int sm_count) {
-    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, W>;
+    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, RESIDENT, W>;
     const int warp_slots = decode_warp_slot_capacity<DEC_WARPS>(max_context, splits, page_size);
     const DecodeLayout layout = decode_layout(HEAD_DIM, HPB, DEC_WARPS, splits, warp_slots);
     if (layout.total > 200 * 1024) return TVB_BAD_ARGUMENT;
@@ -665,14 +666,16 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
             sm_count = 0;
     }
     const bool wide = head_dim <= 128 && (long long)requests * num_kv * (group / heads_here) * splits <= sm_count;
+    const bool roomy = (long long)requests * num_kv * (group / heads_here) * splits <= 3ll * sm_count;
 #define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
                     token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
                     requests, num_q, num_kv, window, scale, splits, write_cache, max_context, pdl, s, heads_here, \
                     sm_count
 #define DECODE_BY_WARPS(D, H, WT)                                       \
     do {                                                                \
-        if (wide) return launch_decode<D, H, 8, WT>(DECODE_ARGS);       \
-        return launch_decode<D, H, 4, WT>(DECODE_ARGS);                 \
+        if (wide) return launch_decode<D, H, 8, 1, WT>(DECODE_ARGS);    \
+        if (roomy) return launch_decode<D, H, 4, (D > 128 ? 1 : 3), WT>(DECODE_ARGS); \
+        return launch_decode<D, H, 4, (D > 128 ? 1 : 4), WT>(DECODE_ARGS);            \
     } while (0)
 #define DECODE_BY_HPB(D, WT)                                            \
     do {                                                                \
