@@ -43,7 +43,7 @@ _launches = 0
 # (griddepcontrol.wait): they may start, and fetch weights, while the kernel before them ends.
 # TINYVLLM_B200_PDL=0 turns it off; a comma-separated list (gemm,norm,attention,sample) keeps it
 # for those kernels only.
-_PDL_DEFAULT = ("gemm",)
+_PDL_DEFAULT = ("gemm", "norm")
 _setting = os.environ.get("TINYVLLM_B200_PDL", "1")
 PDL = frozenset() if _setting == "0" else frozenset(_PDL_DEFAULT if _setting == "1" else _setting.split(","))
 
