@@ -164,6 +164,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             ++ring;
             return true;
         };
+        pdl_wait();                             // q, keys and values come from the kernel before this one
         for (int round = 0; alive; ++round) {
             Item it;
             if (!item_of(round, it)) break;
@@ -268,6 +269,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---- softmax rows: group 0 = warps 2..5 takes the even blocks of a tile, group 1 = warps 6..9
         // the odd ones; a warp's number modulo 4 names the 32 lanes of tensor memory it may read.
         const int quarter = warp & 3, group = (warp - 2) >> 2;
+        pdl_wait();                             // before this kernel's first write to global memory
         const int row = quarter * 32 + lane;
         const uint32_t lane_address = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint32_t s_address = lane_address + group * KT;
@@ -438,6 +440,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
     }
 
+    pdl_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (*abort_flag) {
@@ -515,7 +518,7 @@ extern "C" int tvb_attention_prefill_tc(const void* q, long long q_token_stride,
                                         const int* block_tables, int table_stride, const int* positions,
                                         const int* tile_row, const int* tile_first, const int* tile_count,
                                         int num_tiles, void* out, int num_q, int num_kv, int head_dim, int page_size,
-                                        int window, float scale, void* stream) {
+                                        int window, float scale, int pdl, void* stream) {
     if (num_tiles <= 0 || tokens <= 0) return 0;
     if (!tvb_attention_prefill_tc_supports(head_dim, num_q, num_kv, page_size) || q_token_stride % 8 ||
         ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)key_cache & 15) || ((uintptr_t)value_cache & 15) ||
@@ -544,7 +547,7 @@ extern "C" int tvb_attention_prefill_tc(const void* q, long long q_token_stride,
     }
     const long long items = (long long)num_tiles * num_q;
     const int ctas = (int)(items < sms ? items : sms);
-    TvbLaunch launch(dim3(ctas), dim3(THREADS), SHARED_BYTES, (cudaStream_t)stream, 0);
+    TvbLaunch launch(dim3(ctas), dim3(THREADS), SHARED_BYTES, (cudaStream_t)stream, pdl);
     cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, map_q, map_k, map_v, block_tables, table_stride,
                                        positions, tile_row, tile_first, tile_count, (bf16*)out,
                                        (int64_t)num_q * HD, num_tiles, num_q, num_kv, page_size, window,

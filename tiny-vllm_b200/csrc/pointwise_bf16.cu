@@ -183,6 +183,9 @@ qk_norm_rope_store_bf16_kernel(bf16* __restrict__ qkv, const W* __restrict__ q_w
             wk_lo[e] = to_float<W>(k_weight[8 * l + e]), wk_hi[e] = to_float<W>(k_weight[HALF + 8 * l + e]);
         }
     }
+    // position, slot, angles and weights do not come from the kernel before this one; the projection does
+    pdl_wait();
+    pdl_launch_dependents();
     bf16* row = qkv + (int64_t)token * heads * HEAD_DIM + 8 * l;
     const int64_t cache_row = slot >= 0 ? ((int64_t)(slot / page_size) * num_kv * page_size + slot % page_size) : 0;
 
@@ -261,15 +264,17 @@ extern "C" int tvb_qk_norm_rope_store_bf16(void* qkv, const void* q_weight, cons
                                            const int* positions, const int* slots, void* key_cache,
                                            void* value_cache, int tokens, int num_q, int num_kv,
                                            int head_dim, int page_size, int table_positions, float eps,
-                                           int weight_dtype, void* stream) {
+                                           int weight_dtype, int pdl, void* stream) {
     if (tokens <= 0) return 0;
     if (!tvb_qk_norm_rope_store_bf16_supports(head_dim) || num_q <= 0 || num_kv < 0 || (slots && page_size <= 0))
         return TVB_BAD_ARGUMENT;
     if (head_dim % 8 || ((num_q + 2 * num_kv) * head_dim) % 8) return TVB_BAD_ARGUMENT;
     const int64_t blocks = ((int64_t)tokens + 7) / 8;         // a warp per token, eight to a block
     cudaStream_t s = (cudaStream_t)stream;
+    TvbLaunch launch(dim3((unsigned)blocks), dim3(256), 0, s, pdl);
+    cudaError_t launched = cudaSuccess;
 #define QK_LAUNCH(D, WT)                                                                                   \
-    qk_norm_rope_store_bf16_kernel<D, WT><<<(unsigned)blocks, 256, 0, s>>>(                                \
+    launched = cudaLaunchKernelEx(&launch.config, qk_norm_rope_store_bf16_kernel<D, WT>,                   \
         (bf16*)qkv, (const WT*)q_weight, (const WT*)k_weight, cos_table, sin_table, positions, slots,      \
         (bf16*)key_cache, (bf16*)value_cache, tokens, num_q, num_kv, page_size, table_positions, eps)
 #define QK_BY_DIM(WT)                                     \
@@ -283,5 +288,5 @@ extern "C" int tvb_qk_norm_rope_store_bf16(void* qkv, const void* q_weight, cons
     if (weight_dtype == TVB_F32) QK_BY_DIM(float);
     else if (weight_dtype == TVB_BF16) QK_BY_DIM(bf16);
     else return TVB_BAD_ARGUMENT;
-    return tvb_last_error();
+    return launched == cudaSuccess ? tvb_last_error() : (int)launched;
 }

@@ -41,8 +41,9 @@ _launches = 0
 
 # Programmatic dependent launch for the kernels that wait for their predecessor themselves
 # (griddepcontrol.wait): they may start, and fetch weights, while the kernel before them ends.
-# TINYVLLM_B200_PDL=0 turns it off; a comma-separated list (gemm,norm,attention,sample) keeps it
-# for those kernels only.
+# TINYVLLM_B200_PDL=0 turns it off; a comma-separated list (gemm,norm,attention,prefill,sample) keeps
+# it for those kernels only (attention: the decode attention; prefill: the prompt's q/k norm, rotation
+# and cache write, and the tcgen05 attention).
 _PDL_DEFAULT = ("gemm", "norm")
 _setting = os.environ.get("TINYVLLM_B200_PDL", "1")
 PDL = frozenset() if _setting == "0" else frozenset(_PDL_DEFAULT if _setting == "1" else _setting.split(","))
@@ -232,10 +233,10 @@ def qk_norm_rope_store(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: 
     page_size = key_cache.shape[2] if slots is not None else 0
     if qkv.dtype == torch.bfloat16 and head_dim in (16, 32, 64, 128, 256):
         fn = _fn("pointwise_bf16", "tvb_qk_norm_rope_store_bf16",
-                 [c_void_p] * 9 + [c_int] * 6 + [c_float, c_int, c_void_p])
+                 [c_void_p] * 9 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p])
         _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
                   positions.data_ptr(), _ptr(slots), _ptr(key_cache), _ptr(value_cache), tokens, num_q,
-                  num_kv, head_dim, page_size, table_positions, eps, weight_tag, _stream()),
+                  num_kv, head_dim, page_size, table_positions, eps, weight_tag, _pdl("prefill"), _stream()),
                "qk_norm_rope_store")
         return
     fn = _fn("pointwise", "tvb_qk_norm_rope_store",
@@ -508,12 +509,12 @@ def attention_prefill_tc(q: torch.Tensor, q_token_stride: int, key_cache: torch.
     fn = _fn("attention_prefill_tc", "tvb_attention_prefill_tc",
              [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-              c_void_p])
+              c_int, c_void_p])
     global _attention_tc_unchecked
     _check(fn(q.data_ptr(), q_token_stride, tokens, key_cache.data_ptr(), value_cache.data_ptr(),
               key_cache.shape[0], block_tables.data_ptr(), block_tables.shape[1], positions.data_ptr(),
               tile_row.data_ptr(), tile_first.data_ptr(), tile_count.data_ptr(), tiles, out.data_ptr(),
-              num_q, num_kv, head_dim, key_cache.shape[2], window or 0, scale, _stream()),
+              num_q, num_kv, head_dim, key_cache.shape[2], window or 0, scale, _pdl("prefill"), _stream()),
            "attention_prefill_tc")
     _attention_tc_unchecked = True
     _guarded_counts[1] += 1
