@@ -12,22 +12,31 @@
 // memory of the cluster's first CTA (distributed shared memory), which merges them
 // in rank order: no scratch in global memory and no second kernel.
 //
-// Every warp walks its keys in tiles of 8 through a ring of cp.async stages of its own in shared
+// Every warp walks its keys in tiles through a ring of cp.async stages of its own in shared
 // memory (16-byte chunks swizzled by the key, so that ldmatrix reads them without bank conflicts);
 // the cache slots of its keys are looked up once, up front, and the first stage is in flight
 // before the kernel waits for the projection (keys and values already in the cache do not depend
 // on it, nor do the norm weights and the rotation's table row, which are asked for up front too).
-// The q heads of the CTA are the rows of an m16n8k16 tensor-core tile (rows past HPB are
-// zero): S = Q K^T and O += P V are mma.sync with float32 accumulators (the second product's k of
-// 16 is the tile's 8 keys and 8 zeros), a quarter of the instructions of a dot product spread
-// over lanes.  Small tiles and four warps keep a CTA's shared memory near 42 KB, so that four CTAs
-// share an SM: measured, residency counts for more here than instructions (tiles of 16 keys were
-// slower than the dot products they replaced, tiles of 8 are faster).  Softmax is float32; P is
-// rounded to bfloat16 for the second product while the denominator sums the unrounded values (as
-// tinyvllm/kernels/paged_decode.cu:322-356 does).  The size of a piece follows from the request's
-// own position (and window) alone and is a whole number of tiles: pieces of a request differ by
-// one tile at most, so the CTAs of a cluster reach its barrier together (pieces of whole multiples
-// of 64 keys left the last CTAs of a cluster with little or nothing to do, and the others waiting).
+// The products are mma.sync m16n8k16 with float32 accumulators, in one of two arrangements:
+//
+// * head size 128, tiles of 16 keys: the KEYS are the rows of the first product, S^T = K Q^T (the
+//   CTA's up to 8 q heads are its 8 columns), and the k of the second, O^T += V^T P^T, whose b
+//   operand P^T comes from the first product's accumulators by two 8 x 8 transposes in registers
+//   (movmatrix).  Every row of every product and every accumulator register is in use: 16 products
+//   and 16 ldmatrix for 16 keys, and the loop waits for memory, not for its own instructions.
+// * the other head sizes, tiles of 8 keys: the q heads are the rows of both products (rows past
+//   the heads are zero) and the second product's k of 16 is the tile's 8 keys and 8 zeros: 48
+//   products for 16 keys.  Measured on head size 128 this form was bound by each warp's chain of
+//   about 300 instructions a tile (`ncu`: no memory stall, 0.4 instructions a cycle and scheduler).
+//
+// Few warps and small tiles keep several CTAs on an SM (three of four warps or four of three with
+// 16-key tiles; grids smaller than the GPU get one CTA of eight warps an SM).  Softmax is
+// float32; P is rounded to bfloat16 for the second product while the denominator sums the
+// unrounded values (as tinyvllm/kernels/paged_decode.cu:322-356 does).  The size of a piece
+// follows from the request's own position (and window) alone and is a whole number of tiles:
+// pieces of a request differ by one tile at most, so the CTAs of a cluster reach its barrier
+// together (pieces of whole multiples of 64 keys left the last CTAs of a cluster with little or
+// nothing to do, and the others waiting).
 #include <cooperative_groups.h>
 #include <type_traits>
 
@@ -35,8 +44,12 @@
 
 namespace cg = cooperative_groups;
 
-#define DEC_TILE 8          // keys of a stage (the second product's k = 16 is half zeros)
-#define DEC_STAGES 2        // stages of each warp's ring of keys and values in shared memory
+// Keys of a stage: TILE is a template parameter of the kernel.  8: the q heads are the rows of the
+// products' tiles and the keys their columns (the second product's k = 16 is half zeros); 16: the
+// keys are the rows of the first product (S^T = K Q^T) and the k of the second (O^T += V^T P^T),
+// the q heads the columns of both.
+// DEC_STAGES, the stages of each warp's ring of keys and values in shared memory, is a template
+// parameter of the kernel (2 with tiles of 8 keys).
 #define DEC_MAX_SPLITS 8
 
 // Where things lie in a CTA's dynamic shared memory (byte offsets; worked out by the launcher).
@@ -56,13 +69,13 @@ struct DecodeLayout {
     int part_m;       // float [splits][HPB]: partials of every CTA of the cluster; only the first CTA's
     int part_l;       //   copy is used, the others write theirs into it
     int part_o;       // float [splits][HPB][HEAD_DIM]
-    int ring;         // per warp: DEC_STAGES x (keys, values) x [8 keys][HEAD_DIM] bfloat16, chunk c of key k at
+    int ring;         // per warp: DEC_STAGES x (keys, values) x [TILE keys][HEAD_DIM] bfloat16, chunk c of key k at
                       //   c ^ (k & 7); after the loop the warp's partial output float [HPB][HEAD_DIM] lies here
     int slots;        // int [DEC_WARPS][warp_slot_capacity]
     int total;        // bytes
 };
 
-static DecodeLayout decode_layout(int head_dim, int hpb, int warps, int splits, int warp_slots) {
+static DecodeLayout decode_layout(int head_dim, int hpb, int warps, int splits, int warp_slots, int tile, int stages) {
     DecodeLayout l;
     int at = 0;
     auto take = [&](int bytes) { const int here = at; at += (bytes + 15) / 16 * 16; return here; };
@@ -74,7 +87,7 @@ static DecodeLayout decode_layout(int head_dim, int hpb, int warps, int splits, 
     l.part_m = take(splits * hpb * 4);
     l.part_l = take(splits * hpb * 4);
     l.part_o = take(splits * hpb * head_dim * 4);
-    l.ring = take(warps * DEC_STAGES * 2 * DEC_TILE * head_dim * 2);
+    l.ring = take(warps * stages * 2 * tile * head_dim * 2);
     l.slots = take(warps * warp_slots * 4);
     l.total = at;
     return l;
@@ -94,6 +107,20 @@ __device__ __forceinline__ void dec_mma(float (&d)[4], uint32_t a0, uint32_t a2,
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
+}
+
+// d (16 x 8) += a (16 x 16) . b (16 x 8), all four registers of a and d in use
+__device__ __forceinline__ void dec_mma_full(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// The transpose of an 8 x 8 matrix of 16-bit values held as a product's fragment (lane l: row l / 4,
+// columns 2 (l % 4) and the next): afterwards lane l holds rows 2 (l % 4) and the next of column l / 4.
+__device__ __forceinline__ uint32_t dec_transpose_8x8(uint32_t v) {
+    uint32_t t;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(t) : "r"(v));
+    return t;
 }
 
 // One head of the new token in a warp's registers: lane l holds elements l + 32 i of the first half
@@ -189,8 +216,9 @@ __device__ __forceinline__ void store_head(const HeadRegs<HEAD_DIM>& x, T* to, i
 // and is up to a tenth faster with them than with 128 and spills, so the cap follows the grid:
 // four CTAs of four warps an SM (128 registers) only where the grid needs them, three (160) for
 // grids of up to three CTAs an SM, none for the eight-warp CTAs of grids smaller than the GPU and
-// for a head of 256, which keeps its output tile in twice the registers.
-template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, typename W>
+// for a head of 256, which keeps its output tile in twice the registers.  With 16-key tiles
+// (twice the ring per warp) the larger grids get CTAs of three warps, four to an SM.
+template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, int TILE, int DEC_STAGES, typename W>
 __global__ void __launch_bounds__(DEC_WARPS * 32, RESIDENT)
 decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_table,
@@ -205,10 +233,10 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     // arrays hold; rows past heads_here stay zero): groups of 3, 5, 6 or 7 heads run on the next size up
     constexpr int CPR = HEAD_DIM / 8;          // 16-byte chunks of a key's row
     constexpr int KPI = 32 / CPR;              // keys a warp copies per instruction
-    constexpr int WARP_KEYS = DEC_TILE;
-    static_assert(HPB <= 8 && 32 % CPR == 0 && DEC_TILE % KPI == 0 && HEAD_DIM % 32 == 0, "shape of the tile");
+    constexpr int WARP_KEYS = TILE;
+    static_assert(HPB <= 8 && 32 % CPR == 0 && TILE % KPI == 0 && HEAD_DIM % 32 == 0 && (TILE == 8 || TILE == 16), "shape of the tile");
     extern __shared__ __align__(16) unsigned char shared_raw[];
-    constexpr int TILE_WORDS = DEC_TILE * HEAD_DIM / 8;                 // 16-byte words of a tile of keys
+    constexpr int TILE_WORDS = TILE * HEAD_DIM / 8;                 // 16-byte words of a tile of keys
     // the arrays of the layout, worked out where they are used (nothing of this stays in registers
     // through the loop over the keys)
 #define q_s (reinterpret_cast<float*>(shared_raw + layout.q))                  /* [HPB][HEAD_DIM] */
@@ -270,7 +298,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     // request alone; piece `split` is this CTA's.  Keys [first, last] of it are in the cache.
     const int lo = window > 0 ? max(0, position - window + 1) : 0;
     const int range_first = lo - lo % 64;
-    const int split_keys = ((position - range_first + splits) / splits + DEC_TILE - 1) / DEC_TILE * DEC_TILE;
+    const int split_keys = ((position - range_first + splits) / splits + TILE - 1) / TILE * TILE;
     const int own_split = (position - range_first) / split_keys;     // holds the new token
     const int base = range_first + split * split_keys;
     const int first = max(lo, base);
@@ -293,7 +321,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
 
     // Cache rows of this warp's keys, looked up once: where a tile of 8 keys lies inside one page,
     // the row of the tile's first key (-1: the page is not there); else one row per key (-1: no key).
-    const bool by_tile = page_size % DEC_TILE == 0;
+    const bool by_tile = page_size % TILE == 0;
     mine = min(mine, by_tile ? warp_slot_capacity : warp_slot_capacity / WARP_KEYS);     // sized for the context limit
     int* my_slots = slot_s + warp * warp_slot_capacity;
     if (by_tile) {
@@ -320,7 +348,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         uint4* values_to = ring_of(warp, i % DEC_STAGES, 1);
         const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
 #pragma unroll
-        for (int u = 0; u < DEC_TILE / KPI; ++u) {
+        for (int u = 0; u < TILE / KPI; ++u) {
             const int key = u * KPI + key_in_instr;
             int slot;
             if (by_tile) {
@@ -402,92 +430,234 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
             q_frag[ks][1] = pack_bf16x2(qh[8], qh[9]);
         }
     }
-    float m_run = -INFINITY, l_run = 0.0f;      // of row g; the four lanes of a row hold the same
-    float o_run[HEAD_DIM / 8][4];               // [n tile][row g: columns 2 t4, 2 t4 + 1 | row g + 8: unused]
+    if constexpr (TILE == 16) {
+        // ---- keys as rows.  S^T[key][head] = K Q^T: the tile's 16 keys are the rows, the CTA's q heads
+        // the 8 columns (q_frag is the b operand as it stands: head g, dimensions 2 t4.. of the k
+        // step); O^T[dimension][head] += V^T P^T with the keys as k.  A lane holds heads 2 t4 and
+        // 2 t4 + 1: of keys g and g + 8 in S^T, of dimensions g and g + 8 of every 16 in O^T.
+        float m_run[2] = {-INFINITY, -INFINITY};    // of heads 2 t4, 2 t4 + 1; the same in the 8 lanes of a t4
+        float l_run[2] = {0.0f, 0.0f};              // this lane's share (its keys g, g + 8 of every tile)
+        float o_run[HEAD_DIM / 16][4];
 #pragma unroll
-    for (int n = 0; n < HEAD_DIM / 8; ++n)
+        for (int n = 0; n < HEAD_DIM / 16; ++n)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) o_run[n][i] = 0.0f;
+            for (int e = 0; e < 4; ++e) o_run[n][e] = 0.0f;
+        // lane l of an ldmatrix names a row of one of its four 8 x 8 matrices: matrix l / 8, row l % 8
+        const int matrix = lane >> 3, matrix_row = lane & 7;
+        // K as the a operand: matrices (keys 0..7 | 8..15) x (chunk 2 ks | 2 ks + 1) in that order
+        const int k_key = matrix_row + 8 * (matrix & 1);
+        const int k_row = k_key * CPR, k_flip = (matrix >> 1) ^ matrix_row;          // chunk ^ (key & 7) = 2 ks ^ k_flip
+        // V^T as the a operand (transposing loads): matrices (chunk 2 mt | 2 mt + 1) x (keys 0..7 | 8..15)
+        const int v_key = matrix_row + 8 * (matrix >> 1);
+        const int v_row = v_key * CPR, v_flip = (matrix & 1) ^ matrix_row;
 
-    for (int i = 0; i < mine; ++i) {
-        // the next sub-tile is asked for before this one is waited for (asking after the products
-        // instead, with every stage filled up front, measured 1 % slower on the whole step)
-        if (i + DEC_STAGES - 1 < mine) issue(i + DEC_STAGES - 1);
-        cp_async_commit();
-        cp_async_wait<DEC_STAGES - 1>();        // sub-tile i has landed ...
-        __syncwarp();                           // ... for every lane of the warp
-        const uint4* k_tile = ring_of(warp, i % DEC_STAGES, 0);
-        const uint4* v_tile = ring_of(warp, i % DEC_STAGES, 1);
-        const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
-
-        // S[row][key] for the 8 keys of the tile
-        float s_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        {
-            const int key = lane & 7;
+        // A tile that lies inside a page and inside the piece is copied from one address: what a lane
+        // adds to it does not change from tile to tile (chunk `sub` of keys key_in_instr,
+        // key_in_instr + KPI, ...; with u KPI + key_in_instr for the key, its place in the stage is
+        // (lane_place ^ (u KPI & 7)) + u KPI CPR: one XOR and constants).
+        const uint32_t my_ring = smem_address(ring_of(warp, 0, 0));
+        const uint32_t lane_place = key_in_instr * CPR + (sub ^ key_in_instr);
+        const bf16* k_lane = key_cache + (key_in_instr * HEAD_DIM + sub * 8);
+        const bf16* v_lane = value_cache + (key_in_instr * HEAD_DIM + sub * 8);
+        auto issue_whole = [&](int i) {
+            const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
+            const int tile_slot = by_tile ? my_slots[i] : -1;
+            if (tile_slot < 0 || key0 < first || key0 + TILE - 1 > last) {           // the whole warp
+                issue(i);
+                return;
+            }
+            const uint32_t keys_to = my_ring + (uint32_t)((i % DEC_STAGES) * 2 * TILE_WORDS * 16);
+            const bf16* k_from = k_lane + (int64_t)tile_slot * HEAD_DIM;
+            const bf16* v_from = v_lane + (int64_t)tile_slot * HEAD_DIM;
 #pragma unroll
-            for (int ks2 = 0; ks2 < HEAD_DIM / 32; ++ks2) {
-                uint32_t b[4];
-                const int chunk = ks2 * 4 + (lane >> 3);
-                dec_ldmatrix_x4(b, k_tile + key * CPR + (chunk ^ key));
-                dec_mma(s_acc, q_frag[2 * ks2][0], q_frag[2 * ks2][1], b[0], b[1]);
-                dec_mma(s_acc, q_frag[2 * ks2 + 1][0], q_frag[2 * ks2 + 1][1], b[2], b[3]);
+            for (int u = 0; u < TILE / KPI; ++u) {
+                const uint32_t to = keys_to + ((lane_place ^ ((u * KPI) & 7)) + u * KPI * CPR) * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(to), "l"(k_from + u * KPI * HEAD_DIM));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(to + TILE_WORDS * 16), "l"(v_from + u * KPI * HEAD_DIM));
+            }
+        };
+
+        for (int i = 0; i < mine; ++i) {
+            if (i + DEC_STAGES - 1 < mine) issue_whole(i + DEC_STAGES - 1);
+            cp_async_commit();
+            cp_async_wait<DEC_STAGES - 1>();        // sub-tile i has landed ...
+            __syncwarp();                           // ... for every lane of the warp
+            const uint4* k_tile = ring_of(warp, i % DEC_STAGES, 0);
+            const uint4* v_tile = ring_of(warp, i % DEC_STAGES, 1);
+            const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
+
+            // even and odd k steps sum apart: a product waits for the one two before it only
+            float s_even[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s_odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int ks = 0; ks < HEAD_DIM / 16; ks += 2) {
+                uint32_t a_even[4], a_odd[4];
+                dec_ldmatrix_x4(a_even, k_tile + k_row + ((2 * ks) ^ k_flip));
+                dec_ldmatrix_x4(a_odd, k_tile + k_row + ((2 * ks + 2) ^ k_flip));
+                dec_mma_full(s_even, a_even, q_frag[ks][0], q_frag[ks][1]);
+                dec_mma_full(s_odd, a_odd, q_frag[ks + 1][0], q_frag[ks + 1][1]);
+            }
+            // online softmax per head (column): this lane holds keys g (e = 0) and g + 8 (e = 1)
+            float score[2][2];                      // [key e][head j]
+            float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + g + 8 * e;
+                const bool valid = key >= first && key <= last;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    score[e][j] = valid ? __fmul_rn(__fadd_rn(s_even[2 * e + j], s_odd[2 * e + j]), scale) : -INFINITY;
+                    tile_max[j] = fmaxf(tile_max[j], score[e][j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                tile_max[j] = fmaxf(tile_max[j], __shfl_xor_sync(0xffffffffu, tile_max[j], 4));
+                tile_max[j] = fmaxf(tile_max[j], __shfl_xor_sync(0xffffffffu, tile_max[j], 8));
+                tile_max[j] = fmaxf(tile_max[j], __shfl_xor_sync(0xffffffffu, tile_max[j], 16));
+            }
+            float rescale[2], prob[2][2];
+            bool changed = false;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float new_max = fmaxf(m_run[j], tile_max[j]);            // finite: the sub-tile has a valid key
+                rescale[j] = m_run[j] == -INFINITY ? 0.0f : __expf(m_run[j] - new_max);
+                changed = changed || new_max != m_run[j];
+                m_run[j] = new_max;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) prob[e][j] = score[e][j] == -INFINITY ? 0.0f : __expf(score[e][j] - new_max);
+                l_run[j] = l_run[j] * rescale[j] + (prob[0][j] + prob[1][j]);
+            }
+            // P^T as the b operand: the transposes of P[keys 0..7][heads] and P[keys 8..15][heads]
+            const uint32_t p_lo = dec_transpose_8x8(pack_bf16x2(prob[0][0], prob[0][1]));
+            const uint32_t p_hi = dec_transpose_8x8(pack_bf16x2(prob[1][0], prob[1][1]));
+            if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll
+                for (int n = 0; n < HEAD_DIM / 16; ++n) {
+                    o_run[n][0] *= rescale[0]; o_run[n][1] *= rescale[1];
+                    o_run[n][2] *= rescale[0]; o_run[n][3] *= rescale[1];
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < HEAD_DIM / 16; ++mt) {
+                uint32_t a[4];
+                dec_ldmatrix_x4_trans(a, v_tile + v_row + ((2 * mt) ^ v_flip));
+                dec_mma_full(o_run[mt], a, p_lo, p_hi);
+            }
+            __syncwarp();                           // the stage may be filled again
+        }
+        pdl_launch_dependents();
+
+        // ---- the warp's partial result to where its ring was; the lanes' shares of the denominators
+        // are added up over the 8 lanes of a t4 first
+        cp_async_wait<0>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 4);
+            l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 8);
+            l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 16);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int head = 2 * t4 + j;
+            if (head < heads_here) {
+                float* mine_o = warp_o_of(warp) + head * HEAD_DIM;
+#pragma unroll
+                for (int n = 0; n < HEAD_DIM / 16; ++n) {
+                    mine_o[n * 16 + g] = o_run[n][j];
+                    mine_o[n * 16 + g + 8] = o_run[n][2 + j];
+                }
+                if (g == 0) { warp_m_s[warp * HPB + head] = m_run[j]; warp_l_s[warp * HPB + head] = l_run[j]; }
             }
         }
-        // online softmax of row g over the 8 keys (this lane holds keys 2 t4, 2 t4 + 1)
-        float score[2];
-        bool valid[2];
-        float tile_max = -INFINITY;
+    } else {
+        float m_run = -INFINITY, l_run = 0.0f;      // of row g; the four lanes of a row hold the same
+        float o_run[HEAD_DIM / 8][4];               // [n tile][row g: columns 2 t4, 2 t4 + 1 | row g + 8: unused]
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const int key = key0 + 2 * t4 + e;
-            valid[e] = key >= first && key <= last;
-            score[e] = valid[e] ? __fmul_rn(s_acc[e], scale) : -INFINITY;
-            tile_max = fmaxf(tile_max, score[e]);
-        }
-        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-        const float new_max = fmaxf(m_run, tile_max);          // finite: the sub-tile has a valid key
-        const float rescale = m_run == -INFINITY ? 0.0f : __expf(m_run - new_max);
-        const bool moved = __any_sync(0xffffffffu, new_max != m_run);
-        m_run = new_max;
-        float prob[2];
+        for (int n = 0; n < HEAD_DIM / 8; ++n)
 #pragma unroll
-        for (int e = 0; e < 2; ++e) prob[e] = valid[e] ? __expf(score[e] - new_max) : 0.0f;
-        float sum = prob[0] + prob[1];
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        l_run = l_run * rescale + sum;
-        const uint32_t p_lo = pack_bf16x2(prob[0], prob[1]);            // keys 0..7; k 8..15 of the product are zero
-        if (moved) {
-#pragma unroll
-            for (int n = 0; n < HEAD_DIM / 8; ++n) { o_run[n][0] *= rescale; o_run[n][1] *= rescale; }
-        }
-        // O += P V, 32 head dimensions (four n tiles) per ldmatrix
-#pragma unroll
-        for (int n4 = 0; n4 < HEAD_DIM / 32; ++n4) {
-            uint32_t b[4];
-            const int key = lane & 7;
-            const int chunk = n4 * 4 + (lane >> 3);
-            dec_ldmatrix_x4_trans(b, v_tile + key * CPR + (chunk ^ key));
-#pragma unroll
-            for (int m = 0; m < 4; ++m) dec_mma(o_run[4 * n4 + m], p_lo, 0u, b[m], 0u);
-        }
-        __syncwarp();                           // the stage may be filled again
-    }
-    pdl_launch_dependents();
+            for (int i = 0; i < 4; ++i) o_run[n][i] = 0.0f;
 
-    // ---- the warps' partial results, merged below in a fixed order; a warp's output goes where its
-    // ring was (every tile it asked for has been used)
-    cp_async_wait<0>();
-    __syncwarp();
-    if (g < heads_here) {
-        float* mine_o = warp_o_of(warp) + g * HEAD_DIM;
+        for (int i = 0; i < mine; ++i) {
+            // the next sub-tile is asked for before this one is waited for (asking after the products
+            // instead, with every stage filled up front, measured 1 % slower on the whole step)
+            if (i + DEC_STAGES - 1 < mine) issue(i + DEC_STAGES - 1);
+            cp_async_commit();
+            cp_async_wait<DEC_STAGES - 1>();        // sub-tile i has landed ...
+            __syncwarp();                           // ... for every lane of the warp
+            const uint4* k_tile = ring_of(warp, i % DEC_STAGES, 0);
+            const uint4* v_tile = ring_of(warp, i % DEC_STAGES, 1);
+            const int key0 = base + (first_tile + i * DEC_WARPS) * WARP_KEYS;
+
+            // S[row][key] for the 8 keys of the tile
+            float s_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            {
+                const int key = lane & 7;
 #pragma unroll
-        for (int n = 0; n < HEAD_DIM / 8; ++n) {
-            mine_o[n * 8 + 2 * t4] = o_run[n][0];
-            mine_o[n * 8 + 2 * t4 + 1] = o_run[n][1];
+                for (int ks2 = 0; ks2 < HEAD_DIM / 32; ++ks2) {
+                    uint32_t b[4];
+                    const int chunk = ks2 * 4 + (lane >> 3);
+                    dec_ldmatrix_x4(b, k_tile + key * CPR + (chunk ^ key));
+                    dec_mma(s_acc, q_frag[2 * ks2][0], q_frag[2 * ks2][1], b[0], b[1]);
+                    dec_mma(s_acc, q_frag[2 * ks2 + 1][0], q_frag[2 * ks2 + 1][1], b[2], b[3]);
+                }
+            }
+            // online softmax of row g over the 8 keys (this lane holds keys 2 t4, 2 t4 + 1)
+            float score[2];
+            bool valid[2];
+            float tile_max = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + 2 * t4 + e;
+                valid[e] = key >= first && key <= last;
+                score[e] = valid[e] ? __fmul_rn(s_acc[e], scale) : -INFINITY;
+                tile_max = fmaxf(tile_max, score[e]);
+            }
+            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+            const float new_max = fmaxf(m_run, tile_max);          // finite: the sub-tile has a valid key
+            const float rescale = m_run == -INFINITY ? 0.0f : __expf(m_run - new_max);
+            const bool moved = __any_sync(0xffffffffu, new_max != m_run);
+            m_run = new_max;
+            float prob[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) prob[e] = valid[e] ? __expf(score[e] - new_max) : 0.0f;
+            float sum = prob[0] + prob[1];
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l_run = l_run * rescale + sum;
+            const uint32_t p_lo = pack_bf16x2(prob[0], prob[1]);            // keys 0..7; k 8..15 of the product are zero
+            if (moved) {
+#pragma unroll
+                for (int n = 0; n < HEAD_DIM / 8; ++n) { o_run[n][0] *= rescale; o_run[n][1] *= rescale; }
+            }
+            // O += P V, 32 head dimensions (four n tiles) per ldmatrix
+#pragma unroll
+            for (int n4 = 0; n4 < HEAD_DIM / 32; ++n4) {
+                uint32_t b[4];
+                const int key = lane & 7;
+                const int chunk = n4 * 4 + (lane >> 3);
+                dec_ldmatrix_x4_trans(b, v_tile + key * CPR + (chunk ^ key));
+#pragma unroll
+                for (int m = 0; m < 4; ++m) dec_mma(o_run[4 * n4 + m], p_lo, 0u, b[m], 0u);
+            }
+            __syncwarp();                           // the stage may be filled again
         }
-        if (t4 == 0) { warp_m_s[warp * HPB + g] = m_run; warp_l_s[warp * HPB + g] = l_run; }
+        pdl_launch_dependents();
+
+        // ---- the warps' partial results, merged below in a fixed order; a warp's output goes where its
+        // ring was (every tile it asked for has been used)
+        cp_async_wait<0>();
+        __syncwarp();
+        if (g < heads_here) {
+            float* mine_o = warp_o_of(warp) + g * HEAD_DIM;
+#pragma unroll
+            for (int n = 0; n < HEAD_DIM / 8; ++n) {
+                mine_o[n * 8 + 2 * t4] = o_run[n][0];
+                mine_o[n * 8 + 2 * t4 + 1] = o_run[n][1];
+            }
+            if (t4 == 0) { warp_m_s[warp * HPB + g] = m_run; warp_l_s[warp * HPB + g] = l_run; }
+        }
     }
     __syncthreads();
     cluster_wait();
@@ -578,14 +748,14 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
 #undef warp_m_s
 #undef warp_l_s
 
-template <int DEC_WARPS>
+template <int DEC_WARPS, int TILE>
 static int decode_warp_slot_capacity(int max_context, int splits, int page_size) {
-    const int split_keys = ((max_context + 64 + splits - 1) / splits + DEC_TILE - 1) / DEC_TILE * DEC_TILE;
-    const int tiles = split_keys / (DEC_TILE * DEC_WARPS) + 2;
-    return page_size % DEC_TILE == 0 ? tiles : tiles * DEC_TILE;
+    const int split_keys = ((max_context + 64 + splits - 1) / splits + TILE - 1) / TILE * TILE;
+    const int tiles = split_keys / (TILE * DEC_WARPS) + 2;
+    return page_size % TILE == 0 ? tiles : tiles * TILE;
 }
 
-template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, typename W>
+template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, int TILE, int DEC_STAGES, typename W>
 static int launch_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                          const float* cos_table, const float* sin_table, int table_positions,
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
@@ -593,9 +763,9 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
                          int splits, int write_cache, int max_context, int pdl, cudaStream_t stream, int heads_here,
                          int sm_count) {
-    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, RESIDENT, W>;
-    const int warp_slots = decode_warp_slot_capacity<DEC_WARPS>(max_context, splits, page_size);
-    const DecodeLayout layout = decode_layout(HEAD_DIM, HPB, DEC_WARPS, splits, warp_slots);
+    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, RESIDENT, TILE, DEC_STAGES, W>;
+    const int warp_slots = decode_warp_slot_capacity<DEC_WARPS, TILE>(max_context, splits, page_size);
+    const DecodeLayout layout = decode_layout(HEAD_DIM, HPB, DEC_WARPS, splits, warp_slots, TILE, DEC_STAGES);
     if (layout.total > 200 * 1024) return TVB_BAD_ARGUMENT;
     static int configured = 0;                   // the largest size asked for so far, per instantiation
     if (layout.total > configured) {
@@ -673,9 +843,14 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
                     sm_count
 #define DECODE_BY_WARPS(D, H, WT)                                       \
     do {                                                                \
-        if (wide) return launch_decode<D, H, 8, 1, WT>(DECODE_ARGS);    \
-        if (roomy) return launch_decode<D, H, 4, (D > 128 ? 1 : 3), WT>(DECODE_ARGS); \
-        return launch_decode<D, H, 4, (D > 128 ? 1 : 4), WT>(DECODE_ARGS);            \
+        if (D == 128) {                                                       \
+            if (wide) return launch_decode<128, H, 8, 1, 16, 2, WT>(DECODE_ARGS);  \
+            if (roomy) return launch_decode<128, H, 4, 3, 16, 2, WT>(DECODE_ARGS); \
+            return launch_decode<128, H, 3, 4, 16, 2, WT>(DECODE_ARGS);       \
+        }                                                                     \
+        if (wide) return launch_decode<D, H, 8, 1, 8, 2, WT>(DECODE_ARGS);    \
+        if (roomy) return launch_decode<D, H, 4, (D > 128 ? 1 : 3), 8, 2, WT>(DECODE_ARGS); \
+        return launch_decode<D, H, 4, (D > 128 ? 1 : 4), 8, 2, WT>(DECODE_ARGS);            \
     } while (0)
 #define DECODE_BY_HPB(D, WT)                                            \
     do {                                                                \

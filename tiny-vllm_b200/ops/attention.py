@@ -43,14 +43,15 @@ def decode_splits(max_model_len: int, rows: int = 1) -> int:
     """Cluster size of the fused decode kernel: into how many pieces a request's keys are cut.
     The size of a piece follows from the request's own position inside the kernel.  Few requests
     need many pieces to fill the GPU; with many requests the pieces' fixed cost (set-up, merge)
-    outweighs that, so their number falls with the rows of the step: about 48 pieces a kv head
-    over all rows, 2 at least (measured at 16 q / 8 kv heads, context 2,100, us a layer: 8 rows
-    8 pieces 20.9, 6 pieces 21.0 alone and 1 % faster inside the step; 16 rows 4 pieces 33.1,
-    3 pieces 32.4; 32 rows 2 pieces 56.5, 4 pieces 59.9; 64 rows 2 pieces 103.2, 1 piece 107.1).
+    outweighs that, so their number falls with the rows of the step: about 32 pieces a kv head
+    over all rows; beyond 48 rows two pieces, with which the grid runs as CTAs of three warps in
+    two waves (measured at 16 q / 8 kv heads, head size 128, context 2,100, us a layer: 8 rows
+    4 pieces 18.7, 6 pieces 20.0; 16 rows 2 pieces 30.9, 4 pieces 31.9; 32 rows 1 piece 53.1,
+    2 pieces 56.0; 64 rows 2 pieces 95.9, 1 piece 104.4, 3 pieces 102.5).
     A request's result differs between piece counts by rounding only (the order in which partial
     sums are merged)."""
     by_length = max(1, min(DECODE_MAX_SPLITS, -(-max_model_len // DECODE_SPLIT_GRAIN)))
-    by_rows = max(2, min(DECODE_MAX_SPLITS, 48 // max(rows, 1)))
+    by_rows = 2 if rows > 48 else max(1, min(DECODE_MAX_SPLITS, 32 // max(rows, 1)))
     return max(1, min(by_length, by_rows))
 
 
