@@ -482,7 +482,9 @@ def test_attention_prefill_tc_refuses():
                                    # groups of 5 (40 q heads on 8 kv heads), 3, 6 and 7: fewer heads than the tile
                                    # holds; 12 = two CTAs of 6; 10 at head size 256 = two of 5 would not fit: five of 2
                                    (10, 2, 128, 16, 4), (3, 1, 64, 16, 2), (12, 2, 128, 16, 8), (7, 1, 128, 32, 3),
-                                   (24, 2, 64, 16, 2), (10, 1, 256, 16, 2)])
+                                   (24, 2, 64, 16, 2), (10, 1, 256, 16, 2),
+                                   # head size 128 walks tiles of 16 keys: pages that hold half a tile, three tiles
+                                   (16, 8, 128, 8, 8), (4, 2, 128, 48, 6), (64, 8, 128, 16, 1)])
 def test_attention_decode_fused(shape, window):
     """Raw projection in, attention out: against q/k norm + rotation + attention of the plain
     functions, with the new key and value checked in the cache."""
