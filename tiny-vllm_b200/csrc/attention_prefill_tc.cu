@@ -73,6 +73,7 @@ __device__ __forceinline__ float exp2_fast(float x) {
     return y;
 }
 
+template <bool PAIRED>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* block_tables, int table_stride,
@@ -82,10 +83,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t* aligned = raw_shared + (base - smem_address(raw_shared));
+    // PAIRED: two q heads of one kv head at a time, one softmax group each, both on every block of
+    // keys: a K or V tile in shared memory serves both (two Q tiles and a ring of four; else one
+    // and five).
+    constexpr int RING = PAIRED ? SLOTS - 1 : SLOTS;
     const uint32_t q_at = base;
-    const uint32_t kv_at = base + TILE_BYTES;
+    const uint32_t kv_at = base + (PAIRED ? 2 : 1) * TILE_BYTES;
     float* exchange = reinterpret_cast<float*>(aligned + TILE_BYTES * (1 + SLOTS));      // [QT][2]
-    const uint32_t bars = kv_at + SLOTS * TILE_BYTES + EXCHANGE_BYTES;
+    const uint32_t bars = base + (1 + SLOTS) * TILE_BYTES + EXCHANGE_BYTES;
     auto bar = [&](int i) { return bars + 8u * i; };
     uint32_t* tmem_base_slot =
         reinterpret_cast<uint32_t*>(aligned + TILE_BYTES * (1 + SLOTS) + EXCHANGE_BYTES + BARRIERS * 8);
@@ -93,7 +98,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     int* status = &tvb_attention_prefill_tc_status_word;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int items = num_tiles * num_q;
+    const int per_tile = PAIRED ? num_q / 2 : num_q;       // items of a tile of tokens
+    const int items = num_tiles * per_tile;
     const int pages_per_block = KT / page_size;
 
     if (threadIdx.x == 0) {
@@ -120,8 +126,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int g = (int)gridDim.x, c = (int)blockIdx.x;
         const int index = round * g + ((round & 1) ? g - 1 - c : c);
         if (index >= items) return false;
-        const int tile = index / num_q;
-        it.head = index % num_q;
+        const int tile = index / per_tile;
+        it.head = (index % per_tile) * (PAIRED ? 2 : 1);
         it.kv_head = it.head / (num_q / num_kv);
         it.first = tile_first[tile];
         it.count = tile_count[tile];
@@ -151,8 +157,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             return lane < pages_per_block && index < it.valid_pages ? __ldg(it.table + index) : -1;
         };
         auto load_tile = [&](const CUtensorMap* map, const Item& it, int page) -> bool {
-            const int slot = ring % SLOTS;
-            const uint32_t phase = (ring / SLOTS) & 1u;
+            const int slot = ring % RING;
+            const uint32_t phase = (ring / RING) & 1u;
             if (!lane_wait(B_KV_EMPTY + slot, phase ^ 1u, 1)) return false;
             if (lane == 0) mbar_arrive_expect(bar(B_KV_FULL + slot), TILE_BYTES);
             __syncwarp();
@@ -165,34 +171,138 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             return true;
         };
         pdl_wait();                             // q, keys and values come from the kernel before this one
-        for (int round = 0; alive; ++round) {
-            Item it;
-            if (!item_of(round, it)) break;
-            // pages of the block whose V is next, of the block whose K is next, and of the one after
-            int page_v = page_of(it, it.block0);
-            int page_k = it.blocks > 1 ? page_of(it, it.block0 + 1) : -1;
-            if (!lane_wait(B_Q_EMPTY, (done_items & 1u) ^ 1u, 2)) break;
-            if (lane == 0) {
-                mbar_arrive_expect(bar(B_Q_FULL), TILE_BYTES);
-                tma_load_2d(q_at, &map_q, it.head * HD, it.first, bar(B_Q_FULL));
-                tma_load_2d(q_at + HALF_BYTES, &map_q, it.head * HD + 64, it.first, bar(B_Q_FULL));
+        if constexpr (PAIRED) {
+            // the tiles of an item in the order K0, V0, K1, V1, ...
+            for (int round = 0; alive; ++round) {
+                Item it;
+                if (!item_of(round, it)) break;
+                int page = page_of(it, it.block0);
+                if (!lane_wait(B_Q_EMPTY, (done_items & 1u) ^ 1u, 2)) break;
+                if (lane == 0) {
+                    mbar_arrive_expect(bar(B_Q_FULL), 2 * TILE_BYTES);
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        tma_load_2d(q_at + b * TILE_BYTES, &map_q, (it.head + b) * HD, it.first, bar(B_Q_FULL));
+                        tma_load_2d(q_at + b * TILE_BYTES + HALF_BYTES, &map_q, (it.head + b) * HD + 64, it.first, bar(B_Q_FULL));
+                    }
+                }
+                for (int j = 0; j < it.blocks && alive; ++j) {
+                    const int page_after = j + 1 < it.blocks ? page_of(it, it.block0 + j + 1) : -1;
+                    alive = load_tile(&map_k, it, page);
+                    if (alive) alive = load_tile(&map_v, it, page);
+                    page = page_after;
+                }
+                ++done_items;
             }
-            alive = load_tile(&map_k, it, page_v);
-            for (int j = 0; j < it.blocks && alive; ++j) {
-                const int page_after = j + 2 < it.blocks ? page_of(it, it.block0 + j + 2) : -1;
-                if (j + 1 < it.blocks) alive = load_tile(&map_k, it, page_k);
-                if (alive) alive = load_tile(&map_v, it, page_v);
-                page_v = page_k;
-                page_k = page_after;
+        } else {
+            for (int round = 0; alive; ++round) {
+                Item it;
+                if (!item_of(round, it)) break;
+                // pages of the block whose V is next, of the block whose K is next, and of the one after
+                int page_v = page_of(it, it.block0);
+                int page_k = it.blocks > 1 ? page_of(it, it.block0 + 1) : -1;
+                if (!lane_wait(B_Q_EMPTY, (done_items & 1u) ^ 1u, 2)) break;
+                if (lane == 0) {
+                    mbar_arrive_expect(bar(B_Q_FULL), TILE_BYTES);
+                    tma_load_2d(q_at, &map_q, it.head * HD, it.first, bar(B_Q_FULL));
+                    tma_load_2d(q_at + HALF_BYTES, &map_q, it.head * HD + 64, it.first, bar(B_Q_FULL));
+                }
+                alive = load_tile(&map_k, it, page_v);
+                for (int j = 0; j < it.blocks && alive; ++j) {
+                    const int page_after = j + 2 < it.blocks ? page_of(it, it.block0 + j + 2) : -1;
+                    if (j + 1 < it.blocks) alive = load_tile(&map_k, it, page_k);
+                    if (alive) alive = load_tile(&map_v, it, page_v);
+                    page_v = page_k;
+                    page_k = page_after;
+                }
+                ++done_items;
             }
-            ++done_items;
         }
         __syncwarp();
     } else if (warp == 1 || warp == 10) {
         // ---- products.  The tiles of an item with n blocks come through the ring in the order K0, K1,
         // V0, K2, V1, ..., V(n-1): K of block j is the item's tile 2 j - 1 (0 for j = 0), V of block j
         // its tile 2 j + 2 (2 n - 1 for the last).  Block j belongs to softmax group j & 1.
-        if (lane == 0 && warp == 1) {
+        if (PAIRED && lane == 0 && warp == 1) {
+            // both groups' S = Q K^T of every block: K of block j is the item's tile 2 j
+            constexpr uint32_t idesc_qk = instruction_descriptor_bf16(QT, KT, false);
+            uint32_t ring_base = 0, used = 0, done_items = 0;
+            bool alive = true;
+            for (int round = 0; alive; ++round) {
+                Item it;
+                if (!item_of(round, it)) break;
+                if (!mbar_wait(bar(B_Q_FULL), done_items & 1u, abort_flag, status, 8)) break;
+                for (int j = 0; j < it.blocks && alive; ++j) {
+                    const uint32_t n = used + j;                        // every group's n-th block
+                    const uint32_t tile = ring_base + 2 * j;
+                    const uint32_t slot = tile % RING, phase = (tile / RING) & 1u;
+                    if (!mbar_wait(bar(B_KV_FULL + slot), phase, abort_flag, status, 3)) { alive = false; break; }
+                    const uint32_t k_tile = kv_at + slot * TILE_BYTES;
+#pragma unroll
+                    for (uint32_t b = 0; b < 2; ++b) {
+                        // S of the group is also where its P lies: the product that read P of the block
+                        // before must have finished
+                        if (n > 0 && !mbar_wait(bar(B_P_READ + b), (n - 1) & 1u, abort_flag, status, 4)) { alive = false; break; }
+                        // The second group starts an item when the first has its first block's softmax
+                        // behind it: from then on one group's softmax runs under the other's products
+                        // (started together, both would do their softmax at the same time, on the same
+                        // issue slots and special-function unit, and the tensor cores would wait for both).
+                        if (b == 1 && j == 0 && !mbar_wait(bar(B_P_FULL), n & 1u, abort_flag, status, 9)) { alive = false; break; }
+                        tc_fence_after_sync();
+#pragma unroll
+                        for (int kk = 0; kk < HD / 16; ++kk) {
+                            const uint32_t half = (kk / 4) * HALF_BYTES, step = 2u * (kk % 4);
+                            tc_mma(tmem_base + b * KT, tile_descriptor(q_at + b * TILE_BYTES + half) + step,
+                                   tile_descriptor(k_tile + half) + step, idesc_qk, kk != 0);
+                        }
+                        tc_commit(bar(B_S_FULL + b));
+                    }
+                    if (alive) tc_commit(bar(B_KV_EMPTY + slot));
+                }
+                if (alive) tc_commit(bar(B_Q_EMPTY));
+                ring_base += 2 * it.blocks;
+                used += it.blocks;
+                ++done_items;
+            }
+        } else if (PAIRED && lane == 0) {
+            // both groups' O += P V of every block: V of block j is the item's tile 2 j + 1
+            constexpr uint32_t idesc_pv = instruction_descriptor_bf16(QT, HD, true);
+            uint32_t ring_base = 0, used = 0, done_items = 0;
+            bool alive = true;
+            for (int round = 0; alive; ++round) {
+                Item it;
+                if (!item_of(round, it)) break;
+                for (int j = 0; j < it.blocks && alive; ++j) {
+                    const uint32_t n = used + j;
+                    const uint32_t tile = ring_base + 2 * j + 1;
+                    const uint32_t slot = tile % RING, phase = (tile / RING) & 1u;
+                    const bool first_of_item = j == 0, last_of_item = j + 1 == it.blocks;
+                    if (!mbar_wait(bar(B_KV_FULL + slot), phase, abort_flag, status, 5)) { alive = false; break; }
+                    const uint32_t v_tile = kv_at + slot * TILE_BYTES;
+#pragma unroll
+                    for (uint32_t b = 0; b < 2; ++b) {
+                        if (!mbar_wait(bar(B_P_FULL + b), n & 1u, abort_flag, status, 6)) { alive = false; break; }
+                        if (first_of_item && !mbar_wait(bar(B_O_FREE + b), (done_items & 1u) ^ 1u, abort_flag, status, 7)) {
+                            alive = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+#pragma unroll
+                        for (int kk = 0; kk < KT / 16; ++kk) {
+                            tc_mma_a_in_tmem(tmem_base + 2 * KT + b * HD, tmem_base + b * KT + kk * 8,
+                                             tile_descriptor_mn_major(v_tile + kk * 2048, HALF_BYTES), idesc_pv,
+                                             !(first_of_item && kk == 0));
+                        }
+                        tc_commit(bar(B_P_READ + b));
+                        if (last_of_item) tc_commit(bar(B_O_LAST + b));
+                    }
+                    if (alive) tc_commit(bar(B_KV_EMPTY + slot));
+                }
+                ring_base += 2 * it.blocks;
+                used += it.blocks;
+                ++done_items;
+            }
+        } else if (lane == 0 && warp == 1) {
             constexpr uint32_t idesc_qk = instruction_descriptor_bf16(QT, KT, false);
             uint32_t ring_base = 0, used_a = 0, used_b = 0, done_items = 0;
             bool alive = true;
@@ -294,10 +404,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int lowest = window > 0 ? q_pos - window + 1 : 0;      // first key this row sees
             float reference = -INFINITY;      // what the exponentials of this row subtract (in log2 units)
             float l = 0.0f;                   // the denominator of this group's blocks
-            for (int j = group; j < it.blocks && alive; j += 2, ++used) {
+            for (int j = PAIRED ? 0 : group; j < it.blocks && alive; j += PAIRED ? 1 : 2, ++used) {
                 const uint32_t parity = used & 1u;
                 const int key0 = (it.block0 + j) * KT;
-                const bool has_previous = j >= 2;
+                const bool has_previous = j >= (PAIRED ? 1 : 2);
                 if (!warp_wait(B_S_FULL + group, parity, 10)) { alive = false; break; }
                 tc_fence_after_sync();
                 // below every row's diagonal and inside every row's window: no mask
@@ -385,6 +495,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 warp_arrive(B_P_FULL + group);
             }
             if (!alive) break;
+            if constexpr (PAIRED) {
+                // ---- the group's own head: O over its denominator, when the last product into O has finished
+                if (!warp_wait(B_O_LAST + group, finals & 1u, 13)) break;
+                ++finals;
+                const float inverse = l > 0.0f ? 1.0f / l : 0.0f;
+                tc_fence_after_sync();
+                bf16* out_row = out + (int64_t)(it.first + row) * out_stride + (it.head + group) * HD;
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t a[32];
+                    tmem_load_32(o_address + c, a);
+                    tmem_load_wait();
+                    if (c + 32 == HD) {
+                        tc_fence_before_sync();
+                        warp_arrive(B_O_FREE + group);
+                    }
+                    if (row < it.count) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8) {
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(a[e + i]) * inverse;
+                            *reinterpret_cast<uint4*>(out_row + c + e) = pack_bf16x8(f);
+                        }
+                    }
+                }
+                ++done_items;
+                continue;
+            }
             const int own_blocks = (it.blocks - group + 1) / 2;
             // the last product into this group's O has finished
             if (own_blocks > 0) {
@@ -536,16 +675,21 @@ extern "C" int tvb_attention_prefill_tc(const void* q, long long q_token_stride,
     if (!cache_map(&map_k, key_cache, pages, num_kv, page_size) ||
         !cache_map(&map_v, value_cache, pages, num_kv, page_size))
         return (int)cudaErrorNotSupported;
-    auto kernel = attention_prefill_tc_kernel;
-    static bool configured[64] = {false};
+    // Two q heads of a kv head per item where the heads pair up: every K and V tile then serves both
+    // (one head an item is bound by the copies of K and V: 64 KB a block for 8.4 MFLOP).  With few
+    // items (a prompt of 2,048 tokens of 16 heads: 128 pairs for 148 CTAs) single heads spread
+    // better: 39.7 against 47.9 us; at 8,192 tokens pairs take 285 against 382 us.
+    const bool paired = (num_q / num_kv) % 2 == 0 && (long long)num_tiles * (num_q / 2) * 2 >= 3ll * sms;
+    auto kernel = paired ? attention_prefill_tc_kernel<true> : attention_prefill_tc_kernel<false>;
+    static bool configured[2][64] = {{false}};
     int device = 0;
     cudaGetDevice(&device);
-    if (device >= 0 && device < 64 && !configured[device]) {
+    if (device >= 0 && device < 64 && !configured[paired][device]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SHARED_BYTES);
         if (e != cudaSuccess) return (int)e;
-        configured[device] = true;
+        configured[paired][device] = true;
     }
-    const long long items = (long long)num_tiles * num_q;
+    const long long items = (long long)num_tiles * (paired ? num_q / 2 : num_q);
     const int ctas = (int)(items < sms ? items : sms);
     TvbLaunch launch(dim3(ctas), dim3(THREADS), SHARED_BYTES, (cudaStream_t)stream, pdl);
     cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, map_q, map_k, map_v, block_tables, table_stride,
