@@ -821,13 +821,15 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
         return TVB_BAD_ARGUMENT;
     const int group = num_q / num_kv;
     // q heads a CTA serves (they share its keys); the tile that holds them is the next of 1, 2, 4, 8.
-    // Eight heads cost residency (87 KB of shared memory at head size 128) but no key is read twice.
+    // With eight heads no key is read twice.
     const int heads_here = decode_heads_per_cta(group, head_dim);
     const int hpb = heads_here <= 1 ? 1 : heads_here <= 2 ? 2 : heads_here <= 4 ? 4 : 8;
     cudaStream_t s = (cudaStream_t)stream;
-    // Four warps a CTA keep four CTAs on an SM, which is what counts when the grid fills the GPU;
-    // a grid of fewer CTAs than SMs (one or two requests) is faster with eight warps a CTA, each
-    // with half as many keys to walk (batch 1, context 2,100: 10.3 us against 12.8 us).
+    // The shape of a CTA follows the grid.  A grid of fewer CTAs than SMs (one or two requests) gets
+    // eight warps a CTA, each with half as many keys to walk (batch 1, context 2,100: 10.3 us against
+    // 12.8 us) and no register cap; grids of up to three CTAs an SM get four warps and three CTAs an
+    // SM (160 registers, no spills); larger ones four CTAs an SM: of four warps with 8-key tiles, of
+    // three with 16-key tiles (whose rings are twice as large).
     static int sm_count = 0;
     if (sm_count == 0) {
         int device = 0;
