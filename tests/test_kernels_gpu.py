@@ -441,6 +441,19 @@ def test_attention_prefill_tc(shape, window):
     close(got, want, dtype, bf16=1.2e-2)
 
 
+@pytest.mark.parametrize("window", [None, 1000])
+def test_attention_prefill_tc_two_heads_an_item(window):
+    """Enough tiles that the launcher gives every item two q heads of a kv head (a softmax group
+    each, every K and V tile used by both): a long prompt beside shorter ones, groups of 2 and 4."""
+    for nq, nkv, lengths, queries in ((16, 8, [3700, 130, 600], [3700, 130, 300]), (16, 4, [3900], [3900])):
+        d, dtype = 128, torch.bfloat16
+        case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=16, lengths=lengths, queries=queries, seed=nq + nkv)
+        want = plain_paged(case, d ** -0.5, window, dtype)
+        got, big, rest = run_prefill_tc(case, nq=nq, nkv=nkv, d=d, window=window, scale=d ** -0.5)
+        assert len(big[0]) * nq >= 3 * torch.cuda.get_device_properties(0).multi_processor_count    # pairs are used
+        close(got, want, dtype, bf16=1.2e-2)
+
+
 def test_attention_prefill_tc_window_edge_far_key_and_growing_maximum():
     """One key far back scaled up so that its score stands out (it must be found, or be cut off
     exactly at the window's edge), and keys that grow towards the end so that every row's
