@@ -82,11 +82,15 @@ def test_rope_tables_match_the_float32_formula():
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 @pytest.mark.parametrize("heads", [(8, 2, 64), (3, 3, 80), (16, 8, 128), (2, 1, 256), (5, 5, 16), (40, 8, 32),
-                                   (36, 4, 128)])
+                                   (36, 4, 128), (36, 4, 128, 500), (36, 4, 128, 1300)])
 def test_qk_norm_rope_store(dtype, heads):
-    nq, nkv, d = heads
+    # 23 tokens: every batch of a token's heads has a CTA of its own; 500: two CTAs share three
+    # batches; 1,300: one CTA goes round all of them
+    nq, nkv, d = heads[:3]
     torch.manual_seed(d)
-    tokens, page, pages = 23, 8, 9
+    tokens = heads[3] if len(heads) > 3 else 23
+    page = 8
+    pages = tokens // page + 7
     qkv = torch.randn(tokens, (nq + 2 * nkv) * d).to(dtype)
     qw, kw = (1 + 0.1 * torch.randn(d)).to(dtype), (1 + 0.1 * torch.randn(d)).to(dtype)
     positions = torch.randint(0, 3000, (tokens,), dtype=torch.int32)
