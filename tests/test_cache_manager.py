@@ -59,6 +59,30 @@ def test_plan_commit_tables_and_slots():
     m.check()
 
 
+def test_the_next_request_gets_neighbouring_pages_in_rising_order():
+    """A fresh pool hands out rising page numbers, and what a request gives back (at its end, or
+    when a plan is rolled back) comes out again in the same order: the prefill attention copies
+    neighbouring pages several at a time."""
+    m = manager(pages=12, page_size=4)
+    m.open("a")
+    plan = m.plan([("a", 22)])
+    first = list(plan.entries[0].tables[0])
+    assert first == list(range(first[0], first[0] + 6))
+    m.commit(plan)
+    m.open("b")
+    planned = m.plan([("b", 9)])
+    held = list(planned.entries[0].tables[0])
+    m.rollback(planned)
+    planned = m.plan([("b", 9)])
+    assert list(planned.entries[0].tables[0]) == held == list(range(held[0], held[0] + 3))
+    m.commit(planned)
+    m.close("a")
+    m.open("c")
+    plan = m.plan([("c", 24)])
+    assert list(plan.entries[0].tables[0]) == first
+    m.check()
+
+
 def test_commit_of_what_was_written_gives_the_rest_back():
     """A plan for several tokens per request (a run of decode steps) that ended early."""
     m = manager(pages=12, page_size=4)

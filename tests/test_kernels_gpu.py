@@ -129,13 +129,26 @@ def by_slot(cache):
     return cache.permute(0, 2, 1, 3).reshape(pages * page, nkv, d)
 
 
-def paged_case(dtype, *, nq, nkv, d, page, lengths, queries, seed, boost=None):
+def paged_case(dtype, *, nq, nkv, d, page, lengths, queries, seed, boost=None, layout="shuffled"):
     """Requests with ``lengths`` keys each scattered over shuffled pages; the last ``queries[i]``
     positions of request i are query tokens.  ``boost`` = (request, key position, factor) scales one
-    key so that its score stands out."""
+    key so that its score stands out.  ``layout`` "rising": every request's pages are neighbours
+    in rising order; "mixed": rising stretches of 1 to 9 pages in shuffled order, every third one
+    falling."""
     g = torch.Generator().manual_seed(seed)
     total_pages = sum(-(-n // page) for n in lengths) + 3
-    order = torch.randperm(total_pages, generator=g).tolist()
+    if layout == "shuffled":
+        order = torch.randperm(total_pages, generator=g).tolist()
+    elif layout == "rising":
+        order = list(range(total_pages))[::-1]                     # pages are popped from the end
+    else:
+        stretches, at = [], 0
+        while at < total_pages:
+            n = int(torch.randint(1, 10, (1,), generator=g))
+            stretch = list(range(at, min(total_pages, at + n)))
+            stretches.append(stretch[::-1] if len(stretches) % 3 == 2 else stretch)
+            at += n
+        order = [page_id for i in torch.randperm(len(stretches), generator=g).tolist() for page_id in stretches[i]][::-1]
     kc = torch.zeros(total_pages, nkv, page, d)
     vc = torch.zeros_like(kc)
     kc.fill_(float("nan")), vc.fill_(float("nan"))              # reading a foreign slot shows
@@ -442,6 +455,32 @@ def test_attention_prefill_tc(shape, window):
     got, big, rest = run_prefill_tc(case, nq=nq, nkv=nkv, d=d, window=window, scale=d ** -0.5)
     assert big[0] and rest[0]                      # both kernels had tiles
     assert sum(big[2]) + sum(rest[2]) == case["q"].shape[0]
+    close(got, want, dtype, bf16=1.2e-2)
+
+
+@pytest.mark.parametrize("layout", ["rising", "mixed"])
+@pytest.mark.parametrize("shape", [(4, 2, 8), (4, 2, 16), (16, 8, 16), (2, 1, 32)])
+def test_attention_prefill_tc_pages_that_lie_together(shape, layout):
+    """Pages of fewer than 32 tokens are copied two or four at a time where the block table names
+    neighbours in rising order: whole requests of such pages, and stretches of 1 to 9 pages, rising
+    and falling, that start anywhere in a block of keys (a foreign page read shows as NaN)."""
+    nq, nkv, page = shape
+    d, dtype = 128, torch.bfloat16
+    for window in (None, 200):
+        case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=[300, 1, 70, 515, 64, 1000],
+                          queries=[130, 1, 70, 3, 64, 777], seed=nq + page, layout=layout)
+        if layout == "rising":
+            first = case["tables"][5, :1000 // page]
+            assert torch.equal(first, first[0] + torch.arange(first.numel(), dtype=torch.int32))
+        want = plain_paged(case, d ** -0.5, window, dtype)
+        got, big, rest = run_prefill_tc(case, nq=nq, nkv=nkv, d=d, window=window, scale=d ** -0.5)
+        assert big[0]
+        close(got, want, dtype, bf16=1.2e-2)
+    # two q heads an item
+    case = paged_case(dtype, nq=16, nkv=8, d=d, page=16, lengths=[3700, 130, 600], queries=[3700, 130, 300],
+                      seed=5, layout=layout)
+    want = plain_paged(case, d ** -0.5, None, dtype)
+    got, big, rest = run_prefill_tc(case, nq=16, nkv=8, d=d, window=None, scale=d ** -0.5)
     close(got, want, dtype, bf16=1.2e-2)
 
 

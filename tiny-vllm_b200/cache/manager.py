@@ -70,7 +70,10 @@ class PagePool:
         return pages
 
     def give(self, pages, owner) -> None:
-        """Return pages; in the order given, so the last one is reused first."""
+        """Return pages; in the order given, so the last one is reused first.  The manager hands
+        a block table back last page first: the next request then gets the same pages in the same
+        (from a fresh pool: rising) order, and the prefill attention copies neighbouring pages
+        several at a time."""
         for page in pages:
             if not 0 <= page < self.num_pages:
                 raise CacheError(f"page {page} does not exist")

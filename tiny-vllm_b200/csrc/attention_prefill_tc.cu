@@ -76,7 +76,8 @@ __device__ __forceinline__ float exp2_fast(float x) {
 template <bool PAIRED>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_v, const int* block_tables, int table_stride,
+                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k_run,
+                            const __grid_constant__ CUtensorMap map_v_run, int run, const int* block_tables, int table_stride,
                             const int* positions, const int* tile_row, const int* tile_first, const int* tile_count,
                             bf16* out, int64_t out_stride, int num_tiles, int num_q, int num_kv, int page_size,
                             int window, float scale_log2) {
@@ -113,6 +114,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         prefetch_tensormap(&map_q);
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_v);
+        if (!PAIRED && run > 1) {
+            prefetch_tensormap(&map_k_run);
+            prefetch_tensormap(&map_v_run);
+        }
     }
     if (warp == 1) tmem_alloc(smem_address(tmem_base_slot), TMEM_COLS);
     tc_fence_before_sync();
@@ -170,6 +175,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             ++ring;
             return true;
         };
+        // The same for one head an item, where the products wait for their tiles: small pages that
+        // lie one after the other in the cache come in one copy of `run` pages (a copy of 2 KB costs
+        // the copy unit nearly what one of 4 KB does: 1.5 us a block of 128 keys with pages of 16
+        // tokens copied singly, 1.15 us in pairs); a run that is broken, or reaches past the
+        // request's pages, comes page by page.  With two heads an item the copies are not what the
+        // products wait for, and this longer code on a warp that shares its issue slots with two
+        // softmax warps cost 6 % there (8,192 tokens: 302 against 281 us).
+        auto load_tile_runs = [&](const CUtensorMap* map, const CUtensorMap* map_run, const Item& it, int page) -> bool {
+            const int slot = ring % RING;
+            const uint32_t phase = (ring / RING) & 1u;
+            if (!lane_wait(B_KV_EMPTY + slot, phase ^ 1u, 1)) return false;
+            if (lane == 0) mbar_arrive_expect(bar(B_KV_FULL + slot), TILE_BYTES);
+            bool together = false;
+            if (run > 1) {
+                const int place = lane & (run - 1);
+                const int leader_page = __shfl_sync(0xffffffffu, page, lane - place);
+                const bool in_place = page >= 0 && leader_page >= 0 && page == leader_page + place;
+                const uint32_t run_lanes = ((1u << run) - 1u) << (lane - place);
+                together = (__ballot_sync(0xffffffffu, in_place) & run_lanes) == run_lanes;
+            }
+            __syncwarp();
+            if (lane < pages_per_block) {
+                const uint32_t dst = kv_at + slot * TILE_BYTES + (uint32_t)(lane * page_size * 128);
+                if (!together) {
+                    tma_load_4d(dst, map, 0, 0, it.kv_head, page, bar(B_KV_FULL + slot));
+                    tma_load_4d(dst + HALF_BYTES, map, 64, 0, it.kv_head, page, bar(B_KV_FULL + slot));
+                } else if ((lane & (run - 1)) == 0) {
+                    tma_load_4d(dst, map_run, 0, 0, it.kv_head, page, bar(B_KV_FULL + slot));
+                    tma_load_4d(dst + HALF_BYTES, map_run, 64, 0, it.kv_head, page, bar(B_KV_FULL + slot));
+                }
+            }
+            ++ring;
+            return true;
+        };
         pdl_wait();                             // q, keys and values come from the kernel before this one
         if constexpr (PAIRED) {
             // the tiles of an item in the order K0, V0, K1, V1, ...
@@ -207,11 +246,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tma_load_2d(q_at, &map_q, it.head * HD, it.first, bar(B_Q_FULL));
                     tma_load_2d(q_at + HALF_BYTES, &map_q, it.head * HD + 64, it.first, bar(B_Q_FULL));
                 }
-                alive = load_tile(&map_k, it, page_v);
+                alive = load_tile_runs(&map_k, &map_k_run, it, page_v);
                 for (int j = 0; j < it.blocks && alive; ++j) {
                     const int page_after = j + 2 < it.blocks ? page_of(it, it.block0 + j + 2) : -1;
-                    if (j + 1 < it.blocks) alive = load_tile(&map_k, it, page_k);
-                    if (alive) alive = load_tile(&map_v, it, page_v);
+                    if (j + 1 < it.blocks) alive = load_tile_runs(&map_k, &map_k_run, it, page_k);
+                    if (alive) alive = load_tile_runs(&map_v, &map_v_run, it, page_v);
                     page_v = page_k;
                     page_k = page_after;
                 }
@@ -597,23 +636,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 struct MapKey {
     const void* p;
     long long pages;
-    int kv_heads, page_size;
+    int kv_heads, page_size, run;
     bool operator==(const MapKey& o) const {
-        return p == o.p && pages == o.pages && kv_heads == o.kv_heads && page_size == o.page_size;
+        return p == o.p && pages == o.pages && kv_heads == o.kv_heads && page_size == o.page_size && run == o.run;
     }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.p) ^ (size_t)(k.pages * 131 + k.kv_heads * 17 + k.page_size);
+        return std::hash<const void*>()(k.p) ^ (size_t)(k.pages * 131 + k.kv_heads * 17 + k.page_size + k.run * 7919);
     }
 };
 
-// Map of a cache [pages, kv_heads, page_size, 128]: boxes of one page of one kv head, 64 values wide.
-bool cache_map(CUtensorMap* map, const void* cache, long long pages, int kv_heads, int page_size) {
+// Map of a cache [pages, kv_heads, page_size, 128]: boxes of `run` pages of one kv head, 64 values wide.
+bool cache_map(CUtensorMap* map, const void* cache, long long pages, int kv_heads, int page_size, int run) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> known;
     static std::mutex guard;
     std::lock_guard<std::mutex> lock(guard);
-    const MapKey key{cache, pages, kv_heads, page_size};
+    const MapKey key{cache, pages, kv_heads, page_size, run};
     auto found = known.find(key);
     if (found != known.end()) {
         *map = found->second;
@@ -622,7 +661,7 @@ bool cache_map(CUtensorMap* map, const void* cache, long long pages, int kv_head
     const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)page_size, (cuuint64_t)kv_heads, (cuuint64_t)pages};
     const cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)page_size * HD * 2,
                                    (cuuint64_t)kv_heads * page_size * HD * 2};
-    const cuuint32_t box[4] = {64, (cuuint32_t)page_size, 1, 1};
+    const cuuint32_t box[4] = {64, (cuuint32_t)page_size, 1, (cuuint32_t)run};
     if (!tvb_make_map(map, cache, 4, dims, strides, box)) return false;
     if (known.size() > 4096) known.clear();
     known.emplace(key, *map);
@@ -672,8 +711,14 @@ extern "C" int tvb_attention_prefill_tc(const void* q, long long q_token_stride,
         const cuuint32_t box[2] = {64, QT};
         if (!tvb_make_map(&map_q, q, 2, dims, strides, box)) return (int)cudaErrorNotSupported;
     }
-    if (!cache_map(&map_k, key_cache, pages, num_kv, page_size) ||
-        !cache_map(&map_v, value_cache, pages, num_kv, page_size))
+    // pages of fewer than 32 tokens come two or four to a copy where they lie together (one head an item)
+    int run = 32 / page_size < 1 ? 1 : 32 / page_size;
+    while (run > 1 && run > pages) run /= 2;
+    CUtensorMap map_k_run, map_v_run;
+    if (!cache_map(&map_k, key_cache, pages, num_kv, page_size, 1) ||
+        !cache_map(&map_v, value_cache, pages, num_kv, page_size, 1) ||
+        !cache_map(&map_k_run, key_cache, pages, num_kv, page_size, run) ||
+        !cache_map(&map_v_run, value_cache, pages, num_kv, page_size, run))
         return (int)cudaErrorNotSupported;
     // Two q heads of a kv head per item where the heads pair up: every K and V tile then serves both
     // (one head an item is bound by the copies of K and V: 64 KB a block for 8.4 MFLOP).  With few
@@ -692,7 +737,7 @@ extern "C" int tvb_attention_prefill_tc(const void* q, long long q_token_stride,
     const long long items = (long long)num_tiles * (paired ? num_q / 2 : num_q);
     const int ctas = (int)(items < sms ? items : sms);
     TvbLaunch launch(dim3(ctas), dim3(THREADS), SHARED_BYTES, (cudaStream_t)stream, pdl);
-    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, map_q, map_k, map_v, block_tables, table_stride,
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, map_q, map_k, map_v, map_k_run, map_v_run, run, block_tables, table_stride,
                                        positions, tile_row, tile_first, tile_count, (bf16*)out,
                                        (int64_t)num_q * HD, num_tiles, num_q, num_kv, page_size, window,
                                        scale * 1.4426950408889634f);
