@@ -28,14 +28,26 @@ rms_norm_bf16_kernel(const bf16* x, const bf16* residual, const W* __restrict__ 
     const bf16* rr = residual ? residual + (int64_t)in_row * width : nullptr;
     float values[NORM_WORDS][8];
     float squares = 0.0f;
+    // all loads of the row first (they are ordered with the stores below, so a load after a store
+    // would wait for a second trip to memory)
+    uint4 x_words[NORM_WORDS], r_words[NORM_WORDS];
+#pragma unroll
+    for (int i = 0; i < NORM_WORDS; ++i) {
+        const int at = (lane + i * TPR) * 8;
+        x_words[i] = r_words[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (live && at < width) {
+            x_words[i] = ld_global_16(xr + at);
+            if (rr) r_words[i] = ld_global_16(rr + at);
+        }
+    }
 #pragma unroll
     for (int i = 0; i < NORM_WORDS; ++i) {
         const int at = (lane + i * TPR) * 8;
         if (live && at < width) {
-            unpack_bf16x8(ld_global_16(xr + at), values[i]);
+            unpack_bf16x8(x_words[i], values[i]);
             if (rr) {
                 float other[8];
-                unpack_bf16x8(ld_global_16(rr + at), other);
+                unpack_bf16x8(r_words[i], other);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) values[i][e] = round_to<bf16>(__fadd_rn(values[i][e], other[e]));
             }
