@@ -390,11 +390,15 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
         if (new_here && has_q) load_head<HEAD_DIM>(k_head, token + (int64_t)(num_q + kv_head) * HEAD_DIM, lane);
         if (new_here && warp == DEC_WARPS - 1) {
             const unsigned short* v = token + (int64_t)(num_q + num_kv + kv_head) * HEAD_DIM;
+            // the loads first: they are ordered with the stores, and one after a store would be
+            // another trip to memory
+            unsigned short bits[HEAD_DIM / 32];
+#pragma unroll
+            for (int i = 0; i < HEAD_DIM / 32; ++i) bits[i] = ld_global_u16(v + lane + 32 * i);
 #pragma unroll
             for (int i = 0; i < HEAD_DIM / 32; ++i) {
-                const unsigned short bits = ld_global_u16(v + lane + 32 * i);
-                v_new_s[lane + 32 * i] = bf16_bits_to_float(bits);
-                if (cache_at >= 0) reinterpret_cast<unsigned short*>(value_cache + cache_at)[lane + 32 * i] = bits;
+                v_new_s[lane + 32 * i] = bf16_bits_to_float(bits[i]);
+                if (cache_at >= 0) reinterpret_cast<unsigned short*>(value_cache + cache_at)[lane + 32 * i] = bits[i];
             }
         }
         if (new_here && has_q) {
