@@ -44,14 +44,17 @@ def decode_splits(max_model_len: int, rows: int = 1) -> int:
     The size of a piece follows from the request's own position inside the kernel.  Few requests
     need many pieces to fill the GPU; with many requests the pieces' fixed cost (set-up, merge)
     outweighs that, so their number falls with the rows of the step: about 32 pieces a kv head
-    over all rows; beyond 48 rows two pieces, with which the grid runs as CTAs of three warps in
-    two waves (measured at 16 q / 8 kv heads, head size 128, context 2,100, us a layer: 8 rows
-    4 pieces 18.7, 6 pieces 20.0; 16 rows 2 pieces 30.9, 4 pieces 31.9; 32 rows 1 piece 53.1,
-    2 pieces 56.0; 64 rows 2 pieces 95.9, 1 piece 104.4, 3 pieces 102.5).
+    over all rows (32 / rows, rounded); beyond 48 rows two pieces, with which the grid runs as CTAs
+    of three warps in two waves (measured at 16 q / 8 kv heads, head size 128, context 2,100, us a
+    layer: 8 rows 4 pieces 18.7, 6 pieces 20.0; 12 rows 2 pieces 27.0, 3 pieces 25.7; 16 rows
+    2 pieces 30.9, 4 pieces 31.9; 20 rows 1 piece 44.1, 2 pieces 40.3, 4 pieces 48.8; 24 rows
+    1 piece 44.4, 2 pieces 43.3, 3 pieces 53.8; 32 rows 1 piece 53.1, 2 pieces 56.0; 48 rows
+    1 piece 78.7, 2 pieces 88.7; 64 rows 2 pieces 95.9, 1 piece 104.4, 3 pieces 102.5).
     A request's result differs between piece counts by rounding only (the order in which partial
     sums are merged)."""
     by_length = max(1, min(DECODE_MAX_SPLITS, -(-max_model_len // DECODE_SPLIT_GRAIN)))
-    by_rows = 2 if rows > 48 else max(1, min(DECODE_MAX_SPLITS, 32 // max(rows, 1)))
+    rows = max(rows, 1)
+    by_rows = 2 if rows > 48 else max(1, min(DECODE_MAX_SPLITS, (64 + rows) // (2 * rows)))
     return max(1, min(by_length, by_rows))
 
 
