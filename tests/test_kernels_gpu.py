@@ -593,6 +593,37 @@ def test_attention_decode_fused(shape, window):
     close(again, torch.stack(rows), dtype, bf16=1.2e-2)
 
 
+def test_attention_decode_pieces_fitted_to_few_rows():
+    """With two or three rows the number of pieces is the largest with which the kernel's form for
+    small grids has all its clusters on the GPU at once; one row and four or more keep theirs."""
+    import types
+
+    from tinyvllm_b200.ops.attention import decode_splits, fitted_splits
+    mixer = types.SimpleNamespace(num_heads=16, num_kv_heads=8, head_dim=128, q_norm_weight=torch.ones(128))
+    asked = decode_splits(4096, 2)
+    assert asked == 8
+    for rows in (1, 2, 3, 4, 8):
+        pieces = fitted_splits(decode_splits(4096, rows), rows, mixer, 16, 4096)
+        fits = k().attention_decode_fits_wide(rows, num_q=16, num_kv=8, head_dim=128, page_size=16, splits=pieces,
+                                              max_context=4096, weight_dtype=torch.float32)
+        if rows == 1:
+            assert pieces == 8 and fits
+        elif rows <= 3:
+            assert 4 <= pieces <= 8
+            assert fits or pieces == 8                # nothing fitted: the asked number stays
+            if pieces < 8:                            # and one piece more would not have fitted
+                assert not k().attention_decode_fits_wide(rows, num_q=16, num_kv=8, head_dim=128, page_size=16,
+                                                          splits=pieces + 1, max_context=4096,
+                                                          weight_dtype=torch.float32)
+        else:
+            assert pieces == decode_splits(4096, rows)
+    # a grid larger than the GPU never fits; a shape the kernel does not take neither
+    assert not k().attention_decode_fits_wide(64, num_q=16, num_kv=8, head_dim=128, page_size=16, splits=8,
+                                              max_context=4096)
+    assert not k().attention_decode_fits_wide(1, num_q=16, num_kv=8, head_dim=80, page_size=16, splits=8,
+                                              max_context=4096)
+
+
 def test_attention_decode_padding_and_unsupported():
     from tinyvllm_b200.ops.kernels import KernelError
     assert k().attention_decode_supports(128, 16, 8, 8)

@@ -766,7 +766,7 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                          void* value_cache, const int* block_tables, int table_stride, int page_size,
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
                          int splits, int write_cache, int max_context, int pdl, cudaStream_t stream, int heads_here,
-                         int sm_count) {
+                         int sm_count, int* clusters_that_fit = nullptr) {
     auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, RESIDENT, TILE, DEC_STAGES, W>;
     const int warp_slots = decode_warp_slot_capacity<DEC_WARPS, TILE>(max_context, splits, page_size);
     const DecodeLayout layout = decode_layout(HEAD_DIM, HPB, DEC_WARPS, splits, warp_slots, TILE, DEC_STAGES);
@@ -779,6 +779,20 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
     }
     TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / heads_here), requests), dim3(DEC_WARPS * 32),
                      (size_t)layout.total, stream, pdl, splits);
+    if (clusters_that_fit) {
+        // Not a launch: how many clusters of this shape the GPU holds at once (the CTAs of a cluster
+        // need SMs of one GPC; remembered per cluster size and shared memory).
+        static int known[DEC_MAX_SPLITS + 1][2] = {};          // [splits] = {shared bytes, clusters}
+        if (known[splits][0] != layout.total || known[splits][1] <= 0) {
+            int clusters = 0;
+            cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &launch.config);
+            if (e != cudaSuccess) { cudaGetLastError(); clusters = 0; }
+            known[splits][0] = layout.total;
+            known[splits][1] = clusters;
+        }
+        *clusters_that_fit = known[splits][1];
+        return 0;
+    }
     cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, (const bf16*)qkv, (const W*)q_weight, (const W*)k_weight, eps,
                                        cos_table, sin_table, table_positions, positions, token_row, slots,
                                        (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
@@ -811,14 +825,17 @@ extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv
 // write_cache: 0 the new key and value are used but not stored, 1 they are stored in slot slots[i],
 // 2 they are in the cache already, as the other keys are, and q comes normalised and rotated (the
 // decoded tokens of a step that also holds prompt portions, after the pass that prepares all its tokens).
-extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
-                                    const float* cos_table, const float* sin_table, int table_positions,
-                                    const int* positions, const int* token_row, const int* slots,
-                                    void* key_cache, void* value_cache, const int* block_tables,
-                                    int table_stride, int page_size, void* out, int requests, int num_q,
-                                    int num_kv, int head_dim, int window, float scale, int splits,
-                                    int write_cache, int max_context, int weight_dtype, int pdl,
-                                    void* stream) {
+// fits_wide != null: nothing is launched; *fits_wide says whether this call would run as CTAs of
+// eight warps with all its clusters on the GPU at once.
+static int decode_dispatch(const void* qkv, const void* q_weight, const void* k_weight, float eps,
+                           const float* cos_table, const float* sin_table, int table_positions,
+                           const int* positions, const int* token_row, const int* slots,
+                           void* key_cache, void* value_cache, const int* block_tables,
+                           int table_stride, int page_size, void* out, int requests, int num_q,
+                           int num_kv, int head_dim, int window, float scale, int splits,
+                           int write_cache, int max_context, int weight_dtype, int pdl,
+                           void* stream, int* fits_wide) {
+    if (fits_wide) *fits_wide = 0;
     if (requests <= 0) return 0;
     if (!tvb_attention_decode_supports(head_dim, num_q, num_kv, splits) || page_size <= 0 ||
         requests > 65535 || max_context <= 0)
@@ -841,7 +858,11 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
             cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
             sm_count = 0;
     }
-    const bool wide = head_dim <= 128 && (long long)requests * num_kv * (group / heads_here) * splits <= sm_count;
+    // (eight warps a CTA only if every cluster is on the GPU at once: clusters of 8 CTAs of that
+    // size fit 14 to 16 times, not 148 / 8 times, and a second round of them doubles the time)
+    const long long clusters = (long long)requests * num_kv * (group / heads_here);
+    const bool wide = head_dim <= 128 && clusters * splits <= sm_count;
+    int wide_room = 0;
     const bool roomy = (long long)requests * num_kv * (group / heads_here) * splits <= 3ll * sm_count;
 #define DECODE_ARGS qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, \
                     token_row, slots, key_cache, value_cache, block_tables, table_stride, page_size, out, \
@@ -850,11 +871,15 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
 #define DECODE_BY_WARPS(D, H, WT)                                       \
     do {                                                                \
         if (D == 128) {                                                       \
-            if (wide) return launch_decode<128, H, 8, 1, 16, 2, WT>(DECODE_ARGS);  \
+            const bool all_at_once = wide && launch_decode<128, H, 8, 1, 16, 2, WT>(DECODE_ARGS, &wide_room) == 0 && clusters <= wide_room; \
+            if (fits_wide) { *fits_wide = all_at_once ? 1 : 0; return 0; }        \
+            if (all_at_once) return launch_decode<128, H, 8, 1, 16, 2, WT>(DECODE_ARGS); \
             if (roomy) return launch_decode<128, H, 4, 3, 16, 2, WT>(DECODE_ARGS); \
             return launch_decode<128, H, 3, 4, 16, 2, WT>(DECODE_ARGS);       \
         }                                                                     \
-        if (wide) return launch_decode<D, H, 8, 1, 8, 2, WT>(DECODE_ARGS);    \
+        const bool all_at_once = wide && launch_decode<D, H, 8, 1, 8, 2, WT>(DECODE_ARGS, &wide_room) == 0 && clusters <= wide_room; \
+        if (fits_wide) { *fits_wide = all_at_once ? 1 : 0; return 0; }        \
+        if (all_at_once) return launch_decode<D, H, 8, 1, 8, 2, WT>(DECODE_ARGS); \
         if (roomy) return launch_decode<D, H, 4, (D > 128 ? 1 : 3), 8, 2, WT>(DECODE_ARGS); \
         return launch_decode<D, H, 4, (D > 128 ? 1 : 4), 8, 2, WT>(DECODE_ARGS);            \
     } while (0)
@@ -874,4 +899,30 @@ extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const
     if (weight_dtype == TVB_F32) DECODE_BY_DIM(float);
     if (weight_dtype == TVB_BF16) DECODE_BY_DIM(bf16);
     return TVB_BAD_ARGUMENT;
+}
+
+extern "C" int tvb_attention_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
+                                    const float* cos_table, const float* sin_table, int table_positions,
+                                    const int* positions, const int* token_row, const int* slots,
+                                    void* key_cache, void* value_cache, const int* block_tables,
+                                    int table_stride, int page_size, void* out, int requests, int num_q,
+                                    int num_kv, int head_dim, int window, float scale, int splits,
+                                    int write_cache, int max_context, int weight_dtype, int pdl,
+                                    void* stream) {
+    return decode_dispatch(qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, token_row,
+                           slots, key_cache, value_cache, block_tables, table_stride, page_size, out, requests, num_q,
+                           num_kv, head_dim, window, scale, splits, write_cache, max_context, weight_dtype, pdl,
+                           stream, nullptr);
+}
+
+// 1 if `requests` rows cut into `splits` pieces run as CTAs of eight warps with every cluster on the
+// GPU at once (the form that keeps most bytes in flight per SM when the grid is small); 0 if not,
+// or if the shape is not taken.  Launches nothing.
+extern "C" int tvb_attention_decode_fits_wide(int requests, int num_q, int num_kv, int head_dim, int page_size,
+                                              int splits, int max_context, int weight_dtype) {
+    int fits = 0;
+    const int code = decode_dispatch(nullptr, nullptr, nullptr, 0.0f, nullptr, nullptr, 0, nullptr, nullptr, nullptr,
+                                     nullptr, nullptr, nullptr, 0, page_size, nullptr, requests, num_q, num_kv,
+                                     head_dim, 0, 1.0f, splits, 1, max_context, weight_dtype, 0, nullptr, &fits);
+    return code == 0 ? fits : 0;
 }

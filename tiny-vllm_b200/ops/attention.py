@@ -58,6 +58,30 @@ def decode_splits(max_model_len: int, rows: int = 1) -> int:
     return max(1, min(by_length, by_rows))
 
 
+FEW_ROWS = 3                 # rows up to which the pieces are fitted to the kernel's form for small grids
+FEWEST_FITTED_SPLITS = 4
+
+
+def fitted_splits(splits: int, rows: int, mixer, page_size: int, max_context: int) -> int:
+    """With two or three rows the fused decode kernel's form for small grids (CTAs of eight warps,
+    which keep twice the bytes in flight) still has room, but only if every cluster is on the GPU
+    at once, and clusters of 8 CTAs fit 14 to 16 times: the largest number of pieces with which
+    they all fit, if that leaves 4 or more (measured at 16 q / 8 kv heads, head size 128, us a
+    layer at contexts of 2,100 / 8,190: 2 rows 8 pieces, which do not fit, 12.9 / 29.6, 6 pieces
+    10.8 / 20.9; 3 rows 8 pieces 13.4 / 31.0, 5 pieces 11.3 / 23.7; from 4 rows on the smaller CTAs
+    with more pieces are as fast)."""
+    if rows > FEW_ROWS or splits <= FEWEST_FITTED_SPLITS:
+        return splits
+    weight = mixer.q_norm_weight
+    for candidate in range(splits, FEWEST_FITTED_SPLITS - 1, -1):
+        if kernels.attention_decode_fits_wide(
+                rows, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.head_dim,
+                page_size=page_size, splits=candidate, max_context=max_context,
+                weight_dtype=None if weight is None else weight.dtype):
+            return candidate
+    return splits
+
+
 # tiles with fewer tokens than this go to the 64-row kernel: a 128-row tensor-memory tile is mostly
 # empty for them
 TC_MIN_TILE_TOKENS = 32
@@ -135,7 +159,8 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
             qkv, **heads, positions=ctx.positions, token_row=ctx.token_row, slots=ctx.slots[group],
             q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0,
             cos=cos, sin=sin, key_cache=keys, value_cache=values, block_tables=ctx.block_tables[group],
-            window=mixer.window, scale=mixer.scale, splits=ctx.decode_splits,
+            window=mixer.window, scale=mixer.scale,
+            splits=fitted_splits(ctx.decode_splits, qkv.shape[0], mixer, keys.shape[2], ctx.max_context),
             max_context=ctx.max_context)
     kernels.qk_norm_rope_store(
         qkv, **heads, positions=ctx.positions, q_weight=mixer.q_norm_weight,
@@ -158,7 +183,7 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
             # in the cache already, so the fused decode kernel runs without its norm, rotation and
             # cache write: context split over a cluster, keys streamed once per group of q heads.
             part = slice(first, first + count)
-            splits = decode_splits(ctx.max_context, count)
+            splits = fitted_splits(decode_splits(ctx.max_context, count), count, mixer, keys.shape[2], ctx.max_context)
             if kernels.attention_decode_supports(mixer.head_dim, mixer.num_heads, mixer.num_kv_heads, splits):
                 kernels.attention_decode(
                     qkv[part], **heads, positions=ctx.positions[part], token_row=ctx.token_row[part],

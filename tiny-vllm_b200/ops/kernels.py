@@ -411,6 +411,24 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     return out
 
 
+_fits_wide: dict[tuple, bool] = {}
+
+
+def attention_decode_fits_wide(rows: int, *, num_q: int, num_kv: int, head_dim: int, page_size: int,
+                               splits: int, max_context: int, weight_dtype: torch.dtype | None = None) -> bool:
+    """Whether ``rows`` rows cut into ``splits`` pieces run in the fused decode kernel's form for
+    small grids (CTAs of eight warps, one an SM) with all their clusters on the GPU at once.  Asks
+    the runtime how many clusters of that shape fit; launches nothing.  Remembered per shape."""
+    tag = BF16 if weight_dtype is None else dtype_tag(weight_dtype)
+    key = (rows, num_q, num_kv, head_dim, page_size, splits, max_context, tag)
+    known = _fits_wide.get(key)
+    if known is None:
+        fn = _fn("attention_decode", "tvb_attention_decode_fits_wide",
+                 [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int])
+        known = _fits_wide[key] = bool(fn(rows, num_q, num_kv, head_dim, page_size, splits, max_context, tag))
+    return known
+
+
 def attention_prefill_supports(head_dim: int, num_q: int, num_kv: int) -> bool:
     fn = _fn("attention_prefill", "tvb_attention_prefill_supports", [c_int, c_int, c_int])
     return bool(fn(head_dim, num_q, num_kv))
