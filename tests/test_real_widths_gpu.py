@@ -146,13 +146,18 @@ def test_every_way_of_cutting_at_real_widths(name, dtype, mode, wide_runners, wi
 
 
 @pytest.mark.parametrize("name", ["w06", "w32"])
-def test_decode_graphs_with_padding_rows_against_the_oracle(name, wide_runners, wide_folders):
+def test_decode_graphs_with_padding_rows_against_the_oracle(name, wide_runners, wide_folders, monkeypatch):
     """Three requests decode in a graph captured for four rows (one row is padding), in bfloat16: the
     logits the graph leaves are the oracle's and, to rounding in the head, those of the same steps
-    run eagerly."""
+    run eagerly.  (The eager steps cut every context into as many pieces as the graph of four rows
+    does: the number fitted to three rows would merge partial sums in another order, which is a
+    difference of rounding in the attention, not of the padding row that this test is about.)"""
     from tinyvllm_b200.engine.graphs import DecodeGraphs
     from tinyvllm_b200.engine.step import StepEntry
+    from tinyvllm_b200.ops import attention as attention_ops
     from tinyvllm_b200.sampling.params import SamplingParams
+
+    monkeypatch.setattr(attention_ops, "FEW_ROWS", 0)
 
     dtype = torch.bfloat16
     requests = {rid: tokens for rid, tokens in list(requests_of(name).items())[1:4]}      # 150, 70, 300 tokens
