@@ -16,7 +16,8 @@ weights, bfloat16.
 * ``roofline``: bytes a decode step must read (every weight once + the cache of the live
   requests) / time / measured HBM bandwidth.
 * ``points``: decode at batch 1 and 64; decode at batch 8 from a context of 16,384 tokens (with its
-  fraction of the HBM roofline) and a prefill of 8,192 tokens (with its fraction of the tensor peak).
+  fraction of the HBM roofline), a prefill of 8,192 tokens (with its fraction of the tensor peak) and
+  decode of one request alone at a context of 32,768.
 
 Every step reads more than the 126 MB of L2 (the weights alone are 1.19 GB), so the inputs are
 larger than L2 and no flush is needed between timed steps.
@@ -307,6 +308,7 @@ def decode_bytes(engine, batch: int, mean_context: float) -> float:
 
 LONG_CONTEXT = 16384           # context of the long-context decode point
 LONG_PREFILL = 8192            # tokens of the long prefill point
+LONE_CONTEXT = 32768           # context of the point with one request alone
 
 
 def prefill_flops(layers: int, tokens: int) -> float:
@@ -506,6 +508,21 @@ def headline(args, warmup: int) -> int:
                     prefill_flops(args.layers, LONG_PREFILL) / (long_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)
                 long_engine.close()
                 del long_engine
+                gc.collect()
+                torch.cuda.empty_cache()
+            # one request alone with a context of 32,768 (the decode attention cuts it over several
+            # clusters a kv head, so that more than 64 of the SMs read its keys)
+            with tempfile.TemporaryDirectory() as other:
+                lone_steps = min(args.steps, 32)
+                lone_engine = make_engine(other, args.layers, 1, new_tokens=new_tokens_of(lone_steps, warmup),
+                                          prompt_tokens=LONE_CONTEXT)
+                result = run_decode(lone_engine, 1, lone_steps, warmup, None, prompt_tokens=LONE_CONTEXT)
+                lone_bytes = decode_bytes(lone_engine, 1, result["mean_context"])
+                points["decode_b1_ctx32k"] = round(result["tokens_per_s"], 1)
+                points["decode_b1_ctx32k_hbm_frac"] = round(
+                    lone_bytes / (result["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4)
+                lone_engine.close()
+                del lone_engine
                 gc.collect()
                 torch.cuda.empty_cache()
     sampler.stop()

@@ -155,6 +155,62 @@ def test_trace_run_program(dtype_name, model_folders, tmp_path):
     rh.compare(got, rh.oracle(model_folders[name], requests, dtype), dtype, what="trace_run")
 
 
+def test_a_lone_long_request_is_cut_over_several_clusters(model_folders, monkeypatch):
+    """From a length on (brought down to 96 tokens here) a request that decodes alone has its keys
+    cut over several clusters per kv head: eagerly, and in the decode graph of one row that long
+    requests have for themselves; shorter ones keep the other graph."""
+    from tinyvllm_b200.engine.graphs import DecodeGraphs
+    from tinyvllm_b200.engine.step import StepEntry
+    from tinyvllm_b200.ops import attention as attention_ops
+    from tinyvllm_b200.ops import kernels
+    from tinyvllm_b200.sampling.params import SamplingParams
+
+    monkeypatch.setattr(attention_ops, "FAR_FROM_KEYS", 96)
+    name, dtype = "e", torch.bfloat16
+    vocab = TINY_CONFIGS[name].vocab_size
+    requests = {"long": random_tokens(vocab, 400, 77), "short": random_tokens(vocab, 60, 78)}
+    tail = 24
+    seen = []
+    real = kernels.attention_decode
+
+    def watched(*args, far_groups=1, **kwargs):
+        seen.append(far_groups)
+        return real(*args, far_groups=far_groups, **kwargs)
+
+    monkeypatch.setattr(kernels, "attention_decode", watched)
+    for use_graphs in (False, True):
+        runner = make_runner(model_folders[name], dtype, PAGE_SIZES[name], 40 if use_graphs else 41)
+        graphs = None
+        if use_graphs:
+            graphs = DecodeGraphs(runner, [1, 2], max_model_len=runner.max_model_len)
+            assert graphs.far_bucket is not None
+            graphs.capture()
+        got = {}
+        with torch.inference_mode():
+            for rid, tokens in requests.items():
+                runner.open(rid)
+                runner.run([StepEntry(rid, tuple(tokens[:-tail]), ())])
+                seen.clear()
+                for step in range(tail):
+                    entries = [StepEntry(rid, (tokens[len(tokens) - tail + step],), (0,))]
+                    if graphs is None:
+                        logits = runner.run(entries)
+                    else:
+                        plan = runner.plan(entries)
+                        prepared = graphs.prepare(plan, entries, [SamplingParams()], [0])
+                        assert (prepared[0] is graphs.far_bucket) == (rid == "long")
+                        _, logits = graphs.launch(prepared, plan)
+                        runner.manager.commit(plan)
+                    got[(rid, len(tokens) - tail + step)] = logits[0].float().cpu().clone()
+                if graphs is None:                 # eager steps: every layer's launch says how it was cut
+                    assert seen and all(groups > 1 for groups in seen) == (rid == "long")
+                    assert all(groups == 1 for groups in seen) == (rid == "short")
+                runner.close(rid)
+        positions = {rid: {p for (r, p) in got if r == rid} for rid in requests}
+        expected = rh.oracle(model_folders[name], requests, dtype, positions=positions)
+        rh.compare(got, expected, dtype, what=f"lone long request, graphs {use_graphs}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 def test_steps_replayed_as_graphs_give_the_eager_logits(dtype, model_folders):
     """A step whose signature keeps coming back is captured at its third occurrence and replayed

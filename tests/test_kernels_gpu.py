@@ -593,6 +593,61 @@ def test_attention_decode_fused(shape, window):
     close(again, torch.stack(rows), dtype, bf16=1.2e-2)
 
 
+@pytest.mark.parametrize("window", [None, 2000])
+@pytest.mark.parametrize("plan", [(4, 4), (6, 2), (2, 3)])
+def test_attention_decode_request_cut_over_several_clusters(plan, window):
+    """A request's keys cut over several clusters per kv head, whose first CTAs leave their pieces
+    in global memory for the cluster that arrives last: requests long and short (pieces that hold
+    no key), from a length on only, and twice in a row (the counters are left at zero)."""
+    pieces, groups = plan
+    nq, nkv, d, page, dtype = 4, 2, 128, 16, torch.bfloat16
+    lengths = [3000, 37, 700]
+    case = paged_case(dtype, nq=nq, nkv=nkv, d=d, page=page, lengths=lengths, queries=[1] * len(lengths), seed=pieces)
+    requests = len(lengths)
+    assert k().attention_decode_fits_wide(requests * groups, num_q=nq, num_kv=nkv, head_dim=d, page_size=page,
+                                          splits=pieces, max_context=3100, weight_dtype=torch.float32)
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(requests, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    qw, kw = (1 + 0.1 * torch.randn(d, generator=g)), (1 + 0.1 * torch.randn(d, generator=g))
+    cos, sin = plain.rope_tables(d, 3100, 10_000.0)
+    positions = case["positions"]
+    slots = torch.tensor([int(case["tables"][r, int(p) // page]) * page + int(p) % page
+                          for r, p in enumerate(positions)], dtype=torch.int32)
+    q = qkv[:, :nq * d].float().view(requests, nq, d)
+    kn = qkv[:, nq * d:(nq + nkv) * d].float().view(requests, nkv, d)
+    vn = qkv[:, (nq + nkv) * d:].float().view(requests, nkv, d)
+    pos = positions.long()
+    want_q, want_k = plain.qk_norm_rope(q, kn, qw, kw, cos[pos], sin[pos], 1e-6, dtype)
+    rows = []
+    for r, p in enumerate(pos.tolist()):
+        keys = torch.cat([case["keys"][r][:p], want_k[r:r + 1]])
+        values = torch.cat([case["values"][r][:p], vn[r:r + 1]])
+        rows.append(plain.causal_attention(want_q[r:r + 1], keys, values, d ** -0.5, window, dtype,
+                                           q_positions=torch.tensor([p]))[0])
+    want = torch.stack(rows)
+    for far_from in (1, 600, 5000):                 # all requests; the two longer ones; none
+        for _ in range(2):
+            kc, vc = case["kc"].to(DEV).clone(), case["vc"].to(DEV).clone()
+            got = k().attention_decode(
+                qkv.to(DEV), num_q=nq, num_kv=nkv, head_dim=d, positions=positions.to(DEV),
+                token_row=case["token_row"].to(DEV), slots=slots.to(DEV), q_weight=qw.to(DEV), k_weight=kw.to(DEV),
+                eps=1e-6, cos=cos.to(DEV), sin=sin.to(DEV), key_cache=kc, value_cache=vc,
+                block_tables=case["tables"].to(DEV), window=window, scale=d ** -0.5, splits=pieces,
+                max_context=3100, far_groups=groups, far_from=far_from).view(requests, nq, d)
+            close(got, want, dtype, bf16=1.2e-2)
+            flat_k = by_slot(kc)[slots.long().to(DEV)]
+            close(flat_k, want_k, dtype, bf16=1.6e-2)                  # the new key is stored once, by its piece
+            assert torch.equal(by_slot(vc)[slots.long().to(DEV)].cpu(), vn.to(dtype))
+    from tinyvllm_b200.ops.kernels import KernelError
+    with pytest.raises(KernelError):               # more clusters than the GPU holds at once
+        k().attention_decode(
+            qkv.to(DEV), num_q=nq, num_kv=nkv, head_dim=d, positions=positions.to(DEV),
+            token_row=case["token_row"].to(DEV), slots=slots.to(DEV), q_weight=qw.to(DEV), k_weight=kw.to(DEV),
+            eps=1e-6, cos=cos.to(DEV), sin=sin.to(DEV), key_cache=case["kc"].to(DEV), value_cache=case["vc"].to(DEV),
+            block_tables=case["tables"].to(DEV), window=window, scale=d ** -0.5, splits=8, max_context=3100,
+            far_groups=8, far_from=1)
+
+
 def test_attention_decode_pieces_fitted_to_few_rows():
     """With two or three rows the number of pieces is the largest with which the kernel's form for
     small grids has all its clusters on the GPU at once; one row and four or more keep theirs."""

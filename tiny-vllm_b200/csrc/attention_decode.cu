@@ -218,7 +218,22 @@ __device__ __forceinline__ void store_head(const HeadRegs<HEAD_DIM>& x, T* to, i
 // grids of up to three CTAs an SM, none for the eight-warp CTAs of grids smaller than the GPU and
 // for a head of 256, which keeps its output tile in twice the registers.  With 16-key tiles
 // (twice the ring per warp) the larger grids get CTAs of three warps, four to an SM.
-template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, int TILE, int DEC_STAGES, typename W>
+//
+// FAR (one request with a long context, where clusters of the largest size that fits would leave
+// half of the SMs idle): the keys of a request that holds `far.from` or more are cut `far.groups`
+// times more finely and every group of `splits` pieces has a cluster of its own; the first CTA of
+// a cluster leaves its merged piece (maximum, denominator, sums) in global memory and counts itself
+// in; the cluster that finds all others counted merges the groups in their order and stores the
+// result.  Nobody waits: a cluster that is not last is done.  With fewer keys the first group's
+// cluster does everything as without FAR and the others leave at once.
+struct FarArgs {
+    int groups;          // clusters per (request, kv head, block of q heads)
+    int from;            // keys from which a request is cut over all groups
+    float* pieces;       // [requests][gridDim.y / groups][groups][HPB][HEAD_DIM + 2]
+    int* arrived;        // [requests][gridDim.y / groups], zero between launches
+};
+
+template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, int TILE, int DEC_STAGES, typename W, bool FAR = false>
 __global__ void __launch_bounds__(DEC_WARPS * 32, RESIDENT)
 decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_table,
@@ -228,7 +243,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                         bf16* __restrict__ value_cache, const int* __restrict__ block_tables,
                         int table_stride, int page_size, bf16* __restrict__ out, int num_q, int num_kv,
                         int window, float scale, int write_cache, int warp_slot_capacity, int heads_here,
-                        DecodeLayout layout) {
+                        DecodeLayout layout, FarArgs far) {
     // heads_here <= HPB q heads of one kv head are this CTA's (HPB is what the tile and the shared
     // arrays hold; rows past heads_here stay zero): groups of 3, 5, 6 or 7 heads run on the next size up
     constexpr int CPR = HEAD_DIM / 8;          // 16-byte chunks of a key's row
@@ -255,8 +270,10 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     const int splits = gridDim.x;
     const int group = num_q / num_kv;
     const int blocks_per_kv = group / heads_here;
-    const int kv_head = blockIdx.y / blocks_per_kv;
-    const int first_q_head = kv_head * group + (blockIdx.y % blocks_per_kv) * heads_here;
+    const int y_block = FAR ? blockIdx.y / far.groups : blockIdx.y;       // (kv head, block of its q heads)
+    const int far_group = FAR ? blockIdx.y % far.groups : 0;
+    const int kv_head = y_block / blocks_per_kv;
+    const int first_q_head = kv_head * group + (y_block % blocks_per_kv) * heads_here;
     const int request = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = num_q + 2 * num_kv;
@@ -265,10 +282,18 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     bf16* out_row = out + ((int64_t)request * num_q + first_q_head) * HEAD_DIM;
     if (row < 0 || position < 0) {              // padding: the whole cluster leaves together
         pdl_wait();
-        if (split == 0)
+        if (split == 0 && far_group == 0)
             for (int i = threadIdx.x; i < heads_here * HEAD_DIM; i += blockDim.x) out_row[i] = __float2bfloat16_rn(0.0f);
         return;
     }
+    // groups of pieces that this request is cut into: all of them from far.from keys on
+    int far_groups = 1;
+    if constexpr (FAR) {
+        const int keys = window > 0 ? min(position + 1, window) : position + 1;
+        far_groups = keys >= far.from ? far.groups : 1;
+        if (far_group >= far_groups) return;    // the whole cluster
+    }
+    const int pieces = splits * far_groups, piece = far_group * splits + split;
 
     // Every CTA says that it runs; the stores into the first CTA's shared memory at the end wait
     // until all of them have said so.
@@ -298,9 +323,9 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     // request alone; piece `split` is this CTA's.  Keys [first, last] of it are in the cache.
     const int lo = window > 0 ? max(0, position - window + 1) : 0;
     const int range_first = lo - lo % 64;
-    const int split_keys = ((position - range_first + splits) / splits + TILE - 1) / TILE * TILE;
-    const int own_split = (position - range_first) / split_keys;     // holds the new token
-    const int base = range_first + split * split_keys;
+    const int split_keys = ((position - range_first + pieces) / pieces + TILE - 1) / TILE * TILE;
+    const int own_piece = (position - range_first) / split_keys;     // holds the new token
+    const int base = range_first + piece * split_keys;
     const int first = max(lo, base);
     // write_cache 2: the new token's key and value are in the cache already (and q is ready): it is
     // a key like the others, nothing of it is taken from the projection
@@ -376,8 +401,8 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     pdl_wait();                                 // the projection comes from the kernel before this one
     {
         const unsigned short* token = reinterpret_cast<const unsigned short*>(qkv) + (int64_t)request * heads * HEAD_DIM;
-        const bool new_here = split == own_split && !cached_new;
-        const bool stores = write_cache == 1 && (blockIdx.y % blocks_per_kv) == 0;
+        const bool new_here = piece == own_piece && !cached_new;
+        const bool stores = write_cache == 1 && (y_block % blocks_per_kv) == 0;
         int64_t cache_at = -1;
         if (new_here && stores) {
             const int slot = slots[request];
@@ -684,7 +709,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
             l += warp_l_s[w * HPB + h] * f;
             o += warp_o_of(w)[h * HEAD_DIM + dim] * f;
         }
-        if (split == own_split && !cached_new) {   // the new token itself, from shared memory
+        if (piece == own_piece && !cached_new) {   // the new token itself, from shared memory
             const float s = s_new_s[h];
             const float new_max = fmaxf(m, s);
             const float f_old = m == -INFINITY ? 0.0f : __expf(m - new_max);
@@ -706,9 +731,17 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     // ---- the first CTA merges the pieces in rank order
     cluster.sync();
     if (split == 0) {
+        // FAR, a request cut over several clusters: this cluster's merged piece goes to global memory
+        float* far_mine = nullptr;
+        if constexpr (FAR) {
+            if (far_groups > 1)
+                far_mine = far.pieces + (((int64_t)request * (gridDim.y / far.groups) + y_block) * far.groups + far_group) *
+                                            (HPB * (HEAD_DIM + 2));
+        }
         for (int index = threadIdx.x; index < heads_here * HEAD_DIM; index += blockDim.x) {
             const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
             float l = 0.0f, o = 0.0f;
+            float top = -INFINITY;             // FAR: the maximum that l and o are relative to
             if constexpr (HPB >= 2) {
                 // unrolled over the largest cluster, so that the loads and exponentials of all pieces
                 // are in flight together; the sums keep the rank order.  (With one q head a CTA the
@@ -729,6 +762,7 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                     l += pl[r] * f;
                     o += po[r] * f;
                 }
+                if constexpr (FAR) top = m;
             } else {
                 float m = -INFINITY;
                 for (int r = 0; r < splits; ++r) m = fmaxf(m, part_m_s[r * HPB + h]);
@@ -738,8 +772,53 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
                     l += part_l_s[r * HPB + h] * f;
                     o += part_o_s[(r * HPB + h) * HEAD_DIM + dim] * f;
                 }
+                if constexpr (FAR) top = m;
+            }
+            if constexpr (FAR) {
+                if (far_mine) {
+                    float* head = far_mine + h * (HEAD_DIM + 2);
+                    head[dim] = o;
+                    if (dim == 0) { head[HEAD_DIM] = top; head[HEAD_DIM + 1] = l; }
+                    continue;
+                }
             }
             out_row[index] = __float2bfloat16_rn(o / l);
+        }
+        if constexpr (FAR) {
+            if (far_mine) {
+                // Count this cluster in; the one that finds all others counted has their pieces
+                // before it (the fences order each cluster's stores before its count, and the
+                // last one's loads after it) and merges them in the order of the groups.
+                int* last_s = reinterpret_cast<int*>(shared_raw + layout.s_new);      // free by now
+                __threadfence();
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    int* count = far.arrived + (int64_t)request * (gridDim.y / far.groups) + y_block;
+                    const int before = atomicAdd(count, 1);
+                    const int last = before == far_groups - 1;
+                    if (last) *count = 0;                  // for the next launch
+                    *last_s = last;
+                }
+                __syncthreads();
+                if (*last_s == 0) return;
+                __threadfence();
+                const float* all = far_mine - (int64_t)far_group * (HPB * (HEAD_DIM + 2));
+                for (int index = threadIdx.x; index < heads_here * HEAD_DIM; index += blockDim.x) {
+                    const int h = index / HEAD_DIM, dim = index % HEAD_DIM;
+                    float m = -INFINITY;
+                    for (int r = 0; r < far_groups; ++r)
+                        m = fmaxf(m, __ldcg(all + (r * HPB + h) * (HEAD_DIM + 2) + HEAD_DIM));
+                    float l = 0.0f, o = 0.0f;
+                    for (int r = 0; r < far_groups; ++r) {
+                        const float* head = all + (r * HPB + h) * (HEAD_DIM + 2);
+                        const float pm = __ldcg(head + HEAD_DIM);
+                        const float f = pm == -INFINITY ? 0.0f : __expf(pm - m);
+                        l += __ldcg(head + HEAD_DIM + 1) * f;
+                        o += __ldcg(head + dim) * f;
+                    }
+                    out_row[index] = __float2bfloat16_rn(o / l);
+                }
+            }
         }
     }
 }
@@ -759,15 +838,16 @@ static int decode_warp_slot_capacity(int max_context, int splits, int page_size)
     return page_size % TILE == 0 ? tiles : tiles * TILE;
 }
 
-template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, int TILE, int DEC_STAGES, typename W>
+template <int HEAD_DIM, int HPB, int DEC_WARPS, int RESIDENT, int TILE, int DEC_STAGES, typename W, bool FAR = false>
 static int launch_decode(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                          const float* cos_table, const float* sin_table, int table_positions,
                          const int* positions, const int* token_row, const int* slots, void* key_cache,
                          void* value_cache, const int* block_tables, int table_stride, int page_size,
                          void* out, int requests, int num_q, int num_kv, int window, float scale,
                          int splits, int write_cache, int max_context, int pdl, cudaStream_t stream, int heads_here,
-                         int sm_count, int* clusters_that_fit = nullptr) {
-    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, RESIDENT, TILE, DEC_STAGES, W>;
+                         int sm_count, int* clusters_that_fit = nullptr, FarArgs far = FarArgs{1, 0, nullptr, nullptr}) {
+    auto kernel = decode_attention_kernel<HEAD_DIM, HPB, DEC_WARPS, RESIDENT, TILE, DEC_STAGES, W, FAR>;
+    if (FAR != (far.groups > 1) || (FAR && (splits < 2 || !far.pieces || !far.arrived))) return TVB_BAD_ARGUMENT;
     const int warp_slots = decode_warp_slot_capacity<DEC_WARPS, TILE>(max_context, splits, page_size);
     const DecodeLayout layout = decode_layout(HEAD_DIM, HPB, DEC_WARPS, splits, warp_slots, TILE, DEC_STAGES);
     if (layout.total > 200 * 1024) return TVB_BAD_ARGUMENT;
@@ -777,7 +857,7 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
         if (e != cudaSuccess) return (int)e;
         configured = 200 * 1024;
     }
-    TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / heads_here), requests), dim3(DEC_WARPS * 32),
+    TvbLaunch launch(dim3(splits, num_kv * ((num_q / num_kv) / heads_here) * far.groups, requests), dim3(DEC_WARPS * 32),
                      (size_t)layout.total, stream, pdl, splits);
     if (clusters_that_fit) {
         // Not a launch: how many clusters of this shape the GPU holds at once (the CTAs of a cluster
@@ -797,7 +877,7 @@ static int launch_decode(const void* qkv, const void* q_weight, const void* k_we
                                        cos_table, sin_table, table_positions, positions, token_row, slots,
                                        (bf16*)key_cache, (bf16*)value_cache, block_tables, table_stride, page_size,
                                        (bf16*)out, num_q, num_kv, window, scale, write_cache, warp_slots, heads_here,
-                                       layout);
+                                       layout, far);
     return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
@@ -834,8 +914,9 @@ static int decode_dispatch(const void* qkv, const void* q_weight, const void* k_
                            int table_stride, int page_size, void* out, int requests, int num_q,
                            int num_kv, int head_dim, int window, float scale, int splits,
                            int write_cache, int max_context, int weight_dtype, int pdl,
-                           void* stream, int* fits_wide) {
+                           void* stream, int* fits_wide, FarArgs far = FarArgs{1, 0, nullptr, nullptr}) {
     if (fits_wide) *fits_wide = 0;
+    if (far.groups < 1 || (far.groups > 1 && (head_dim != 128 || splits < 2))) return TVB_BAD_ARGUMENT;
     if (requests <= 0) return 0;
     if (!tvb_attention_decode_supports(head_dim, num_q, num_kv, splits) || page_size <= 0 ||
         requests > 65535 || max_context <= 0)
@@ -860,7 +941,7 @@ static int decode_dispatch(const void* qkv, const void* q_weight, const void* k_
     }
     // (eight warps a CTA only if every cluster is on the GPU at once: clusters of 8 CTAs of that
     // size fit 14 to 16 times, not 148 / 8 times, and a second round of them doubles the time)
-    const long long clusters = (long long)requests * num_kv * (group / heads_here);
+    const long long clusters = (long long)requests * num_kv * (group / heads_here) * far.groups;
     const bool wide = head_dim <= 128 && clusters * splits <= sm_count;
     int wide_room = 0;
     const bool roomy = (long long)requests * num_kv * (group / heads_here) * splits <= 3ll * sm_count;
@@ -873,6 +954,11 @@ static int decode_dispatch(const void* qkv, const void* q_weight, const void* k_
         if (D == 128) {                                                       \
             const bool all_at_once = wide && launch_decode<128, H, 8, 1, 16, 2, WT>(DECODE_ARGS, &wide_room) == 0 && clusters <= wide_room; \
             if (fits_wide) { *fits_wide = all_at_once ? 1 : 0; return 0; }        \
+            if (far.groups > 1) {                                                 \
+                /* several clusters a request: only as CTAs of eight warps that are all on the GPU at once */ \
+                if (!all_at_once) return TVB_BAD_ARGUMENT;                        \
+                return launch_decode<128, H, 8, 1, 16, 2, WT, true>(DECODE_ARGS, nullptr, far); \
+            }                                                                     \
             if (all_at_once) return launch_decode<128, H, 8, 1, 16, 2, WT>(DECODE_ARGS); \
             if (roomy) return launch_decode<128, H, 4, 3, 16, 2, WT>(DECODE_ARGS); \
             return launch_decode<128, H, 3, 4, 16, 2, WT>(DECODE_ARGS);       \
@@ -925,4 +1011,33 @@ extern "C" int tvb_attention_decode_fits_wide(int requests, int num_q, int num_k
                                      nullptr, nullptr, nullptr, 0, page_size, nullptr, requests, num_q, num_kv,
                                      head_dim, 0, 1.0f, splits, 1, max_context, weight_dtype, 0, nullptr, &fits);
     return code == 0 ? fits : 0;
+}
+
+// The same with a long request cut over `far_groups` clusters per (kv head, block of q heads), from
+// `far_from` keys on (head size 128; every cluster must be on the GPU at once, which
+// tvb_attention_decode_fits_wide answers for requests * far_groups rows).  far_pieces: float
+// [tvb_attention_decode_far_floats(...)], scratch; far_arrived: int [requests * num_q] or more, zero
+// before the first launch (every launch leaves it zero).
+extern "C" int tvb_attention_decode_far(const void* qkv, const void* q_weight, const void* k_weight, float eps,
+                                        const float* cos_table, const float* sin_table, int table_positions,
+                                        const int* positions, const int* token_row, const int* slots,
+                                        void* key_cache, void* value_cache, const int* block_tables,
+                                        int table_stride, int page_size, void* out, int requests, int num_q,
+                                        int num_kv, int head_dim, int window, float scale, int splits,
+                                        int write_cache, int max_context, int weight_dtype, int pdl,
+                                        int far_groups, int far_from, float* far_pieces, int* far_arrived,
+                                        void* stream) {
+    if (far_groups < 2 || far_from < 1 || !far_pieces || !far_arrived) return TVB_BAD_ARGUMENT;
+    return decode_dispatch(qkv, q_weight, k_weight, eps, cos_table, sin_table, table_positions, positions, token_row,
+                           slots, key_cache, value_cache, block_tables, table_stride, page_size, out, requests, num_q,
+                           num_kv, head_dim, window, scale, splits, write_cache, max_context, weight_dtype, pdl,
+                           stream, nullptr, FarArgs{far_groups, far_from, far_pieces, far_arrived});
+}
+
+// floats of scratch that tvb_attention_decode_far needs
+extern "C" long long tvb_attention_decode_far_floats(int requests, int num_q, int num_kv, int head_dim, int far_groups) {
+    if (num_kv <= 0 || num_q <= 0 || num_q % num_kv || requests <= 0 || far_groups < 1) return 0;
+    const int heads_here = decode_heads_per_cta(num_q / num_kv, head_dim);
+    const int hpb = heads_here <= 1 ? 1 : heads_here <= 2 ? 2 : heads_here <= 4 ? 4 : 8;
+    return (long long)requests * (num_q / heads_here) * far_groups * hpb * (head_dim + 2);
 }

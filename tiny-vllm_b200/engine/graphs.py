@@ -27,9 +27,10 @@ from .step import StepContext
 class _Bucket:
     """Buffers and graph of one batch size."""
 
-    def __init__(self, runner, size: int, blocks: list[int]) -> None:
+    def __init__(self, runner, size: int, blocks: list[int], far: bool = False) -> None:
         groups = len(runner.manager.groups)
         self.size = size
+        self.far = far                    # the graph of a lone request with a long context
         self.blocks = blocks
         sizes = [size, size, size, size, size, size + 1]
         for g in range(groups):
@@ -68,6 +69,12 @@ class DecodeGraphs:
         chunk = kernels.attention_chunk_keys()
         self.split_chunks = -(-max_model_len // chunk) if max_model_len > chunk else 0
         self.buckets = [_Bucket(runner, size, self.blocks) for size in sorted(set(batch_sizes))]
+        # A lone request with a long context has a graph of its own, in which the decode attention
+        # cuts it over several clusters a kv head (``ops.attention.far_plan``); which of the two
+        # graphs of one row a step replays follows from the request's length, which the host knows.
+        self.far_bucket = None
+        if 1 in set(batch_sizes) and max_model_len >= attention_ops.FAR_FROM_KEYS:
+            self.far_bucket = _Bucket(runner, 1, self.blocks, far=True)
         self._pool = None
 
     @property
@@ -88,7 +95,7 @@ class DecodeGraphs:
             cache_sources=self.runner.cache_sources, max_position=self.max_model_len - 1,
             split_chunks=self.split_chunks, workspace_of=self.runner._workspace_of,
             decode_only=True, decode_splits=attention_ops.decode_splits(self.max_model_len, size),
-            max_context=self.max_model_len)
+            decode_far=bucket.far, max_context=self.max_model_len)
 
     def _fill_padding(self, bucket: _Bucket) -> None:
         bucket.host_np[:] = 0
@@ -110,7 +117,7 @@ class DecodeGraphs:
             if need > 0:
                 self.runner.reserve_workspace(need)
         stream = torch.cuda.Stream(device=self.runner.device)
-        for bucket in reversed(self.buckets):
+        for bucket in list(reversed(self.buckets)) + ([self.far_bucket] if self.far_bucket is not None else []):
             self._fill_padding(bucket)
             bucket.device.copy_(bucket.host)
             ctx = self._context(bucket)
@@ -143,7 +150,12 @@ class DecodeGraphs:
         bucket = self.bucket_for(rows)
         return bucket.launches if bucket is not None else 0
 
-    def bucket_for(self, rows: int) -> _Bucket | None:
+    def bucket_for(self, rows: int, longest: int = 0) -> _Bucket | None:
+        """The graph of the smallest size that holds ``rows``; ``longest``: tokens of the longest
+        request of the step (with its new one)."""
+        if (rows == 1 and self.far_bucket is not None and self.far_bucket.graph is not None
+                and longest >= attention_ops.FAR_FROM_KEYS):
+            return self.far_bucket
         for bucket in self.buckets:
             if bucket.size >= rows and bucket.graph is not None:
                 return bucket
@@ -197,7 +209,7 @@ class DecodeGraphs:
         """Lower a step of single tokens into the pinned buffer of the smallest graph that holds it
         (host work only); None if no graph does."""
         rows = len(entries)
-        bucket = self.bucket_for(rows)
+        bucket = self.bucket_for(rows, max((p.start + 1 for p in plan.entries), default=0))
         if bucket is None:
             return None
         self._fill(bucket, plan.entries, rows, [entry.tokens[0] for entry in entries], 0, params, draws)
@@ -231,7 +243,7 @@ class DecodeGraphs:
         GPU does not wait for the host between two steps, nor between the last step the host has
         seen and the next.  None if no graph holds the rows."""
         rows = len(first_tokens)
-        bucket = self.bucket_for(rows)
+        bucket = self.bucket_for(rows, max((p.start + 1 for p in plan.entries), default=0))
         if bucket is None:
             return None
         self.runner.storage.clear_state([p.state_slot for p in plan.entries if p.fresh_state])

@@ -69,6 +69,7 @@ class StepContext:
     workspace_of: object = None          # callable(floats) -> float32 scratch tensor
     decode_only: bool = False            # every entry is a single token
     decode_splits: int = 0               # pieces the fused decode attention cuts a context into
+    decode_far: bool = False             # a lone request with a long context: several clusters a kv head
     max_context: int = 0                 # no request grows beyond this many tokens
     tile_row: torch.Tensor | None = None     # tiles of consecutive query tokens for the tile kernel:
     tile_first: torch.Tensor | None = None   # request row, first flat token and token count of each
@@ -271,7 +272,8 @@ class StepRunner:
         if split_chunks is None:
             split_chunks = attention_ops.choose_split(tokens, max_position)
         # all that decides which kernels a step launches and with which sizes
-        signature = (tuple(sizes), decode_only, split_chunks, single_runs)
+        decode_far = decode_only and rows == 1 and max_position + 1 >= attention_ops.FAR_FROM_KEYS
+        signature = (tuple(sizes), decode_only, split_chunks, single_runs, decode_far)
         device = self._upload(host, None if arena_of is None else arena_of(signature, host.shape[0]))
 
         def dview(i):
@@ -288,6 +290,7 @@ class StepRunner:
             cache_sources=self.cache_sources, max_position=max_position, split_chunks=split_chunks,
             workspace_of=self._workspace_of, decode_only=decode_only,
             decode_splits=attention_ops.decode_splits(self.max_model_len, rows), max_context=self.max_model_len,
+            decode_far=decode_far,
             tile_row=dview(tiles_at) if tiled else None,
             tile_first=dview(tiles_at + 1) if tiled else None,
             tile_count=dview(tiles_at + 2) if tiled else None,

@@ -82,6 +82,30 @@ def fitted_splits(splits: int, rows: int, mixer, page_size: int, max_context: in
     return splits
 
 
+FAR_FROM_KEYS = 12288        # keys from which a lone request is cut over several clusters a kv head
+FAR_PLANS = ((4, 4), (6, 2))  # (pieces a cluster, clusters a kv head), in the order of preference
+
+
+def far_plan(rows: int, mixer, page_size: int, max_context: int):
+    """(pieces a cluster, clusters a kv head) for a lone request with a long context (the step says
+    so: ``StepContext.decode_far``), or None.  Clusters of 8 CTAs give one request of 8 kv heads
+    64 CTAs for 148 SMs; cut 16 times, in 4 clusters of 4 CTAs per kv head whose first CTAs hand
+    their pieces to the last one through global memory, it has 128 (measured at 16 q / 8 kv
+    heads, us a layer: context 32,700 34.8 against 44.8; 16,000 22.1 against 25.7; 12,300 19.6
+    against 21.6; 8,190 16.7 against 17.0; 2,100 10.9 against 8.9: the hand-over costs about 3 us,
+    so shorter requests keep one cluster of 8)."""
+    if rows != 1 or mixer.head_dim != 128:
+        return None
+    weight = mixer.q_norm_weight
+    for pieces, groups in FAR_PLANS:
+        if kernels.attention_decode_fits_wide(
+                rows * groups, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.head_dim,
+                page_size=page_size, splits=pieces, max_context=max_context,
+                weight_dtype=None if weight is None else weight.dtype):
+            return pieces, groups
+    return None
+
+
 # tiles with fewer tokens than this go to the 64-row kernel: a 128-row tensor-memory tile is mostly
 # empty for them
 TC_MIN_TILE_TOKENS = 32
@@ -155,13 +179,21 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
     if (tiled and ctx.decode_only and writes and ctx.decode_splits > 0
             and kernels.attention_decode_supports(mixer.head_dim, mixer.num_heads, mixer.num_kv_heads,
                                                   ctx.decode_splits)):
+        far = None
+        if ctx.decode_far and ctx.decode_splits > 1:
+            far = far_plan(qkv.shape[0], mixer, keys.shape[2], ctx.max_context)
+        if far is not None:
+            splits, far_groups = far
+            far_from = 1                    # the step is one of a long request: always
+        else:
+            splits = fitted_splits(ctx.decode_splits, qkv.shape[0], mixer, keys.shape[2], ctx.max_context)
+            far_groups, far_from = 1, 0
         return kernels.attention_decode(
             qkv, **heads, positions=ctx.positions, token_row=ctx.token_row, slots=ctx.slots[group],
             q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0,
             cos=cos, sin=sin, key_cache=keys, value_cache=values, block_tables=ctx.block_tables[group],
-            window=mixer.window, scale=mixer.scale,
-            splits=fitted_splits(ctx.decode_splits, qkv.shape[0], mixer, keys.shape[2], ctx.max_context),
-            max_context=ctx.max_context)
+            window=mixer.window, scale=mixer.scale, splits=splits, max_context=ctx.max_context,
+            far_groups=far_groups, far_from=far_from)
     kernels.qk_norm_rope_store(
         qkv, **heads, positions=ctx.positions, q_weight=mixer.q_norm_weight,
         k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps or 0.0, cos=cos, sin=sin,

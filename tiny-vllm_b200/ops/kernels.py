@@ -359,7 +359,8 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
                      cos: torch.Tensor | None, sin: torch.Tensor | None, key_cache: torch.Tensor,
                      value_cache: torch.Tensor, block_tables: torch.Tensor, window: int | None,
                      scale: float, splits: int, max_context: int,
-                     out: torch.Tensor | None = None, new_in_cache: bool = False) -> torch.Tensor:
+                     out: torch.Tensor | None = None, new_in_cache: bool = False,
+                     far_groups: int = 1, far_from: int = 0) -> torch.Tensor:
     """One new token per request, from the raw packed projection to the attention output:
     q/k norm and rotation, cache write (unless ``slots`` is None) and attention in one launch.
     ``new_in_cache``: the new tokens' keys and values are in the cache already and q comes
@@ -396,6 +397,23 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
         raise KernelError("attention_decode: tables must be float32 [positions, head_dim / 2]")
     if out is None:
         out = torch.empty((requests, num_q * head_dim), dtype=qkv.dtype, device=qkv.device)
+    if far_groups > 1:
+        # a request of far_from keys or more is cut over far_groups clusters per kv head, which
+        # leave their pieces in global memory (head size 128; all clusters on the GPU at once)
+        pieces, arrived = _far_scratch_of(qkv.device, requests, num_q, num_kv, head_dim, far_groups)
+        fn = _fn("attention_decode", "tvb_attention_decode_far",
+                 [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                  c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+        _check(fn(qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos), _ptr(sin), table_positions,
+                  positions.data_ptr(), token_row.data_ptr(), _ptr(slots), key_cache.data_ptr(),
+                  value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
+                  key_cache.shape[2], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
+                  splits, 2 if new_in_cache else (1 if slots is not None else 0), max_context, weight_tag,
+                  _pdl("attention"), far_groups, max(1, far_from), pieces.data_ptr(), arrived.data_ptr(),
+                  _stream()),
+               "attention_decode (far)")
+        return out
     fn = _fn("attention_decode", "tvb_attention_decode",
              [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -412,6 +430,24 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
 
 
 _fits_wide: dict[tuple, bool] = {}
+_far_scratch: dict[int, list] = {}
+
+
+def _far_scratch_of(device: torch.device, requests: int, num_q: int, num_kv: int, head_dim: int,
+                    groups: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Pieces and counters of the decode attention that cuts a request over several clusters, per
+    device; they grow with the largest launch and the earlier ones are kept, since CUDA graphs keep
+    their addresses.  Launches that use them must follow one another (those of one stream do)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    floats = _fn("attention_decode", "tvb_attention_decode_far_floats",
+                 [c_int, c_int, c_int, c_int, c_int], c_longlong)(requests, num_q, num_kv, head_dim, groups)
+    if floats <= 0:
+        raise KernelError("attention_decode (far): the kernel does not take these heads")
+    held = _far_scratch.setdefault(index, [])
+    if not held or held[-1][0].numel() < floats or held[-1][1].numel() < requests * num_q:
+        held.append((torch.empty(floats, dtype=torch.float32, device=device),
+                     torch.zeros(max(requests * num_q, 1024), dtype=torch.int32, device=device)))
+    return held[-1]
 
 
 def attention_decode_fits_wide(rows: int, *, num_q: int, num_kv: int, head_dim: int, page_size: int,
