@@ -277,6 +277,11 @@ decode_attention_kernel(const bf16* qkv, const W* __restrict__ q_weight,
     const int request = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = num_q + 2 * num_kv;
+    // The block table's row is asked into L1 while position and row are on their way (in a step of
+    // decoded tokens only, request i is row i; a wrong guess costs nothing): the look-up of the
+    // pages then does not wait for a second trip to L2.
+    if (threadIdx.x * 32 < table_stride && threadIdx.x < 64)
+        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(block_tables + (int64_t)request * table_stride + threadIdx.x * 32));
     const int position = positions[request];
     const int row = token_row[request];
     bf16* out_row = out + ((int64_t)request * num_q + first_q_head) * HEAD_DIM;
