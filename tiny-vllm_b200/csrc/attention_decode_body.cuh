@@ -1,3 +1,7 @@
+// This file is the body of the libraries attention_decode_<head size>_<norm weight type>.cu: each of
+// them defines TVB_DECODE_HEAD_DIM (64, 128 or 256) and TVB_DECODE_WEIGHT (float or bf16) and
+// includes it, so that a model compiles the one combination it uses (a sixth of the templates).
+//
 // Decode attention for bfloat16: one new token per request, fused from the packed
 // projection to the attention output.
 //
@@ -896,9 +900,13 @@ static int decode_heads_per_cta(int group, int head_dim) {
     return 1;
 }
 
-// 1 if the kernel takes this shape: head sizes 64, 128, 256; any whole number of q heads per kv head.
+template <typename T> constexpr int tvb_dtype_tag_of();
+template <> constexpr int tvb_dtype_tag_of<float>() { return TVB_F32; }
+template <> constexpr int tvb_dtype_tag_of<bf16>() { return TVB_BF16; }
+
+// 1 if this library takes the shape: its head size; any whole number of q heads per kv head.
 extern "C" int tvb_attention_decode_supports(int head_dim, int num_q, int num_kv, int splits) {
-    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return 0;
+    if (head_dim != TVB_DECODE_HEAD_DIM) return 0;
     if (num_kv <= 0 || num_q <= 0 || num_q % num_kv) return 0;
     return splits >= 1 && splits <= DEC_MAX_SPLITS;
 }
@@ -956,7 +964,7 @@ static int decode_dispatch(const void* qkv, const void* q_weight, const void* k_
                     sm_count
 #define DECODE_BY_WARPS(D, H, WT)                                       \
     do {                                                                \
-        if (D == 128) {                                                       \
+        if constexpr (D == 128) {                                             \
             const bool all_at_once = wide && launch_decode<128, H, 8, 1, 16, 2, WT>(DECODE_ARGS, &wide_room) == 0 && clusters <= wide_room; \
             if (fits_wide) { *fits_wide = all_at_once ? 1 : 0; return 0; }        \
             if (far.groups > 1) {                                                 \
@@ -967,12 +975,13 @@ static int decode_dispatch(const void* qkv, const void* q_weight, const void* k_
             if (all_at_once) return launch_decode<128, H, 8, 1, 16, 2, WT>(DECODE_ARGS); \
             if (roomy) return launch_decode<128, H, 4, 3, 16, 2, WT>(DECODE_ARGS); \
             return launch_decode<128, H, 3, 4, 16, 2, WT>(DECODE_ARGS);       \
+        } else {                                                              \
+            const bool all_at_once = wide && launch_decode<D, H, 8, 1, 8, 2, WT>(DECODE_ARGS, &wide_room) == 0 && clusters <= wide_room; \
+            if (fits_wide) { *fits_wide = all_at_once ? 1 : 0; return 0; }        \
+            if (all_at_once) return launch_decode<D, H, 8, 1, 8, 2, WT>(DECODE_ARGS); \
+            if (roomy) return launch_decode<D, H, 4, (D > 128 ? 1 : 3), 8, 2, WT>(DECODE_ARGS); \
+            return launch_decode<D, H, 4, (D > 128 ? 1 : 4), 8, 2, WT>(DECODE_ARGS);            \
         }                                                                     \
-        const bool all_at_once = wide && launch_decode<D, H, 8, 1, 8, 2, WT>(DECODE_ARGS, &wide_room) == 0 && clusters <= wide_room; \
-        if (fits_wide) { *fits_wide = all_at_once ? 1 : 0; return 0; }        \
-        if (all_at_once) return launch_decode<D, H, 8, 1, 8, 2, WT>(DECODE_ARGS); \
-        if (roomy) return launch_decode<D, H, 4, (D > 128 ? 1 : 3), 8, 2, WT>(DECODE_ARGS); \
-        return launch_decode<D, H, 4, (D > 128 ? 1 : 4), 8, 2, WT>(DECODE_ARGS);            \
     } while (0)
 #define DECODE_BY_HPB(D, WT)                                            \
     do {                                                                \
@@ -981,14 +990,9 @@ static int decode_dispatch(const void* qkv, const void* q_weight, const void* k_
         if (hpb == 8) DECODE_BY_WARPS(D, 8, WT);                        \
         DECODE_BY_WARPS(D, 4, WT);                                      \
     } while (0)
-#define DECODE_BY_DIM(WT)                                               \
-    do {                                                                \
-        if (head_dim == 64) DECODE_BY_HPB(64, WT);                      \
-        if (head_dim == 128) DECODE_BY_HPB(128, WT);                    \
-        DECODE_BY_HPB(256, WT);                                         \
-    } while (0)
-    if (weight_dtype == TVB_F32) DECODE_BY_DIM(float);
-    if (weight_dtype == TVB_BF16) DECODE_BY_DIM(bf16);
+    // this library holds one head size and one type of norm weights
+    if (head_dim != TVB_DECODE_HEAD_DIM || weight_dtype != tvb_dtype_tag_of<TVB_DECODE_WEIGHT>()) return TVB_BAD_ARGUMENT;
+    DECODE_BY_HPB(TVB_DECODE_HEAD_DIM, TVB_DECODE_WEIGHT);
     return TVB_BAD_ARGUMENT;
 }
 

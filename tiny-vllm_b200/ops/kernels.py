@@ -91,6 +91,28 @@ def _fn(library: str, name: str, argtypes, restype=c_int):
     return function
 
 
+def _fn_of(library: str, name: str, argtypes, restype=c_int):
+    """:func:`_fn` for a function that several libraries define (one per head size and weight type)."""
+    key = f"{library}:{name}"
+    function = _functions.get(key)
+    if function is None:
+        function = getattr(load_library(library), name)
+        function.argtypes = argtypes
+        function.restype = restype
+        _functions[key] = function
+    return function
+
+
+DECODE_HEAD_DIMS = (64, 128, 256)
+
+
+def _decode_library(head_dim: int, weight_tag: int) -> str:
+    """The fused decode attention is compiled per head size and type of norm weights."""
+    if head_dim not in DECODE_HEAD_DIMS:
+        raise KernelError(f"attention_decode takes head sizes {DECODE_HEAD_DIMS}, not {head_dim}")
+    return f"attention_decode_{head_dim}_{'f32' if weight_tag == F32 else 'bf16'}"
+
+
 # ------------------------------------------------------------------ embedding
 def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = table[ids[t]]; ids int32."""
@@ -348,9 +370,14 @@ def sample_rows(logits: torch.Tensor, packed: torch.Tensor, out: torch.Tensor | 
 
 
 # ------------------------------------------------- tiled attention (bfloat16)
+DECODE_MAX_PIECES = 8
+
+
 def attention_decode_supports(head_dim: int, num_q: int, num_kv: int, splits: int) -> bool:
-    fn = _fn("attention_decode", "tvb_attention_decode_supports", [c_int, c_int, c_int, c_int])
-    return bool(fn(head_dim, num_q, num_kv, splits))
+    """Head sizes 64, 128 and 256, whole groups of q heads, 1 to 8 pieces (answered here, so that
+    asking compiles nothing; the libraries check the same)."""
+    return (head_dim in DECODE_HEAD_DIMS and num_q > 0 and num_kv > 0 and num_q % num_kv == 0
+            and 1 <= splits <= DECODE_MAX_PIECES)
 
 
 def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: int,
@@ -400,8 +427,8 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
     if far_groups > 1:
         # a request of far_from keys or more is cut over far_groups clusters per kv head, which
         # leave their pieces in global memory (head size 128; all clusters on the GPU at once)
-        pieces, arrived = _far_scratch_of(qkv.device, requests, num_q, num_kv, head_dim, far_groups)
-        fn = _fn("attention_decode", "tvb_attention_decode_far",
+        pieces, arrived = _far_scratch_of(qkv.device, requests, num_q, num_kv, head_dim, far_groups, weight_tag)
+        fn = _fn_of(_decode_library(head_dim, weight_tag), "tvb_attention_decode_far",
                  [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
                   c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
@@ -414,7 +441,7 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
                   _stream()),
                "attention_decode (far)")
         return out
-    fn = _fn("attention_decode", "tvb_attention_decode",
+    fn = _fn_of(_decode_library(head_dim, weight_tag), "tvb_attention_decode",
              [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
               c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p])
@@ -434,13 +461,13 @@ _far_scratch: dict[int, list] = {}
 
 
 def _far_scratch_of(device: torch.device, requests: int, num_q: int, num_kv: int, head_dim: int,
-                    groups: int) -> tuple[torch.Tensor, torch.Tensor]:
+                    groups: int, weight_tag: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Pieces and counters of the decode attention that cuts a request over several clusters, per
     device; they grow with the largest launch and the earlier ones are kept, since CUDA graphs keep
     their addresses.  Launches that use them must follow one another (those of one stream do)."""
     index = device.index if device.index is not None else torch.cuda.current_device()
-    floats = _fn("attention_decode", "tvb_attention_decode_far_floats",
-                 [c_int, c_int, c_int, c_int, c_int], c_longlong)(requests, num_q, num_kv, head_dim, groups)
+    floats = _fn_of(_decode_library(head_dim, weight_tag), "tvb_attention_decode_far_floats",
+                    [c_int, c_int, c_int, c_int, c_int], c_longlong)(requests, num_q, num_kv, head_dim, groups)
     if floats <= 0:
         raise KernelError("attention_decode (far): the kernel does not take these heads")
     held = _far_scratch.setdefault(index, [])
@@ -459,8 +486,11 @@ def attention_decode_fits_wide(rows: int, *, num_q: int, num_kv: int, head_dim: 
     key = (rows, num_q, num_kv, head_dim, page_size, splits, max_context, tag)
     known = _fits_wide.get(key)
     if known is None:
-        fn = _fn("attention_decode", "tvb_attention_decode_fits_wide",
-                 [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int])
+        if head_dim not in DECODE_HEAD_DIMS:
+            _fits_wide[key] = False
+            return False
+        fn = _fn_of(_decode_library(head_dim, tag), "tvb_attention_decode_fits_wide",
+                    [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int])
         known = _fits_wide[key] = bool(fn(rows, num_q, num_kv, head_dim, page_size, splits, max_context, tag))
     return known
 
