@@ -1,3 +1,7 @@
+// This file is the body of the libraries gemm_small_m_nt<1..4>.cu: each defines TVB_SMALL_M_NT (the
+// number of 8-row groups of x it is compiled for) and includes it, so that a decode step compiles
+// the templates of its own batch size only.
+//
 // out[M,N] = x[M,K] . W[N,K]^T for a handful of rows (decode): a weight-streaming
 // kernel.  With M <= 32 every weight is used once, so the product is bound by reading
 // W from HBM; the kernel is built around that read, not around the arithmetic.
@@ -425,13 +429,9 @@ extern "C" int tvb_gemm_small_m(const void* x, long long ldx, const void* w, lon
         if (norm_kind == 3) return SMALL_M(NT, MODE, 3);    \
         return SMALL_M(NT, MODE, 4);                        \
     } while (0)
-#define BY_NT(MODE)                                  \
-    do {                                             \
-        if (nt == 1) BY_NORM(1, MODE);               \
-        if (nt == 2) BY_NORM(2, MODE);               \
-        if (nt == 3) BY_NORM(3, MODE);               \
-        BY_NORM(4, MODE);                            \
-    } while (0)
+    // this library holds one number of 8-row groups
+    if (nt != TVB_SMALL_M_NT) return TVB_BAD_ARGUMENT;
+#define BY_NT(MODE) BY_NORM(TVB_SMALL_M_NT, MODE)
     if (mode == MODE_BF16) BY_NT(MODE_BF16);
     if (mode == MODE_F32) BY_NT(MODE_F32);
     BY_NT(MODE_SILU);

@@ -1,0 +1,4 @@
+// The weight-streaming product for 9 to 16 rows of x: one of four libraries made of
+// gemm_small_m_body.cuh, so that a decode step compiles the templates of its own batch size only.
+#define TVB_SMALL_M_NT 2
+#include "gemm_small_m_body.cuh"

@@ -18,6 +18,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -56,10 +57,26 @@ def _find_nvcc() -> str:
         "the CUDA kernels cannot be built and there is no other path")
 
 
+_INCLUDE = re.compile(r'^\s*#\s*include\s*"([^"]+)"', re.MULTILINE)
+
+
+def _sources_of(name: str) -> list[Path]:
+    """``csrc/<name>.cu`` and the files of this folder that it includes, directly or not."""
+    found: dict[str, Path] = {}
+    waiting = [CSRC / f"{name}.cu"]
+    while waiting:
+        path = waiting.pop()
+        if path.name in found or not path.is_file():
+            continue
+        found[path.name] = path
+        waiting.extend(CSRC / included for included in _INCLUDE.findall(path.read_text(errors="replace")))
+    return [found[key] for key in sorted(found)]
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS + EXTRA_LINK.get(name, ())).encode())
-    for path in [CSRC / f"{name}.cu", *sorted(CSRC.glob("*.cuh")), *sorted(CSRC.glob("*.h"))]:
+    for path in _sources_of(name):
         h.update(path.name.encode())
         h.update(path.read_bytes())
     return h.hexdigest()[:16]

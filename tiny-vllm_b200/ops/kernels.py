@@ -648,8 +648,8 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
     rows = w.shape[0]
     if w.shape[1] != k or x.stride(1) != 1 or w.stride(1) != 1:
         raise KernelError("gemm_small_m: x [m, k] and w [n, k] with contiguous rows")
-    if m > SMALL_M_MAX_ROWS or k % 8 or x.stride(0) % 8 or w.stride(0) % 8:
-        raise KernelError(f"gemm_small_m takes up to {SMALL_M_MAX_ROWS} rows, k and row strides "
+    if m < 1 or m > SMALL_M_MAX_ROWS or k % 8 or x.stride(0) % 8 or w.stride(0) % 8:
+        raise KernelError(f"gemm_small_m takes up to {SMALL_M_MAX_ROWS} rows (and one at least), k and row strides "
                           f"multiples of 8 (m {m}, k {k})")
     if mode == GEMM_SILU and rows % 2:
         raise KernelError("gemm_small_m: a [gate | up] weight has an even number of rows")
@@ -686,7 +686,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, mode: int = GEMM_BF16, *,
     if out is None:
         out = torch.empty((m, n), dtype=torch.float32 if mode == GEMM_F32 else torch.bfloat16,
                           device=x.device)
-    fn = _fn("gemm_small_m", "tvb_gemm_small_m",
+    fn = _fn_of(f"gemm_small_m_nt{(m + 7) // 8}", "tvb_gemm_small_m",
              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
               c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p, c_longlong, c_int, c_void_p])
