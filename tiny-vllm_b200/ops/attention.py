@@ -222,7 +222,8 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
                     slots=None, q_weight=None, k_weight=None, eps=0.0, cos=None, sin=None, key_cache=keys,
                     value_cache=values, block_tables=ctx.block_tables[group], window=mixer.window,
                     scale=mixer.scale, splits=splits, max_context=ctx.max_context, out=out[part],
-                    new_in_cache=True)
+                    new_in_cache=True,
+                    library_of=None if mixer.q_norm_weight is None else mixer.q_norm_weight.dtype)
                 continue
             # chunks for the longest context a request may reach, not for this step's: the count is
             # then the same for every step with these entry sizes, which a recorded step relies on

@@ -387,7 +387,8 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
                      value_cache: torch.Tensor, block_tables: torch.Tensor, window: int | None,
                      scale: float, splits: int, max_context: int,
                      out: torch.Tensor | None = None, new_in_cache: bool = False,
-                     far_groups: int = 1, far_from: int = 0) -> torch.Tensor:
+                     far_groups: int = 1, far_from: int = 0,
+                     library_of: torch.dtype | None = None) -> torch.Tensor:
     """One new token per request, from the raw packed projection to the attention output:
     q/k norm and rotation, cache write (unless ``slots`` is None) and attention in one launch.
     ``new_in_cache``: the new tokens' keys and values are in the cache already and q comes
@@ -414,7 +415,9 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
             raise KernelError("attention_decode: index tensors must be contiguous int32")
     if new_in_cache and not (slots is None and q_weight is None and k_weight is None and cos is None and sin is None):
         raise KernelError("attention_decode: with new_in_cache nothing is normalised, rotated or stored")
-    weight_tag = BF16
+    # without norm weights either library of the head size does: ``library_of`` names the type of
+    # the one the caller uses elsewhere, so that no second one is compiled
+    weight_tag = BF16 if library_of is None else dtype_tag(library_of)
     if q_weight is not None:
         if k_weight is None or q_weight.dtype != k_weight.dtype or q_weight.shape != (head_dim,):
             raise KernelError("attention_decode: norm weights come together, [head_dim], one dtype")
