@@ -50,11 +50,15 @@ def decode_splits(max_model_len: int, rows: int = 1) -> int:
     2 pieces 30.9, 4 pieces 31.9; 20 rows 1 piece 44.1, 2 pieces 40.3, 4 pieces 48.8; 24 rows
     1 piece 44.4, 2 pieces 43.3, 3 pieces 53.8; 32 rows 1 piece 53.1, 2 pieces 56.0; 48 rows
     1 piece 78.7, 2 pieces 88.7; 64 rows 2 pieces 95.9, 1 piece 104.4, 3 pieces 102.5).
+    Between 37 and 45 rows one piece a request gives a few SMs a third CTA with a whole context to
+    read, which the others wait for; three pieces even that out (36 rows 1 piece 59.8, 3 pieces
+    64.1; 38 rows 71.7 and 65.5; 40 rows 74.0 and 68.7; 44 rows 75.7 and 73.4; 46 rows 77.6 and
+    85.9).
     A request's result differs between piece counts by rounding only (the order in which partial
     sums are merged)."""
     by_length = max(1, min(DECODE_MAX_SPLITS, -(-max_model_len // DECODE_SPLIT_GRAIN)))
     rows = max(rows, 1)
-    by_rows = 2 if rows > 48 else max(1, min(DECODE_MAX_SPLITS, (64 + rows) // (2 * rows)))
+    by_rows = 2 if rows > 48 else 3 if 37 <= rows <= 45 else max(1, min(DECODE_MAX_SPLITS, (64 + rows) // (2 * rows)))
     return max(1, min(by_length, by_rows))
 
 
