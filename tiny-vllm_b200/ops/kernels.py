@@ -41,10 +41,14 @@ _launches = 0
 
 # Programmatic dependent launch for the kernels that wait for their predecessor themselves
 # (griddepcontrol.wait): they may start, and fetch weights, while the kernel before them ends.
-# TINYVLLM_B200_PDL=0 turns it off; a comma-separated list (gemm,norm,attention,prefill,sample) keeps
-# it for those kernels only (attention: the decode attention; prefill: the prompt's q/k norm, rotation
-# and cache write, and the tcgen05 attention).
-_PDL_DEFAULT = ("gemm", "norm")
+# TINYVLLM_B200_PDL=0 turns it off; a comma-separated list (gemm,norm,attention,attention_few,prefill,
+# sample) keeps it for those kernels only (attention: the decode attention at every batch size;
+# attention_few: with up to PDL_ATTENTION_ROWS rows only, where its CTAs of eight warps find the SMs
+# free: batch 1 to 3 gain 3 to 4 %, batch 4 is level and batch 6 loses 3 %, its clusters waiting
+# for room beside the projection's CTAs; prefill: the prompt's q/k norm, rotation and cache write,
+# and the tcgen05 attention).
+_PDL_DEFAULT = ("gemm", "norm", "attention_few")
+PDL_ATTENTION_ROWS = 3
 _setting = os.environ.get("TINYVLLM_B200_PDL", "1")
 PDL = frozenset() if _setting == "0" else frozenset(_PDL_DEFAULT if _setting == "1" else _setting.split(","))
 
@@ -427,6 +431,7 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
         raise KernelError("attention_decode: tables must be float32 [positions, head_dim / 2]")
     if out is None:
         out = torch.empty((requests, num_q * head_dim), dtype=qkv.dtype, device=qkv.device)
+    pdl = _pdl("attention") or (_pdl("attention_few") if requests <= PDL_ATTENTION_ROWS else 0)
     if far_groups > 1:
         # a request of far_from keys or more is cut over far_groups clusters per kv head, which
         # leave their pieces in global memory (head size 128; all clusters on the GPU at once)
@@ -440,7 +445,7 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
                   value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
                   key_cache.shape[2], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
                   splits, 2 if new_in_cache else (1 if slots is not None else 0), max_context, weight_tag,
-                  _pdl("attention"), far_groups, max(1, far_from), pieces.data_ptr(), arrived.data_ptr(),
+                  pdl, far_groups, max(1, far_from), pieces.data_ptr(), arrived.data_ptr(),
                   _stream()),
                "attention_decode (far)")
         return out
@@ -453,7 +458,7 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
               value_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
               key_cache.shape[2], out.data_ptr(), requests, num_q, num_kv, head_dim, window or 0, scale,
               splits, 2 if new_in_cache else (1 if slots is not None else 0), max_context, weight_tag,
-              _pdl("attention"),
+              pdl,
               _stream()),
            "attention_decode")
     return out
