@@ -23,7 +23,12 @@ def test_pieces_are_bounded_by_the_context_limit():
     assert decode_splits(1, 1) == 1
 
 
-def test_tiles_cover_every_token_once():
+def test_tiles_cover_every_token_once(monkeypatch):
+    from tinyvllm_b200.ops import kernels
+
+    # the tile sizes of the two kernels, without compiling them
+    monkeypatch.setattr(kernels, "attention_prefill_tile_tokens", lambda: 64)
+    monkeypatch.setattr(kernels, "attention_prefill_tc_tile_tokens", lambda: 128)
     counts, starts = [300, 1, 70, 3, 64, 777], [0, 40, 0, 512, 0, 223]
     big, rest, runs = prefill_tiles(counts, starts, tensor_memory=True, singles_apart=True)
     covered = []
