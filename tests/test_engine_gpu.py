@@ -158,7 +158,8 @@ def test_trace_run_program(dtype_name, model_folders, tmp_path):
 def test_a_lone_long_request_is_cut_over_several_clusters(model_folders, monkeypatch):
     """From a length on (brought down to 96 tokens here) a request that decodes alone has its keys
     cut over several clusters per kv head: eagerly, and in the decode graph of one row that long
-    requests have for themselves; shorter ones keep the other graph."""
+    requests have for themselves; shorter ones keep the other graph, and one that grows past the
+    length changes over."""
     from tinyvllm_b200.engine.graphs import DecodeGraphs
     from tinyvllm_b200.engine.step import StepEntry
     from tinyvllm_b200.ops import attention as attention_ops
@@ -168,7 +169,8 @@ def test_a_lone_long_request_is_cut_over_several_clusters(model_folders, monkeyp
     monkeypatch.setattr(attention_ops, "FAR_FROM_KEYS", 96)
     name, dtype = "e", torch.bfloat16
     vocab = TINY_CONFIGS[name].vocab_size
-    requests = {"long": random_tokens(vocab, 400, 77), "short": random_tokens(vocab, 60, 78)}
+    requests = {"long": random_tokens(vocab, 400, 77), "short": random_tokens(vocab, 60, 78),
+                "grows": random_tokens(vocab, 104, 79)}
     tail = 24
     seen = []
     real = kernels.attention_decode
@@ -190,21 +192,22 @@ def test_a_lone_long_request_is_cut_over_several_clusters(model_folders, monkeyp
             for rid, tokens in requests.items():
                 runner.open(rid)
                 runner.run([StepEntry(rid, tuple(tokens[:-tail]), ())])
-                seen.clear()
                 for step in range(tail):
-                    entries = [StepEntry(rid, (tokens[len(tokens) - tail + step],), (0,))]
+                    position = len(tokens) - tail + step
+                    far = position + 1 >= 96       # tokens of the request with its new one
+                    entries = [StepEntry(rid, (tokens[position],), (0,))]
+                    seen.clear()
                     if graphs is None:
                         logits = runner.run(entries)
+                        # every layer's launch says how it was cut
+                        assert seen and all((groups > 1) == far for groups in seen)
                     else:
                         plan = runner.plan(entries)
                         prepared = graphs.prepare(plan, entries, [SamplingParams()], [0])
-                        assert (prepared[0] is graphs.far_bucket) == (rid == "long")
+                        assert (prepared[0] is graphs.far_bucket) == far
                         _, logits = graphs.launch(prepared, plan)
                         runner.manager.commit(plan)
-                    got[(rid, len(tokens) - tail + step)] = logits[0].float().cpu().clone()
-                if graphs is None:                 # eager steps: every layer's launch says how it was cut
-                    assert seen and all(groups > 1 for groups in seen) == (rid == "long")
-                    assert all(groups == 1 for groups in seen) == (rid == "short")
+                    got[(rid, position)] = logits[0].float().cpu().clone()
                 runner.close(rid)
         positions = {rid: {p for (r, p) in got if r == rid} for rid in requests}
         expected = rh.oracle(model_folders[name], requests, dtype, positions=positions)
