@@ -43,9 +43,9 @@ _launches = 0
 # (griddepcontrol.wait): they may start, and fetch weights, while the kernel before them ends.
 # TINYVLLM_B200_PDL=0 turns it off; a comma-separated list (gemm,norm,attention,attention_few,prefill,
 # sample) keeps it for those kernels only (attention: the decode attention at every batch size;
-# attention_few: with up to PDL_ATTENTION_ROWS rows only, where its CTAs of eight warps find the SMs
-# free: batch 1 to 3 gain 3 to 4 %, batch 4 is level and batch 6 loses 3 %, its clusters waiting
-# for room beside the projection's CTAs; prefill: the prompt's q/k norm, rotation and cache write,
+# attention_few: with up to PDL_ATTENTION_ROWS rows and only where the launch runs as CTAs of eight
+# warps that are all on the GPU at once, which find the SMs free: batch 1 to 3 gain 3 to 4 %, batch
+# 4 is level and batch 6 loses 3 %, its clusters waiting for room beside the projection's CTAs; prefill: the prompt's q/k norm, rotation and cache write,
 # and the tcgen05 attention).
 _PDL_DEFAULT = ("gemm", "norm", "attention_few")
 PDL_ATTENTION_ROWS = 3
@@ -108,6 +108,7 @@ def _fn_of(library: str, name: str, argtypes, restype=c_int):
 
 
 DECODE_HEAD_DIMS = (64, 128, 256)
+BF16_OR_F32 = {F32: torch.float32, BF16: torch.bfloat16}
 
 
 def _decode_library(head_dim: int, weight_tag: int) -> str:
@@ -431,7 +432,12 @@ def attention_decode(qkv: torch.Tensor, *, num_q: int, num_kv: int, head_dim: in
         raise KernelError("attention_decode: tables must be float32 [positions, head_dim / 2]")
     if out is None:
         out = torch.empty((requests, num_q * head_dim), dtype=qkv.dtype, device=qkv.device)
-    pdl = _pdl("attention") or (_pdl("attention_few") if requests <= PDL_ATTENTION_ROWS else 0)
+    pdl = _pdl("attention")
+    if not pdl and _pdl("attention_few") and requests <= PDL_ATTENTION_ROWS:
+        # only where the launch runs as CTAs of eight warps, all on the GPU at once
+        pdl = int(attention_decode_fits_wide(
+            requests * far_groups, num_q=num_q, num_kv=num_kv, head_dim=head_dim, page_size=key_cache.shape[2],
+            splits=splits, max_context=max_context, weight_dtype=BF16_OR_F32[weight_tag]))
     if far_groups > 1:
         # a request of far_from keys or more is cut over far_groups clusters per kv head, which
         # leave their pieces in global memory (head size 128; all clusters on the GPU at once)
